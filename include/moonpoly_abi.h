@@ -1,0 +1,148 @@
+/*
+ * C ABI of libmoonpoly_gemm.so -- the B200 (sm_100a) implementation of MoonPoly's
+ * row-column-column GEMM path.  Plain C: PODs, raw device pointers, sizes, an opaque stream
+ * handle (a cudaStream_t passed as void*; NULL = the legacy default stream).  No C++ or torch
+ * types cross this boundary.  Every function returns an mp_status (0 = success) and never
+ * throws, prints or exits; mp_last_error_string() describes the calling thread's last failure.
+ *
+ * "RCC" everywhere: A row-major [m,k] (lda = k), B column-major [k,n] (stored [n,k], ldb = k),
+ * C column-major [m,n] (ldc = m).  All data pointers are DEVICE pointers owned by the caller;
+ * calls are asynchronous on `stream`.  The library has no CPU fallback: without a CUDA device of
+ * compute capability 10.0 every compute entry point fails with MP_ERR_CUDA / MP_ERR_UNSUPPORTED.
+ *
+ * Each entry point names the reference interface (file:line in skwmw01/MoonPoly-dev) it stands for.
+ */
+#ifndef MOONPOLY_ABI_H_
+#define MOONPOLY_ABI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum mp_status {
+  MP_OK = 0,
+  MP_ERR_INVALID_ARG = 1,   /* null pointer, negative size, bad enum value, bad split_n ...      */
+  MP_ERR_LAYOUT = 2,        /* layout other than (A row, B col, C col)                            */
+  MP_ERR_UNALIGNED_K = 3,   /* k % alignment(pid) != 0; nothing was computed                      */
+  MP_ERR_BAD_PID = 4,       /* pid has no kernel                                                  */
+  MP_ERR_WORKSPACE = 5,     /* caller workspace null or too small                                 */
+  MP_ERR_CUDA = 6,          /* a CUDA runtime/driver call failed                                  */
+  MP_ERR_DEVICE = 7,        /* a kernel recorded an error (bounded wait expired ...)              */
+  MP_ERR_UNSUPPORTED = 8    /* device is not sm_100 / dtype not served                            */
+} mp_status;
+
+/* Values of moonpoly::MoonpolyDataType (moonpoly/include/moonpoly.cuh:20-24). */
+enum { MP_FP16 = 0, MP_INT8 = 1, MP_FP32 = 2 };
+
+/* Values of moonpoly::Fp16PolyPattern (moonpoly/include/moonpoly.cuh:33-37). */
+enum { MP_PATTERN_SINGLE = 1, MP_PATTERN_COMBINE = 2, MP_PATTERN_SPLITK = 3 };
+
+/* Same fields and order as moonpoly::Fp16OnlinePlan (moonpoly/include/moonpoly.cuh:39-45). */
+typedef struct mp_plan {
+  int pattern;
+  int pid;
+  int split_k;
+  int split_n;
+  float estimated_ms;
+} mp_plan;
+
+/* moonpoly::moonpoly_gemm (moonpoly/core/moonpoly_gemm.cu:7-39): dtype switch + layout check
+ * (core/fp16/fp16_dispatch.cu:11-27 and siblings).  For MP_INT8 alpha/beta are truncated to int
+ * and C is int32.  Layout other than (0,1,1) -> MP_ERR_LAYOUT; unknown dtype -> MP_ERR_INVALID_ARG. */
+int mp_gemm(int dtype, int m, int n, int k, const void* A, int a_col_major, const void* B,
+            int b_col_major, void* C, int c_col_major, float alpha, float beta, void* stream);
+
+/* moonpoly::moonpolyLinear (moonpoly/core/moonpoly_gemm.cu:41-44): Y[M,N] = X[M,K] * W[N,K]^T,
+ * all row-major; remapped to RCC (m = N, n = M, A = W, B = X), alpha = 1, beta = 0. */
+int mp_linear(int dtype, int M, int N, int K, const void* X, const void* W, void* Y, void* stream);
+
+/* run_moonpoly_gemm_{fp16,fp32,int8}_row_col_col (core/fp16/fp16_rcc.cu:3263-3269,
+ * core/fp32/fp32_rcc.cu:2272-2282, core/int8/i8_rcc.cu:3143-3157): online selector, then the
+ * chosen pattern/pid in one launch. */
+int mp_gemm_rcc(int dtype, int m, int n, int k, const void* A, const void* B, void* C, float alpha,
+                float beta, void* stream);
+
+/* run_moonpoly_selected_gemm_*_row_col_col[_with_workspace] (core/fp16/fp16_rcc.cu:3271-3295,
+ * 3454-3514; core/fp32/fp32_rcc.cu:2284-2299; core/int8/i8_rcc.cu:3159-3169): forced pid with a
+ * run-time split-K factor (split_k <= 0 means 2, as everywhere in the reference).  `workspace` may
+ * be NULL: the library then uses its own per-stream scratch.  A non-NULL workspace must hold
+ * mp_workspace_size() bytes; it needs no initialisation by the caller.
+ * k % alignment(pid) != 0 -> MP_ERR_UNALIGNED_K and C is untouched (the reference prints a
+ * message and returns without computing). */
+int mp_gemm_rcc_pid(int dtype, int pid, int split_k, int m, int n, int k, const void* A,
+                    const void* B, void* C, float alpha, float beta, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* get_gemm_workspace_size_fp16_row_col_col (core/fp16/fp16_rcc.cu:3306-3316), extended to every
+ * pid and dtype: bytes of scratch mp_gemm_rcc_pid needs for this problem (0 when split_k == 1). */
+int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes);
+
+/* select_fp16_online_plan_row_col_col (core/fp16/fp16_rcc.cu:3220-3222 -> 423-505),
+ * select_fp32_online_plan (core/fp32/fp32_rcc.cu:2225-2267),
+ * select_int8_online_plan (core/int8/i8_rcc.cu:3095-3138).  Host only; no device needed. */
+int mp_select_plan(int dtype, int m, int n, int k, mp_plan* plan);
+
+/* get_gemm_shared_mem_* / get_gemm_alignment_* (core/fp16/fp16_rcc.cu:3534-3553,
+ * core/fp32/fp32_rcc.cu:2302-2311, core/int8/i8_rcc.cu:3171-3181): tile = [pm, pn, pk] where pm
+ * tiles RCC n and pn tiles RCC m; alignment = required divisor of k. */
+int mp_pid_info(int dtype, int pid, int tile[3], int* alignment);
+
+/* gemm_cost_model / gemm_splitk_cost_model (core/fp16/fp16_rcc_cost.cu:161-237 and the fp32/int8
+ * siblings): predicted milliseconds of pid with split_k slices on RCC (m,n,k). */
+int mp_cost_ms(int dtype, int pid, int split_k, int m, int n, int k, float* ms);
+
+/* run_fp16_pattern2_twin_gemm_row_col_col (core/fp16/fp16_rcc.cu:3297-3304 -> 75-108): columns
+ * [0,split_n) and [split_n,n) of C are produced by two tile shapes inside ONE launch.
+ * split_n <= 0 picks 3/4 of n rounded down to 128.  Requires 0 < split_n < n, split_n % 128 == 0,
+ * k % 8 == 0, else MP_ERR_INVALID_ARG (the reference throws std::invalid_argument). */
+int mp_twin_gemm_fp16(int m, int n, int k, int split_n, const void* A, const void* B, void* C,
+                      float alpha, float beta, void* stream);
+
+/* scaled_mm_mikpoly -> cutlass_scaled_mm_mikpoly_unified
+ * (core/int8/scaled_mm/scaled_mm_bindings.cpp:20-92, scaled_mm_mikpoly_unified.cu:362-403):
+ * out[M,N] (row-major, ldc) = a_scales[m] * (b_scales[n] * int32(A[M,K] * B_nk[N,K]^T)) (+ bias[n]),
+ * rounded as the reference's epilogue does (scaled_mm_epilogues_mikpoly.hpp:40-119).
+ * a_scales has M entries or one (a_scalar != 0); b_scales N entries or one.  bias is NULL or N
+ * values of the output type.  out_dtype: 0 = fp16, 1 = bf16. */
+int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t* B_nk, int ldb,
+                    const float* a_scales, int a_scalar, const float* b_scales, int b_scalar,
+                    const void* bias, void* out, int ldc, int out_dtype, void* stream);
+
+/* predict_best_sm80_evt_config / get_sm80_evt_config
+ * (core/int8/scaled_mm/scaled_mm_mikpoly_unified.cu:405-414): tile id the scaled matmul would
+ * pick for (M,N,K), and a tile's (tile_m, tile_n, tile_k, alignment). */
+int mp_scaled_mm_predict(int M, int N, int K);
+int mp_scaled_mm_config(int config_id, int out[4]);
+
+/* is_paper_elite_fp16_pid / paper_elite_fp16_kernel_count / paper_elite_fp16_pids
+ * (generated/fp16/rcc/candidates.cu:35-60). `pids` may be NULL; returns the count. */
+int mp_elite_fp16_pids(int* pids, int capacity);
+
+/* The reference reads its MOONPOLY_* environment flags on every call (core/fp16/fp16_rcc.cu:110-144).
+ * This library caches numeric flags at first use; mp_reload_env() re-reads all of them and drops
+ * memoised plans.  The force-split and enable flags that the reference's tests toggle between
+ * calls are re-read on every call regardless. */
+int mp_reload_env(void);
+
+/* Waits for `stream` (NULL: the whole device) and reports the device-side status word: 0, or the
+ * first error a kernel recorded since the last call (then cleared).  Returns MP_ERR_DEVICE when
+ * the word was non-zero. */
+int mp_device_status(void* stream, int* device_code);
+
+/* Number of SMs of the current device (the reference's constant num_SM = 108,
+ * moonpoly/include/moonpoly.cuh:26, becomes a query); <= 0 when no device is present. */
+int mp_num_sms(void);
+
+/* Number of kernels this library has launched from the calling process so far. */
+unsigned long long mp_launch_count(void);
+
+const char* mp_last_error_string(void);
+const char* mp_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOONPOLY_ABI_H_ */

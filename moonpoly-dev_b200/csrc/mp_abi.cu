@@ -1,0 +1,583 @@
+// C ABI of libmoonpoly_gemm.so: argument checks, plan selection, tensor-map set-up, launches.
+// See include/moonpoly_abi.h for the contract of every entry point.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/moonpoly_abi.h"
+#include "mp_select.h"
+#include "mp_simt_gemm.cuh"
+#include "mp_umma_gemm.cuh"
+
+namespace {
+
+using namespace mp;
+
+thread_local char g_err[512] = "";
+std::atomic<unsigned long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define MP_CUDA_TRY(expr)                                                                         \
+  do {                                                                                            \
+    cudaError_t e__ = (expr);                                                                     \
+    if (e__ != cudaSuccess)                                                                       \
+      return fail(MP_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__,  \
+                  __LINE__);                                                                      \
+  } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// per-device state
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int sms = 0;
+  int cc = 0;
+  bool attrs[3] = {false, false, false};
+};
+constexpr int kMaxDevices = 32;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_mu;
+
+int device_state(DeviceState** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MP_ERR_CUDA, "no CUDA device: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(MP_ERR_CUDA, "device index %d out of range", dev);
+  DeviceState& d = g_dev[dev];
+  if (!d.ready) {
+    std::lock_guard<std::mutex> g(g_mu);
+    if (!d.ready) {
+      int major = 0, minor = 0;
+      MP_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+      MP_CUDA_TRY(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+      MP_CUDA_TRY(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+      d.cc = major * 10 + minor;
+      if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        MP_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (fn == nullptr || q != cudaDriverEntryPointSuccess)
+          return fail(MP_ERR_CUDA, "driver has no cuTensorMapEncodeTiled");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+      }
+      set_num_sms_for_model(d.sms);
+      d.ready = true;
+    }
+  }
+  if (d.cc != 100 && d.cc != 103)
+    return fail(MP_ERR_UNSUPPORTED, "device compute capability %d.%d is not sm_100: this library has no other path",
+                d.cc / 10, d.cc % 10);
+  *out = &d;
+  return MP_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// scratch pool: one buffer per (device, stream), grown on demand, counters kept zero by the kernels
+// ------------------------------------------------------------------------------------------------
+struct Scratch {
+  int dev; cudaStream_t stream; uint8_t* ptr; size_t bytes; size_t counter_bytes;
+};
+std::vector<Scratch> g_scratch;
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes, uint8_t** counters,
+                uint8_t** partials) {
+  int dev = 0;
+  MP_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> g(g_mu);
+  Scratch* s = nullptr;
+  for (auto& e : g_scratch)
+    if (e.dev == dev && e.stream == stream) { s = &e; break; }
+  const size_t want_counters = std::max<size_t>(round_up(counter_bytes, 256), 1 << 16);
+  if (s == nullptr || s->counter_bytes < want_counters || s->bytes < want_counters + partial_bytes) {
+    // Grow: a fresh, larger buffer.  The old one is kept (work already queued may still use it).
+    const size_t cb = std::max(want_counters, s ? s->counter_bytes : 0);
+    const size_t total = cb + std::max<size_t>(round_up(partial_bytes, 1 << 20) * 2, 8 << 20);
+    uint8_t* p = nullptr;
+    MP_CUDA_TRY(cudaMalloc(&p, total));
+    MP_CUDA_TRY(cudaMemsetAsync(p, 0, cb, stream));
+    if (s == nullptr) {
+      g_scratch.push_back(Scratch{dev, stream, p, total, cb});
+      s = &g_scratch.back();
+    } else {
+      s->ptr = p; s->bytes = total; s->counter_bytes = cb;
+    }
+  }
+  *counters = s->ptr;
+  *partials = s->ptr + s->counter_bytes;
+  return MP_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// problem description shared by all dtypes
+// ------------------------------------------------------------------------------------------------
+struct Problem {
+  int dtype;                 // MP_FP16 / MP_INT8 / MP_FP32
+  int epi;                   // EPI_* (tensor path) -- SEPI_* share the numbering for 0..2
+  int m, n, k;               // rows of A, rows of B (stored [n,k]), reduction length
+  const void* A; long long lda;
+  const void* B; long long ldb;
+  void* C; long long c_stride_m, c_stride_n;
+  float alpha = 1.0f, beta = 0.0f;
+  int ialpha = 1, ibeta = 0;
+  const float* a_scales = nullptr; const float* b_scales = nullptr;
+  int a_scalar = 0, b_scalar = 0;
+  const void* bias = nullptr;
+  int out_bf16 = 0;
+};
+
+struct Launch {
+  int orient = 0, bn = 128, split_k = 1;
+  int split_n = 0, bn1 = 0;   // twin: second region [split_n, n) with its own UMMA-N
+  void* workspace = nullptr; size_t workspace_bytes = 0;
+};
+
+int elem_bytes(int dtype) { return dtype == MP_FP16 ? 2 : dtype == MP_INT8 ? 1 : 4; }
+
+int make_tmap(CUtensorMap* tm, int dtype, const void* ptr, long long rows, long long k, long long ld, int box_rows) {
+  const int eb = elem_bytes(dtype);
+  cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)(ld * eb)};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / eb), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == MP_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUresult r = g_encode(tm, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return MP_OK;
+}
+
+bool tma_compatible(const Problem& p) {
+  const int eb = elem_bytes(p.dtype);
+  if (p.k <= 0) return false;
+  if ((reinterpret_cast<uintptr_t>(p.A) & 15) || (reinterpret_cast<uintptr_t>(p.B) & 15)) return false;
+  if ((p.lda * eb) % 16 != 0 || (p.ldb * eb) % 16 != 0) return false;
+  return true;
+}
+
+size_t umma_workspace_bytes(const Problem& p, const Launch& l, size_t* counter_bytes) {
+  const int P = l.orient == 0 ? p.m : p.n;
+  const int Q = l.orient == 0 ? p.n : p.m;
+  const int tiles_p = (P + kUmmaM - 1) / kUmmaM;
+  long long tiles;
+  int bn_max = l.bn;
+  if (l.split_n > 0) {
+    tiles = (long long)tiles_p * ((l.split_n + l.bn - 1) / l.bn + (Q - l.split_n + l.bn1 - 1) / l.bn1);
+    bn_max = std::max(l.bn, l.bn1);
+  } else {
+    tiles = (long long)tiles_p * ((Q + l.bn - 1) / l.bn);
+  }
+  const size_t cb = round_up((size_t)tiles * 4 * sizeof(unsigned), 256);
+  if (counter_bytes) *counter_bytes = cb;
+  if (l.split_k <= 1) return 0;
+  return cb + (size_t)tiles * l.split_k * bn_max * kUmmaM * 4;
+}
+
+template <int KIND, int EPI>
+int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CUtensorMap& ty0,
+                  const CUtensorMap& ty1, const UmmaParams& up, int grid, size_t smem, cudaStream_t stream) {
+  auto kern = umma_gemm_kernel<KIND, EPI>;
+  if (!d.attrs[attr_slot]) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    d.attrs[attr_slot] = true;
+  }
+  kern<<<grid, kUmmaThreads, smem, stream>>>(tx, ty0, ty1, up);
+  MP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
+// Tensor-core path (FP16 / INT8).
+int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+
+  UmmaParams up{};
+  const bool swap = l.orient == 1;
+  const void* X = swap ? p.B : p.A;
+  const void* Y = swap ? p.A : p.B;
+  const long long ldx = swap ? p.ldb : p.lda, ldy = swap ? p.lda : p.ldb;
+  up.P = swap ? p.n : p.m;
+  up.Q = swap ? p.m : p.n;
+  up.K = p.k;
+  up.out = p.C;
+  up.out_stride_p = swap ? p.c_stride_n : p.c_stride_m;
+  up.out_stride_q = swap ? p.c_stride_m : p.c_stride_n;
+  up.tiles_p = (up.P + kUmmaM - 1) / kUmmaM;
+  up.group_p = 8;
+  int bn_max = l.bn;
+  if (l.split_n > 0) {
+    up.num_regions = 2;
+    up.reg[0] = Region{0, l.split_n, l.bn, (l.split_n + l.bn - 1) / l.bn, 0};
+    up.reg[1] = Region{l.split_n, up.Q, l.bn1, (up.Q - l.split_n + l.bn1 - 1) / l.bn1,
+                       up.tiles_p * up.reg[0].tiles_q};
+    up.total_tiles = up.tiles_p * (up.reg[0].tiles_q + up.reg[1].tiles_q);
+    bn_max = std::max(l.bn, l.bn1);
+  } else {
+    up.num_regions = 1;
+    up.reg[0] = Region{0, up.Q, l.bn, (up.Q + l.bn - 1) / l.bn, 0};
+    up.reg[1] = up.reg[0];
+    up.total_tiles = up.tiles_p * up.reg[0].tiles_q;
+  }
+  const int kb_elems = p.dtype == MP_INT8 ? 128 : 64;
+  up.kb_total = (p.k + kb_elems - 1) / kb_elems;
+  int S = std::max(1, std::min(l.split_k, up.kb_total));
+  up.kb_per_slice = (up.kb_total + S - 1) / S;
+  S = (up.kb_total + up.kb_per_slice - 1) / up.kb_per_slice;   // every slice non-empty
+  up.split_k = S;
+  l.split_k = S;
+  up.stage_bytes = kXTileBytes + bn_max * kRowBytes;
+  up.stages = std::min(kMaxStages, (kSmemBudget - 1024 - 256) / up.stage_bytes);
+  up.alpha = p.alpha; up.beta = p.beta; up.ialpha = p.ialpha; up.ibeta = p.ibeta;
+  up.ws_tile_words = bn_max * kUmmaM;
+  up.scale_p = swap ? p.b_scales : p.a_scales;
+  up.scale_q = swap ? p.a_scales : p.b_scales;
+  up.scale_p_scalar = swap ? p.b_scalar : p.a_scalar;
+  up.scale_q_scalar = swap ? p.a_scalar : p.b_scalar;
+  up.n_on_p = swap ? 1 : 0;
+  up.bias = p.bias;
+  up.out_bf16 = p.out_bf16;
+
+  if (S > 1) {
+    size_t cb = 0;
+    const size_t need = umma_workspace_bytes(p, l, &cb);
+    uint8_t *counters = nullptr, *partials = nullptr;
+    if (l.workspace != nullptr) {
+      if (l.workspace_bytes < need)
+        return fail(MP_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", l.workspace_bytes, need);
+      if (reinterpret_cast<uintptr_t>(l.workspace) & 15)
+        return fail(MP_ERR_WORKSPACE, "workspace must be 16-byte aligned");
+      counters = reinterpret_cast<uint8_t*>(l.workspace);
+      partials = counters + cb;
+      MP_CUDA_TRY(cudaMemsetAsync(counters, 0, cb, stream));   // caller memory: contents unknown
+    } else {
+      if (int rc = get_scratch(stream, cb, need - cb, &counters, &partials)) return rc;
+    }
+    up.ws_counters = reinterpret_cast<unsigned*>(counters);
+    up.ws_partials = reinterpret_cast<uint32_t*>(partials);
+  }
+
+  CUtensorMap tx, ty0, ty1;
+  if (int rc = make_tmap(&tx, p.dtype, X, up.P, p.k, ldx, kUmmaM)) return rc;
+  if (int rc = make_tmap(&ty0, p.dtype, Y, up.Q, p.k, ldy, up.reg[0].bn)) return rc;
+  if (up.num_regions == 2) {
+    if (int rc = make_tmap(&ty1, p.dtype, Y, up.Q, p.k, ldy, up.reg[1].bn)) return rc;
+  } else {
+    ty1 = ty0;
+  }
+
+  const long long units = (long long)up.total_tiles * up.split_k;
+  const int grid = (int)std::min<long long>(units, d->sms);
+  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024;
+  if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
+  if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32>(*d, 1, tx, ty0, ty1, up, grid, smem, stream);
+  return launch_umma_t<KIND_I8, EPI_SCALED>(*d, 2, tx, ty0, ty1, up, grid, smem, stream);
+}
+
+// CUDA-core path (FP32 always; FP16 / INT8 when TMA's alignment rules are not met).
+template <typename TIn, int EPI, int TI, int TJ>
+int launch_simt_t(const SimtParams& sp, cudaStream_t stream) {
+  dim3 grid((sp.m + TI - 1) / TI, (sp.n + TJ - 1) / TJ, sp.split_k);
+  simt_gemm_kernel<TIn, EPI, TI, TJ><<<grid, 256, 0, stream>>>(sp);
+  MP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (sp.split_k > 1) {
+    using TAcc = typename SimtAcc<TIn>::type;
+    const size_t total = (size_t)sp.m * sp.n;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 8);
+    simt_splitk_reduce_kernel<TAcc, EPI><<<blocks, 256, 0, stream>>>(sp);
+    MP_CUDA_TRY(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  return MP_OK;
+}
+
+template <int TI, int TJ>
+int launch_simt_f32(const SimtParams& sp, cudaStream_t s) { return launch_simt_t<float, SEPI_F32, TI, TJ>(sp, s); }
+
+int run_simt(const Problem& p, int ti, int tj, int split_k, void* workspace, size_t workspace_bytes,
+             cudaStream_t stream) {
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+  SimtParams sp{};
+  sp.m = p.m; sp.n = p.n; sp.k = p.k;
+  sp.A = p.A; sp.B = p.B; sp.C = p.C;
+  sp.lda = p.lda; sp.ldb = p.ldb;
+  sp.c_stride_i = p.c_stride_m; sp.c_stride_j = p.c_stride_n;
+  sp.alpha = p.alpha; sp.beta = p.beta; sp.ialpha = p.ialpha; sp.ibeta = p.ibeta;
+  sp.a_scales = p.a_scales; sp.b_scales = p.b_scales; sp.a_scalar = p.a_scalar; sp.b_scalar = p.b_scalar;
+  sp.bias = p.bias; sp.out_bf16 = p.out_bf16;
+  int S = std::max(1, split_k);
+  if (p.k > 0) S = std::min(S, (p.k + 15) / 16); else S = 1;
+  sp.k_per_slice = p.k > 0 ? ((p.k + S - 1) / S + 15) / 16 * 16 : 0;
+  if (p.k > 0) S = (p.k + sp.k_per_slice - 1) / sp.k_per_slice;
+  sp.split_k = S;
+  if (S > 1) {
+    const size_t need = (size_t)S * p.m * p.n * 4;
+    if (workspace != nullptr) {
+      if (workspace_bytes < need)
+        return fail(MP_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+      sp.partials = workspace;
+    } else {
+      uint8_t *c = nullptr, *part = nullptr;
+      if (int rc = get_scratch(stream, 256, need, &c, &part)) return rc;
+      sp.partials = part;
+    }
+  }
+  if (p.dtype == MP_FP32) {
+    if (ti == 32 && tj == 32) return launch_simt_f32<32, 32>(sp, stream);
+    if (ti == 64 && tj == 32) return launch_simt_f32<64, 32>(sp, stream);
+    if (ti == 32 && tj == 64) return launch_simt_f32<32, 64>(sp, stream);
+    if (ti == 128 && tj == 32) return launch_simt_f32<128, 32>(sp, stream);
+    if (ti == 32 && tj == 128) return launch_simt_f32<32, 128>(sp, stream);
+    if (ti == 128 && tj == 64) return launch_simt_f32<128, 64>(sp, stream);
+    if (ti == 64 && tj == 128) return launch_simt_f32<64, 128>(sp, stream);
+    if (ti == 128 && tj == 128) return launch_simt_f32<128, 128>(sp, stream);
+    return launch_simt_f32<64, 64>(sp, stream);
+  }
+  if (p.dtype == MP_FP16) return launch_simt_t<__half, SEPI_F16, 64, 64>(sp, stream);
+  if (p.epi == EPI_I32) return launch_simt_t<int8_t, SEPI_I32, 64, 64>(sp, stream);
+  return launch_simt_t<int8_t, SEPI_SCALED, 64, 64>(sp, stream);
+}
+
+int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {
+  if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
+    return fail(MP_ERR_INVALID_ARG, "Unsupported data type %d", dtype);
+  if (m < 0 || n < 0 || k < 0) return fail(MP_ERR_INVALID_ARG, "negative problem size (%d,%d,%d)", m, n, k);
+  if (m > 0 && n > 0 && (C == nullptr || (k > 0 && (A == nullptr || B == nullptr))))
+    return fail(MP_ERR_INVALID_ARG, "null operand pointer");
+  return MP_OK;
+}
+
+Problem rcc_problem(int dtype, int m, int n, int k, const void* A, const void* B, void* C, float alpha, float beta) {
+  Problem p{};
+  p.dtype = dtype;
+  p.epi = dtype == MP_INT8 ? EPI_I32 : EPI_F16;
+  p.m = m; p.n = n; p.k = k;
+  p.A = A; p.lda = k; p.B = B; p.ldb = k;
+  p.C = C; p.c_stride_m = 1; p.c_stride_n = m;
+  p.alpha = alpha; p.beta = beta;
+  p.ialpha = (int)alpha; p.ibeta = (int)beta;
+  return p;
+}
+
+// Runs one pid (or the dedicated split-K tile when pid < 0) on an RCC problem.
+int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (p.m == 0 || p.n == 0) return MP_OK;
+  const int eff_pid = pid >= 0 ? pid : (p.dtype == MP_FP32 ? 23 : 6);
+  const TileCfg c = tile_cfg(p.dtype, eff_pid);
+  if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, p.dtype);
+  if (p.dtype == MP_FP32) return run_simt(p, c.ti, c.tj, split_k, ws, ws_bytes, stream);
+  if (!tma_compatible(p)) return run_simt(p, 64, 64, split_k, ws, ws_bytes, stream);
+  Launch l;
+  l.orient = c.orient; l.bn = c.bn; l.split_k = std::max(1, split_k);
+  l.workspace = ws; l.workspace_bytes = ws_bytes;
+  return run_umma(p, l, stream);
+}
+
+int run_twin(const Problem& p, int split_n, cudaStream_t stream) {
+  if (p.m == 0 || p.n == 0) return MP_OK;
+  if (!tma_compatible(p)) {
+    // two plain launches with the reference's pointer offsets (core/fp16/fp16_rcc.cu:101-103)
+    Problem p0 = p; p0.n = split_n;
+    Problem p1 = p; p1.n = p.n - split_n;
+    p1.B = reinterpret_cast<const uint8_t*>(p.B) + (size_t)split_n * p.ldb * 2;
+    p1.C = reinterpret_cast<uint8_t*>(p.C) + (size_t)split_n * p.c_stride_n * 2;
+    if (int rc = run_simt(p0, 64, 64, 1, nullptr, 0, stream)) return rc;
+    return run_simt(p1, 64, 64, 1, nullptr, 0, stream);
+  }
+  Launch l;
+  l.orient = 0;
+  l.bn = (split_n % 256 == 0) ? 256 : 128;
+  l.split_n = split_n;
+  const int tail = p.n - split_n;
+  l.bn1 = std::min(64, (tail + 15) / 16 * 16);
+  l.split_k = 1;
+  return run_umma(p, l, stream);
+}
+
+}  // namespace
+
+// ================================================================================================
+// exported entry points
+// ================================================================================================
+extern "C" {
+
+const char* mp_last_error_string(void) { return g_err; }
+const char* mp_version(void) { return "moonpoly-b200 0.1 (sm_100a)"; }
+unsigned long long mp_launch_count(void) { return g_launches.load(); }
+
+int mp_num_sms(void) {
+  DeviceState* d = nullptr;
+  if (device_state(&d) != MP_OK) return 0;
+  return d->sms;
+}
+
+int mp_reload_env(void) {
+  mp::reload_env();
+  return MP_OK;
+}
+
+int mp_select_plan(int dtype, int m, int n, int k, mp_plan* plan) {
+  if (plan == nullptr) return fail(MP_ERR_INVALID_ARG, "plan is null");
+  if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
+    return fail(MP_ERR_INVALID_ARG, "Unsupported data type %d", dtype);
+  if (m <= 0 || n <= 0 || k <= 0) return fail(MP_ERR_INVALID_ARG, "non-positive problem size");
+  *plan = mp::select_plan(dtype, m, n, k);
+  return MP_OK;
+}
+
+int mp_pid_info(int dtype, int pid, int tile[3], int* alignment) {
+  const TileCfg c = tile_cfg(dtype, pid);
+  if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, dtype);
+  if (tile) pid_tile_meta(dtype, pid, tile);
+  if (alignment) *alignment = c.align;
+  return MP_OK;
+}
+
+int mp_cost_ms(int dtype, int pid, int split_k, int m, int n, int k, float* ms) {
+  if (ms == nullptr) return fail(MP_ERR_INVALID_ARG, "ms is null");
+  if (!pid_exists(dtype, pid)) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, dtype);
+  *ms = mp::cost_ms(dtype, pid, split_k, m, n, k);
+  return MP_OK;
+}
+
+int mp_elite_fp16_pids(int* pids, int capacity) { return mp::elite_fp16_pids(pids, capacity); }
+
+int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes) {
+  if (bytes == nullptr) return fail(MP_ERR_INVALID_ARG, "bytes is null");
+  *bytes = 0;
+  if (split_k <= 0) split_k = 2;
+  const int eff_pid = pid >= 0 ? pid : (dtype == MP_FP32 ? 23 : 6);
+  const TileCfg c = tile_cfg(dtype, eff_pid);
+  if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, dtype);
+  if (split_k <= 1 || m <= 0 || n <= 0 || k <= 0) return MP_OK;
+  // the larger of the two paths a call may take (tensor tiles, or CUDA-core tiles for unaligned K)
+  const size_t simt = (size_t)split_k * m * n * 4;
+  if (dtype == MP_FP32) { *bytes = simt; return MP_OK; }
+  Problem p{};
+  p.dtype = dtype; p.m = m; p.n = n; p.k = k;
+  Launch l; l.orient = c.orient; l.bn = c.bn; l.split_k = split_k;
+  *bytes = std::max(simt, umma_workspace_bytes(p, l, nullptr));
+  return MP_OK;
+}
+
+int mp_gemm_rcc_pid(int dtype, int pid, int split_k, int m, int n, int k, const void* A, const void* B, void* C,
+                    float alpha, float beta, void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_rcc_args(dtype, m, n, k, A, B, C)) return rc;
+  if (split_k <= 0) split_k = 2;
+  const TileCfg c = tile_cfg(dtype, pid);
+  if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, dtype);
+  if (k % c.align != 0)
+    return fail(MP_ERR_UNALIGNED_K, " k is not aligned, please check! (k=%d, pid %d needs k %% %d == 0)", k, pid, c.align);
+  const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+  return run_pid(p, pid, split_k, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int mp_twin_gemm_fp16(int m, int n, int k, int split_n, const void* A, const void* B, void* C, float alpha,
+                      float beta, void* stream) {
+  if (int rc = check_rcc_args(MP_FP16, m, n, k, A, B, C)) return rc;
+  if (split_n <= 0) split_n = mp::choose_pattern2_split_n(n);
+  if (split_n <= 0 || split_n >= n || split_n % 128 != 0)
+    return fail(MP_ERR_INVALID_ARG,
+                "Pattern2 FP16 RCC requires 0 < split_n < n and split_n aligned to the OP0 N tile");
+  if (k % 8 != 0) return fail(MP_ERR_INVALID_ARG, "Pattern2 FP16 RCC requires K aligned to 8");
+  const Problem p = rcc_problem(MP_FP16, m, n, k, A, B, C, alpha, beta);
+  return run_twin(p, split_n, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int mp_gemm_rcc(int dtype, int m, int n, int k, const void* A, const void* B, void* C, float alpha, float beta,
+                void* stream) {
+  if (int rc = check_rcc_args(dtype, m, n, k, A, B, C)) return rc;
+  if (m == 0 || n == 0) return MP_OK;
+  const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (k == 0) return run_simt(p, 64, 64, 1, nullptr, 0, s);
+  const mp_plan plan = mp::select_plan(dtype, m, n, k);
+  if (dtype == MP_FP16 && plan.pattern == MP_PATTERN_COMBINE) return run_twin(p, plan.split_n, s);
+  return run_pid(p, plan.pid, plan.split_k, nullptr, 0, s);
+}
+
+int mp_gemm(int dtype, int m, int n, int k, const void* A, int a_col_major, const void* B, int b_col_major, void* C,
+            int c_col_major, float alpha, float beta, void* stream) {
+  if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
+    return fail(MP_ERR_INVALID_ARG, "Unsupported data type");
+  if (!(!a_col_major && b_col_major && c_col_major))
+    return fail(MP_ERR_LAYOUT, "Unsupported layout: only A row-major, B column-major, C column-major is served");
+  return mp_gemm_rcc(dtype, m, n, k, A, B, C, alpha, beta, stream);
+}
+
+int mp_linear(int dtype, int M, int N, int K, const void* X, const void* W, void* Y, void* stream) {
+  return mp_gemm(dtype, N, M, K, W, 0, X, 1, Y, 1, 1.0f, 0.0f, stream);
+}
+
+int mp_scaled_mm_predict(int M, int N, int K) { return mp::scaled_mm_select(M, N, K).id; }
+
+int mp_scaled_mm_config(int config_id, int out[4]) {
+  if (config_id < 0 || config_id >= mp::kScaledConfigCount || out == nullptr)
+    return fail(MP_ERR_INVALID_ARG, "Invalid config id: %d", config_id);
+  mp::scaled_mm_config_meta(config_id, out);
+  return MP_OK;
+}
+
+int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t* B_nk, int ldb, const float* a_scales,
+                    int a_scalar, const float* b_scales, int b_scalar, const void* bias, void* out, int ldc,
+                    int out_dtype, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(MP_ERR_INVALID_ARG, "negative problem size");
+  if (M == 0 || N == 0) return MP_OK;
+  if (!A || !B_nk || !out || !a_scales || !b_scales) return fail(MP_ERR_INVALID_ARG, "null operand pointer");
+  if (out_dtype != 0 && out_dtype != 1) return fail(MP_ERR_INVALID_ARG, "Unsupported output dtype %d", out_dtype);
+  if (lda < K || ldb < K || ldc < N) return fail(MP_ERR_INVALID_ARG, "leading dimension smaller than the row");
+  Problem p{};
+  p.dtype = MP_INT8; p.epi = EPI_SCALED;
+  p.m = M; p.n = N; p.k = K;
+  p.A = A; p.lda = lda; p.B = B_nk; p.ldb = ldb;
+  p.C = out; p.c_stride_m = ldc; p.c_stride_n = 1;
+  p.a_scales = a_scales; p.b_scales = b_scales; p.a_scalar = a_scalar ? 1 : 0; p.b_scalar = b_scalar ? 1 : 0;
+  p.bias = bias; p.out_bf16 = out_dtype;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (K == 0 || !tma_compatible(p)) return run_simt(p, 64, 64, 1, nullptr, 0, s);
+  const mp::ScaledCfg cfg = mp::scaled_mm_select(M, N, K);
+  Launch l;
+  l.orient = cfg.orient; l.bn = cfg.bn; l.split_k = cfg.split_k;
+  return run_umma(p, l, s);
+}
+
+int mp_device_status(void* stream, int* device_code) {
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+  if (stream) MP_CUDA_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  else MP_CUDA_TRY(cudaDeviceSynchronize());
+  int code = 0;
+  MP_CUDA_TRY(cudaMemcpyFromSymbol(&code, mp::g_mp_status, sizeof(int)));
+  if (device_code) *device_code = code;
+  if (code != 0) {
+    const int zero = 0;
+    MP_CUDA_TRY(cudaMemcpyToSymbol(mp::g_mp_status, &zero, sizeof(int)));
+    return fail(MP_ERR_DEVICE, "a kernel recorded device status %d (bounded wait expired)", code);
+  }
+  return MP_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,55 @@
+// Host-side pid tables, cost models and online selectors (no CUDA in this file).
+//
+// The pid numbering, the metadata order [pm, pn, pk] (pm tiles RCC n, pn tiles RCC m), the K
+// alignment contract and the grouping into primary / split-K / elite pids follow the reference
+// (moonpoly/core/fp16/fp16_rcc_cost.cu:15-36, generated/fp16/rcc/candidates.cu:35-65,
+// generated/fp16/rcc/splitk_candidates.inc:2764-2858); the tiles behind each pid are Blackwell
+// tiles: one operand on the 128-row UMMA-M side, the other on a 16..256 wide UMMA-N side.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/moonpoly_abi.h"
+
+namespace mp {
+
+// How a pid maps onto the tcgen05 kernel.
+struct TileCfg {
+  bool valid;
+  // orient 0: RCC m (rows of A) on UMMA-M, RCC n tiled by bn.  orient 1: RCC n (rows of B) on
+  // UMMA-M, RCC m tiled by bn.  For FP32 (CUDA-core tiles) ti x tj is the CTA tile over (m, n).
+  int orient;
+  int bn;
+  int align;          // k must be a multiple of this (the reference's per-pid contract)
+  bool split_capable; // member of the reference's split-K capable set
+  int ti, tj;         // FP32 only
+};
+
+TileCfg tile_cfg(int dtype, int pid);
+bool pid_exists(int dtype, int pid);
+// [pm, pn, pk] as reported by get_gemm_shared_mem_*: pm tiles RCC n, pn tiles RCC m.
+void pid_tile_meta(int dtype, int pid, int out[3]);
+
+// Cost of running `pid` with `split_k` slices on RCC (m, n, k), in milliseconds.  Feature
+// convention of the reference: feature_m = n, feature_n = m (core/fp16/fp16_rcc.cu:451-458).
+float cost_ms(int dtype, int pid, int split_k, int m, int n, int k);
+
+// Online selection (memoised per shape and flag state).
+mp_plan select_plan(int dtype, int m, int n, int k);
+
+// Pattern-2 helpers (core/fp16/fp16_rcc.cu:63-73).
+int choose_pattern2_split_n(int n);
+
+// scaled int8 matmul tile choice: config id 0..5, plus a split-K factor for small problems.
+struct ScaledCfg { int id; int orient; int bn; int split_k; };
+ScaledCfg scaled_mm_select(int M, int N, int K);
+void scaled_mm_config_meta(int id, int out[4]);
+constexpr int kScaledConfigCount = 6;
+
+int elite_fp16_pids(int* pids, int capacity);
+
+void reload_env();
+int num_sms_for_model();
+void set_num_sms_for_model(int sms);
+
+}  // namespace mp

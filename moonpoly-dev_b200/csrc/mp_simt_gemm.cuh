@@ -1,0 +1,170 @@
+// CUDA-core GEMM tiles:  C[i + j*ldc] = alpha * sum_k A[i*lda + k] * B[j*ldb + k] + beta * C
+//
+// Used for (a) the FP32 path -- the reference's FP32 kernels are SIMT FFMA, not TF32
+// (moonpoly/core/fp32/fp32_rcc.cu:193-2208, OpClassSimt), so exact fp32 multiply-add semantics are
+// kept and no tensor core is involved -- and (b) FP16 / INT8 problems whose K or base pointers do
+// not meet the 16-byte alignment TMA needs (the reference keeps pids with alignment 1/2/4 for those,
+// moonpoly/core/fp16/fp16_rcc_cost.cu:32-36).
+//
+// A tile of TI x TJ outputs per 256-thread CTA, K walked in steps of 16 through shared memory,
+// every thread owning a (TI/16) x (TJ/16) register block.  Optional parallel split-K writes raw
+// partials to a workspace (grid.z = slices) and a second kernel sums them in slice order
+// (the GemmSplitKParallel + ReduceSplitK arrangement of moonpoly/core/fp32/fp32_rcc.cu:136-187).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace mp {
+
+enum { SEPI_F16 = 0, SEPI_I32 = 1, SEPI_SCALED = 2, SEPI_F32 = 3 };
+
+struct SimtParams {
+  int m, n, k;
+  const void* A; const void* B; void* C;
+  long long lda, ldb;                  // row pitch (elements) of A[m,k] and B[n,k]
+  long long c_stride_i, c_stride_j;    // element strides of C along i (rows of A) and j (rows of B)
+  float alpha, beta;
+  int ialpha, ibeta;
+  int split_k, k_per_slice;
+  void* partials;                      // [split_k][n][m] accumulators when split_k > 1
+  // scaled int8 epilogue: i = token index (a_scales), j = output channel (b_scales, bias)
+  const float* a_scales; const float* b_scales;
+  int a_scalar, b_scalar;
+  const void* bias;
+  int out_bf16;
+};
+
+template <typename T> struct SimtAcc { using type = float; };
+template <> struct SimtAcc<int8_t> { using type = int; };
+
+template <typename TIn> __device__ __forceinline__ typename SimtAcc<TIn>::type simt_cvt(TIn v);
+template <> __device__ __forceinline__ float simt_cvt<float>(float v) { return v; }
+template <> __device__ __forceinline__ float simt_cvt<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ int simt_cvt<int8_t>(int8_t v) { return (int)v; }
+
+template <int EPI, typename TAcc>
+__device__ __forceinline__ void simt_finish(const SimtParams& p, TAcc acc, int i, int j) {
+  const long long off = (long long)i * p.c_stride_i + (long long)j * p.c_stride_j;
+  if constexpr (EPI == SEPI_F32) {
+    float v = p.alpha * acc;
+    float* o = reinterpret_cast<float*>(p.C) + off;
+    if (p.beta != 0.0f) v += p.beta * (*o);
+    *o = v;
+  } else if constexpr (EPI == SEPI_F16) {
+    float v = p.alpha * acc;
+    __half* o = reinterpret_cast<__half*>(p.C) + off;
+    if (p.beta != 0.0f) v += p.beta * __half2float(*o);
+    *o = __float2half_rn(v);
+  } else if constexpr (EPI == SEPI_I32) {
+    int v = p.ialpha * acc;
+    int* o = reinterpret_cast<int*>(p.C) + off;
+    if (p.ibeta != 0) v += p.ibeta * (*o);
+    *o = v;
+  } else {
+    const float bs = p.b_scales[p.b_scalar ? 0 : j];
+    const float as = p.a_scales[p.a_scalar ? 0 : i];
+    const float t1 = __fmul_rn(as, __fmul_rn(__int2float_rn((int)acc), bs));
+    uint16_t h;
+    if (p.out_bf16) {
+      h = __bfloat16_as_ushort(__float2bfloat16_rn(t1));
+      if (p.bias) {
+        const float s = __bfloat162float(__ushort_as_bfloat16(h)) +
+                        __bfloat162float(__ushort_as_bfloat16(reinterpret_cast<const uint16_t*>(p.bias)[j]));
+        h = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+      }
+    } else {
+      h = __half_as_ushort(__float2half_rn(t1));
+      if (p.bias) {
+        const float s = __half2float(__ushort_as_half(h)) +
+                        __half2float(__ushort_as_half(reinterpret_cast<const uint16_t*>(p.bias)[j]));
+        h = __half_as_ushort(__float2half_rn(s));
+      }
+    }
+    reinterpret_cast<uint16_t*>(p.C)[off] = h;
+  }
+}
+
+template <typename TIn, int EPI, int TI, int TJ>
+__global__ void __launch_bounds__(256)
+simt_gemm_kernel(const SimtParams p) {
+  using TAcc = typename SimtAcc<TIn>::type;
+  constexpr int TK = 16;
+  constexpr int RI = TI / 16, RJ = TJ / 16;
+  __shared__ TAcc As[TK][TI + 1];
+  __shared__ TAcc Bs[TK][TJ + 1];
+
+  const TIn* A = reinterpret_cast<const TIn*>(p.A);
+  const TIn* B = reinterpret_cast<const TIn*>(p.B);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int i0 = blockIdx.x * TI, j0 = blockIdx.y * TJ;
+  const int k_begin = blockIdx.z * p.k_per_slice;
+  const int k_end = min(p.k, k_begin + p.k_per_slice);
+
+  TAcc acc[RI][RJ];
+#pragma unroll
+  for (int a = 0; a < RI; ++a)
+#pragma unroll
+    for (int b = 0; b < RJ; ++b) acc[a][b] = TAcc(0);
+
+  for (int k0 = k_begin; k0 < k_end; k0 += TK) {
+    for (int e = threadIdx.x; e < TI * TK; e += 256) {
+      const int r = e / TK, kk = e % TK;
+      const int gi = i0 + r, gk = k0 + kk;
+      As[kk][r] = (gi < p.m && gk < k_end) ? simt_cvt<TIn>(A[(long long)gi * p.lda + gk]) : TAcc(0);
+    }
+    for (int e = threadIdx.x; e < TJ * TK; e += 256) {
+      const int r = e / TK, kk = e % TK;
+      const int gj = j0 + r, gk = k0 + kk;
+      Bs[kk][r] = (gj < p.n && gk < k_end) ? simt_cvt<TIn>(B[(long long)gj * p.ldb + gk]) : TAcc(0);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      TAcc av[RI], bv[RJ];
+#pragma unroll
+      for (int a = 0; a < RI; ++a) av[a] = As[kk][tx + 16 * a];
+#pragma unroll
+      for (int b = 0; b < RJ; ++b) bv[b] = Bs[kk][ty + 16 * b];
+#pragma unroll
+      for (int a = 0; a < RI; ++a)
+#pragma unroll
+        for (int b = 0; b < RJ; ++b) {
+          if constexpr (sizeof(TIn) == 1) acc[a][b] += av[a] * bv[b];
+          else acc[a][b] = fmaf(av[a], bv[b], acc[a][b]);
+        }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int b = 0; b < RJ; ++b)
+#pragma unroll
+    for (int a = 0; a < RI; ++a) {
+      const int i = i0 + tx + 16 * a, j = j0 + ty + 16 * b;
+      if (i < p.m && j < p.n) {
+        if (p.split_k > 1) {
+          reinterpret_cast<TAcc*>(p.partials)[((size_t)blockIdx.z * p.n + j) * (size_t)p.m + i] = acc[a][b];
+        } else {
+          simt_finish<EPI, TAcc>(p, acc[a][b], i, j);
+        }
+      }
+    }
+}
+
+// Sums split-K partials in slice order s = 0..S-1 and applies the epilogue.
+template <typename TAcc, int EPI>
+__global__ void __launch_bounds__(256)
+simt_splitk_reduce_kernel(const SimtParams p) {
+  const size_t total = (size_t)p.m * p.n;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const int j = (int)(e / p.m), i = (int)(e % p.m);
+    const TAcc* src = reinterpret_cast<const TAcc*>(p.partials) + e;
+    TAcc acc = src[0];
+    for (int s = 1; s < p.split_k; ++s) acc += src[(size_t)s * total];
+    simt_finish<EPI, TAcc>(p, acc, i, j);
+  }
+}
+
+}  // namespace mp

@@ -1,0 +1,396 @@
+// Persistent tcgen05 GEMM for sm_100a:   D[P x Q] = X[P x K] * Y[Q x K]^T
+//
+// Both operands are K-contiguous ("K-major"), which is what the row-column-column contract of the
+// reference gives (A row-major [m,k]; B column-major [k,n], i.e. stored [n,k];
+// moonpoly/core/fp16/fp16_rcc.cu:537-544).  The host decides which operand sits on the 128-wide
+// UMMA-M side (X) and which on the 16..256-wide UMMA-N side (Y), and passes the element strides of
+// the output so that either assignment writes the caller's column-major C (or row-major `out` of
+// the scaled int8 matmul) directly.
+//
+// One launch covers the whole problem ("polymerisation" in one kernel): a device-side schedule walks
+// work units = (output tile, K slice).  Tiles may come from two regions with different UMMA-N
+// (the Pattern-2 twin GEMM of moonpoly/core/fp16/fp16_rcc.cu:75-108), and K may be cut into slices
+// (Pattern-3 / pids 400+); slices park fp32/int32 partials in a workspace and the last slice to
+// arrive sums them in slice order, so the result is bit-identical from run to run and no CTA ever
+// waits for another.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (TMEM lane quadrant = warp % 4).  Accumulators are double-buffered in TMEM
+// so the epilogue of one unit overlaps the main loop of the next.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "mp_ptx.cuh"
+
+namespace mp {
+
+__device__ int g_mp_status = 0;   // 0 = ok; otherwise the first MP_DEV_* code any kernel recorded
+
+constexpr int kUmmaM = 128;            // rows of X per tile
+constexpr int kRowBytes = 128;         // one K block = 128 bytes of K per row (64 fp16 / 128 int8)
+constexpr int kXTileBytes = kUmmaM * kRowBytes;
+constexpr int kMaxBN = 256;
+constexpr int kTmemCols = 512;
+constexpr int kMaxStages = 12;
+constexpr int kUmmaThreads = 192;
+constexpr int kSmemBudget = 232448;    // 227 KB opt-in limit per CTA
+
+enum { KIND_F16 = 0, KIND_I8 = 1 };
+enum { EPI_F16 = 0, EPI_I32 = 1, EPI_SCALED = 2 };
+
+struct Region {
+  int q_begin;    // first Q index of the region
+  int q_end;      // one past the last Q index
+  int bn;         // UMMA-N (multiple of 16, <= 256) used for this region
+  int tiles_q;    // ceil((q_end - q_begin) / bn)
+  int tile_base;  // index of the region's first tile in the launch-wide tile numbering
+};
+
+struct UmmaParams {
+  int P, Q, K;
+  int tiles_p;
+  int num_regions;
+  Region reg[2];
+  int total_tiles;
+  int split_k;        // K slices per tile (>= 1); every slice is non-empty
+  int kb_total;       // ceil(K / elements per K block)
+  int kb_per_slice;
+  int stages;
+  int stage_bytes;    // kXTileBytes + bn_max * kRowBytes
+  int group_p;        // raster: tiles are walked in groups of `group_p` rows of tiles
+  void* out;
+  long long out_stride_p, out_stride_q;   // element strides of `out` along P and Q
+  float alpha, beta;
+  int ialpha, ibeta;
+  uint32_t* ws_partials;   // [total_tiles][split_k][bn_max][128] 32-bit words
+  unsigned* ws_counters;   // [total_tiles][4], zero on entry, left zero on exit
+  int ws_tile_words;       // bn_max * 128
+  // scaled int8 matmul epilogue
+  const float* scale_p; const float* scale_q;   // scales indexed along P / along Q
+  int scale_p_scalar, scale_q_scalar;
+  int n_on_p;              // 1: P is the weight/output-channel index (b_scales, bias live on P)
+  const void* bias;        // in the output type, indexed by output channel; may be null
+  int out_bf16;
+};
+
+struct UnitCoord {
+  int region, tile, tp, tq, kb0, kb1, slice;
+};
+
+__device__ __forceinline__ UnitCoord decode_unit(const UmmaParams& p, int w) {
+  UnitCoord u;
+  u.tile = w / p.split_k;
+  u.slice = w - u.tile * p.split_k;
+  u.region = (p.num_regions == 2 && u.tile >= p.reg[1].tile_base) ? 1 : 0;
+  const Region& r = p.reg[u.region];
+  const int t = u.tile - r.tile_base;
+  const int group_sz = p.group_p * r.tiles_q;
+  const int g = t / group_sz;
+  const int first_p = g * p.group_p;
+  const int rows = min(p.group_p, p.tiles_p - first_p);
+  const int in_g = t - g * group_sz;
+  u.tq = in_g / rows;
+  u.tp = first_p + (in_g - u.tq * rows);
+  u.kb0 = u.slice * p.kb_per_slice;
+  u.kb1 = min(p.kb_total, u.kb0 + p.kb_per_slice);
+  return u;
+}
+
+// ------------------------------------------------------------------------------------ epilogue math
+template <int EPI>
+struct EpiCtx {};
+
+__device__ __forceinline__ uint16_t f32_to_out16(float v, int bf16) {
+  if (bf16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  return __half_as_ushort(__float2half_rn(v));
+}
+
+// Final value for one output element from its 32-bit accumulator word.
+template <int EPI>
+__device__ __forceinline__ void finish_store(const UmmaParams& p, uint32_t accw, int pi, int qi,
+                                             float sp, float sq_or_zero) {
+  const long long off = (long long)pi * p.out_stride_p + (long long)qi * p.out_stride_q;
+  if constexpr (EPI == EPI_F16) {
+    float v = p.alpha * __uint_as_float(accw);
+    __half* o = reinterpret_cast<__half*>(p.out) + off;
+    if (p.beta != 0.0f) v += p.beta * __half2float(*o);
+    *o = __float2half_rn(v);
+  } else if constexpr (EPI == EPI_I32) {
+    int v = p.ialpha * (int)accw;
+    int* o = reinterpret_cast<int*>(p.out) + off;
+    if (p.ibeta != 0) v += p.ibeta * (*o);
+    *o = v;
+  } else {
+    // out = RN16( a_scale[token] * RN32( b_scale[channel] * RN32(acc) ) ) (+ bias in the output type)
+    const float bs = p.n_on_p ? sp : sq_or_zero;
+    const float as = p.n_on_p ? sq_or_zero : sp;
+    const float t0 = __fmul_rn(__int2float_rn((int)accw), bs);
+    const float t1 = __fmul_rn(as, t0);
+    uint16_t h = f32_to_out16(t1, p.out_bf16);
+    if (p.bias != nullptr) {
+      const int ch = p.n_on_p ? pi : qi;
+      const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[ch];
+      if (p.out_bf16) {
+        const float s = __bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(b));
+        h = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+      } else {
+        const float s = __half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(b));
+        h = __half_as_ushort(__float2half_rn(s));
+      }
+    }
+    reinterpret_cast<uint16_t*>(p.out)[off] = h;
+  }
+}
+
+// Store 16 consecutive Q columns [q0, q0+16) of row `pi` from accumulator words r[0..15].
+template <int EPI>
+__device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_t (&r)[16], int pi, int q0,
+                                              int q_end) {
+  if (pi >= p.P) return;
+  const int valid = min(16, q_end - q0);
+  if (valid <= 0) return;
+
+  if constexpr (EPI == EPI_F16) {
+    // fast path: row of D is contiguous in memory and the 32-byte run is aligned
+    if (p.out_stride_q == 1 && valid == 16 && p.beta == 0.0f) {
+      __half* o = reinterpret_cast<__half*>(p.out) + (long long)pi * p.out_stride_p + q0;
+      if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const __half2 h = __floats2half2_rn(p.alpha * __uint_as_float(r[2 * j]),
+                                              p.alpha * __uint_as_float(r[2 * j + 1]));
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        return;
+      }
+    }
+  }
+  if constexpr (EPI == EPI_I32) {
+    if (p.out_stride_q == 1 && valid == 16 && p.ibeta == 0) {
+      int* o = reinterpret_cast<int*>(p.out) + (long long)pi * p.out_stride_p + q0;
+      if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          reinterpret_cast<uint4*>(o)[j] =
+              make_uint4(p.ialpha * (int)r[4 * j], p.ialpha * (int)r[4 * j + 1],
+                         p.ialpha * (int)r[4 * j + 2], p.ialpha * (int)r[4 * j + 3]);
+        return;
+      }
+    }
+  }
+
+  float sp = 0.0f;
+  if constexpr (EPI == EPI_SCALED) sp = p.scale_p[p.scale_p_scalar ? 0 : pi];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (j < valid) {
+      float sq = 0.0f;
+      if constexpr (EPI == EPI_SCALED) sq = p.scale_q[p.scale_q_scalar ? 0 : (q0 + j)];
+      finish_store<EPI>(p, r[j], pi, q0 + j, sp, sq);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ the kernel
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY0,
+                 const __grid_constant__ CUtensorMap tmY1, const UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const int stages = p.stages;
+  const uint32_t bar_base = smem_base + (uint32_t)stages * (uint32_t)p.stage_bytes;
+  // barrier slots (8 bytes each): full[stages] | empty[stages] | tfull[2] | tempty[2] | tmem slot
+  auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(stages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * stages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * stages + 2 + b); };
+  volatile uint32_t* tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int* status = &g_mp_status;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmX);
+    tma_prefetch_desc(&tmY0);
+    if (p.num_regions == 2) tma_prefetch_desc(&tmY1);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_units = p.total_tiles * p.split_k;
+  constexpr int kElemsPerKb = (KIND == KIND_I8) ? 128 : 64;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (one lane)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x) {
+        const UnitCoord u = decode_unit(p, w);
+        const Region& r = p.reg[u.region];
+        const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
+        const uint32_t tx = (uint32_t)(kXTileBytes + r.bn * kRowBytes);
+        const int prow = u.tp * kUmmaM;
+        const int qrow = r.q_begin + u.tq * r.bn;
+        for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
+          const int s = (int)(it % (uint32_t)stages);
+          const uint32_t ph = (it / (uint32_t)stages) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, status, MP_DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
+          mbar_arrive_expect_tx(full_bar(s), tx);
+          tma_load_2d(a_dst, &tmX, full_bar(s), kb * kElemsPerKb, prow);
+          tma_load_2d(a_dst + kXTileBytes, tmY, full_bar(s), kb * kElemsPerKb, qrow);
+        }
+      }
+      if (!ok) {
+        // Give copies that were already issued a bounded chance to land before the CTA retires.
+        const uint32_t lo = it > (uint32_t)stages ? it - (uint32_t)stages : 0u;
+        for (uint32_t i = lo; i < it; ++i) {
+          // no status word: the error already recorded must not cut this drain short
+          mbar_wait(full_bar((int)(i % (uint32_t)stages)), (i / (uint32_t)stages) & 1u, nullptr,
+                    MP_DEV_TIMEOUT_DRAIN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (one lane)
+    if (lane == 0) {
+      uint32_t it = 0, ui = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
+        const UnitCoord u = decode_unit(p, w);
+        const Region& r = p.reg[u.region];
+        const uint32_t buf = ui & 1u;
+        const uint32_t use = ui >> 1;
+        if (!mbar_wait(tempty_bar((int)buf), (use & 1u) ^ 1u, status, MP_DEV_TIMEOUT_MMA_TMEM)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * (uint32_t)kMaxBN;
+        const uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kUmmaM, (uint32_t)r.bn)
+                                                 : umma_idesc(1u, 0u, kUmmaM, (uint32_t)r.bn);
+        for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
+          const int s = (int)(it % (uint32_t)stages);
+          const uint32_t ph = (it / (uint32_t)stages) & 1u;
+          if (!mbar_wait(full_bar(s), ph, status, MP_DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
+          const uint32_t b_addr = a_addr + kXTileBytes;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
+            const uint64_t ad = umma_smem_desc_sw128(a_addr + 32u * kk);
+            const uint64_t bd = umma_smem_desc_sw128(b_addr + 32u * kk);
+            const uint32_t acc = (kb > u.kb0 || kk > 0) ? 1u : 0u;
+            if constexpr (KIND == KIND_I8) umma_i8(d_tmem, ad, bd, idesc, acc);
+            else umma_f16(d_tmem, ad, bd, idesc, acc);
+          }
+          tc_commit(empty_bar(s));      // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar((int)buf));   // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quad = warp & 3;
+    uint32_t ui = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
+      const UnitCoord u = decode_unit(p, w);
+      const Region& r = p.reg[u.region];
+      const uint32_t buf = ui & 1u;
+      const uint32_t use = ui >> 1;
+      if (!mbar_wait(tfull_bar((int)buf), use & 1u, status, MP_DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + buf * (uint32_t)kMaxBN + ((uint32_t)(quad * 32) << 16);
+      const int row_in_tile = quad * 32 + lane;
+      const int pi = u.tp * kUmmaM + row_in_tile;
+      const int q_tile0 = r.q_begin + u.tq * r.bn;
+      const int q_end = min(r.q_end, q_tile0 + r.bn);
+
+      if (p.split_k == 1) {
+        for (int c0 = 0; c0 < r.bn; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(t_addr + (uint32_t)c0, v);
+          tmem_ld_wait();
+          store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar((int)buf));
+      } else {
+        // park this slice's raw accumulators: [tile][slice][column][row]; 32 lanes -> 128 contiguous bytes
+        uint32_t* part = p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words;
+        for (int c0 = 0; c0 < r.bn; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld_x16(t_addr + (uint32_t)c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) __stcg(part + (size_t)(c0 + j) * kUmmaM + row_in_tile, v[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar((int)buf));   // TMEM buffer is free again
+        __threadfence();
+        __syncwarp();
+        unsigned prev = 0;
+        unsigned* ctr = p.ws_counters + (size_t)u.tile * 4 + quad;
+        if (lane == 0) prev = atomicAdd(ctr, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == (unsigned)(p.split_k - 1)) {
+          // last slice to arrive for this quadrant of the tile: reduce in slice order and finish
+          __threadfence();
+          const uint32_t* base = p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words;
+          for (int c0 = 0; c0 < r.bn; c0 += 16) {
+            uint32_t v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __ldcg(base + (size_t)(c0 + j) * kUmmaM + row_in_tile);
+            for (int s = 1; s < p.split_k; ++s) {
+              const uint32_t* ps = base + (size_t)s * p.ws_tile_words;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const uint32_t x = __ldcg(ps + (size_t)(c0 + j) * kUmmaM + row_in_tile);
+                if constexpr (KIND == KIND_I8) v[j] = (uint32_t)((int)v[j] + (int)x);
+                else v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(x)));
+              }
+            }
+            store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end);
+          }
+          __syncwarp();
+          if (lane == 0) *ctr = 0u;   // leave the counter as it was found
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace mp

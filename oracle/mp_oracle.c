@@ -1,0 +1,274 @@
+/*
+ * TEST INFRASTRUCTURE — CPU restatement of the MoonPoly row-column-column GEMM
+ * path.  Only the test-suite, the smoke check and the CPU-baseline leg of the
+ * benchmark may load this file; the product library never links or calls it.
+ *
+ * Pinning status: the reference stores no golden vectors for this path (its
+ * CTest programmes compare against cuBLAS at run time).  What pins this
+ * restatement is (i) the reference's own host check loop, restated below,
+ * (ii) its known-answer "constant check" (all-ones operands => every output
+ * equals K, moonpoly/core/moonpoly_gemm.cu:1641-1736) and (iii) the inputs its
+ * CTest programmes use (integer-valued entries in [-2,2], for which every
+ * correct GEMM is exact: tests/cpp/fp16/test_fp16_row_col_col.cu:62-65).
+ * Rounded floating-point results of the reference's device kernels could not
+ * be produced in a GPU-less container, so for those: parity unpinned.
+ *
+ * Index convention (moonpoly/core/moonpoly_gemm.cu:1610-1617):
+ *   A is row-major [m,k]      -> A[row*k + kk]
+ *   B is column-major [k,n]   -> B[kk + col*k]
+ *   C is column-major [m,n]   -> C[row + col*m]
+ *   acc is fp32, summed in ascending kk.
+ * Epilogue (moonpoly/core/fp16/fp16_rcc.cu:522-523, LinearCombination):
+ *   C = round_to_nearest_out( alpha*acc + beta*C_old ), C_old read only if beta != 0.
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+typedef _Float16 half_t;
+
+static inline float bf16_to_f32(uint16_t v) {
+  uint32_t u = ((uint32_t)v) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+static inline uint16_t f32_to_bf16_rn(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u); /* NaN */
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return (uint16_t)(u >> 16);
+}
+
+/* ---- column-range workers (so the same code serves 1 thread and many) ---- */
+
+typedef struct {
+  int kind; /* 0 f16, 1 f32, 2 i8, 3 scaled_mm, 4 f16 with double accumulation */
+  int m, n, k;
+  const void *A, *B;
+  void *C;
+  float alpha, beta;
+  int ialpha, ibeta;
+  /* scaled_mm extras */
+  const float *a_scales, *b_scales;
+  int a_scalar, b_scalar;
+  const void *bias;
+  int out_bf16;
+  int col0, col1; /* half-open range of output columns (or rows for scaled_mm) */
+} job_t;
+
+/* moonpoly/core/moonpoly_gemm.cu:1613-1617 restated for fp16 operands */
+static void gemm_f16_cols(const job_t *j) {
+  const half_t *A = (const half_t *)j->A, *B = (const half_t *)j->B;
+  half_t *C = (half_t *)j->C;
+  const int m = j->m, k = j->k;
+  for (int col = j->col0; col < j->col1; ++col) {
+    for (int row = 0; row < m; ++row) {
+      float acc = 0.0f;
+      const half_t *a = A + (size_t)row * k, *b = B + (size_t)col * k;
+      for (int kk = 0; kk < k; ++kk) acc += (float)a[kk] * (float)b[kk];
+      float r = j->alpha * acc;
+      size_t idx = (size_t)row + (size_t)col * m;
+      if (j->beta != 0.0f) r += j->beta * (float)C[idx];
+      C[idx] = (half_t)r;
+    }
+  }
+}
+
+/* same, but accumulating in double: the yard-stick for tolerance studies */
+static void gemm_f16_cols_f64(const job_t *j) {
+  const half_t *A = (const half_t *)j->A, *B = (const half_t *)j->B;
+  half_t *C = (half_t *)j->C;
+  const int m = j->m, k = j->k;
+  for (int col = j->col0; col < j->col1; ++col) {
+    for (int row = 0; row < m; ++row) {
+      double acc = 0.0;
+      const half_t *a = A + (size_t)row * k, *b = B + (size_t)col * k;
+      for (int kk = 0; kk < k; ++kk) acc += (double)(float)a[kk] * (double)(float)b[kk];
+      double r = (double)j->alpha * acc;
+      size_t idx = (size_t)row + (size_t)col * m;
+      if (j->beta != 0.0f) r += (double)j->beta * (double)(float)C[idx];
+      C[idx] = (half_t)(float)r;
+    }
+  }
+}
+
+static void gemm_f32_cols(const job_t *j) {
+  const float *A = (const float *)j->A, *B = (const float *)j->B;
+  float *C = (float *)j->C;
+  const int m = j->m, k = j->k;
+  for (int col = j->col0; col < j->col1; ++col) {
+    for (int row = 0; row < m; ++row) {
+      float acc = 0.0f;
+      const float *a = A + (size_t)row * k, *b = B + (size_t)col * k;
+      for (int kk = 0; kk < k; ++kk) acc += a[kk] * b[kk];
+      float r = j->alpha * acc;
+      size_t idx = (size_t)row + (size_t)col * m;
+      if (j->beta != 0.0f) r += j->beta * C[idx];
+      C[idx] = r;
+    }
+  }
+}
+
+/* int8 x int8 -> int32, exact (moonpoly/core/int8/i8_rcc.cu:135-160:
+ * LinearCombination<int32_t,4,int32_t,int32_t>: C = ialpha*acc + ibeta*C). */
+static void gemm_i8_cols(const job_t *j) {
+  const int8_t *A = (const int8_t *)j->A, *B = (const int8_t *)j->B;
+  int32_t *C = (int32_t *)j->C;
+  const int m = j->m, k = j->k;
+  for (int col = j->col0; col < j->col1; ++col) {
+    for (int row = 0; row < m; ++row) {
+      int32_t acc = 0;
+      const int8_t *a = A + (size_t)row * k, *b = B + (size_t)col * k;
+      for (int kk = 0; kk < k; ++kk) acc += (int32_t)a[kk] * (int32_t)b[kk];
+      int32_t r = j->ialpha * acc;
+      size_t idx = (size_t)row + (size_t)col * m;
+      if (j->ibeta != 0) r += j->ibeta * C[idx];
+      C[idx] = r;
+    }
+  }
+}
+
+/* W8A8 scaled matmul, rows [col0,col1) of the row-major output.
+ * A [M,K] int8 row-major, B packed [N,K] int8, out [M,N] row-major.
+ * Epilogue order (moonpoly/core/int8/scaled_mm/scaled_mm_epilogues_mikpoly.hpp:40-119):
+ *   t0 = f32(acc) * b_scale[n]          (f32, RN)
+ *   t1 = a_scale[m] * t0                (f32, RN)
+ *   no bias : out = RN_out(t1)
+ *   bias    : out = RN_out( RN_out(t1) + bias[n] )  -- the sum is formed in the
+ *             output type, i.e. an exactly-rounded half/bfloat16 addition. */
+static void scaled_mm_rows(const job_t *j) {
+  const int8_t *A = (const int8_t *)j->A, *B = (const int8_t *)j->B;
+  const int n = j->n, k = j->k;
+  for (int row = j->col0; row < j->col1; ++row) {
+    const float sa = j->a_scales[j->a_scalar ? 0 : row];
+    for (int col = 0; col < n; ++col) {
+      int32_t acc = 0;
+      const int8_t *a = A + (size_t)row * k, *b = B + (size_t)col * k;
+      for (int kk = 0; kk < k; ++kk) acc += (int32_t)a[kk] * (int32_t)b[kk];
+      const float sb = j->b_scales[j->b_scalar ? 0 : col];
+      float t0 = (float)acc * sb;
+      float t1 = sa * t0;
+      size_t idx = (size_t)row * n + col;
+      if (!j->out_bf16) {
+        half_t h = (half_t)t1;
+        if (j->bias) {
+          /* half + half: exact in f32, then one rounding == correctly rounded half add */
+          float s = (float)h + (float)((const half_t *)j->bias)[col];
+          h = (half_t)s;
+        }
+        ((half_t *)j->C)[idx] = h;
+      } else {
+        uint16_t h = f32_to_bf16_rn(t1);
+        if (j->bias) {
+          float s = bf16_to_f32(h) + bf16_to_f32(((const uint16_t *)j->bias)[col]);
+          h = f32_to_bf16_rn(s);
+        }
+        ((uint16_t *)j->C)[idx] = h;
+      }
+    }
+  }
+}
+
+static void *worker(void *p) {
+  const job_t *j = (const job_t *)p;
+  switch (j->kind) {
+    case 0: gemm_f16_cols(j); break;
+    case 1: gemm_f32_cols(j); break;
+    case 2: gemm_i8_cols(j); break;
+    case 3: scaled_mm_rows(j); break;
+    case 4: gemm_f16_cols_f64(j); break;
+  }
+  return NULL;
+}
+
+static void run_split(job_t base, int extent, int threads) {
+  if (threads < 1) threads = 1;
+  if (threads > extent) threads = extent > 0 ? extent : 1;
+  if (threads == 1) {
+    base.col0 = 0;
+    base.col1 = extent;
+    worker(&base);
+    return;
+  }
+  pthread_t *tid = (pthread_t *)malloc(sizeof(pthread_t) * threads);
+  job_t *jobs = (job_t *)malloc(sizeof(job_t) * threads);
+  for (int t = 0; t < threads; ++t) {
+    jobs[t] = base;
+    jobs[t].col0 = (int)((long long)extent * t / threads);
+    jobs[t].col1 = (int)((long long)extent * (t + 1) / threads);
+    pthread_create(&tid[t], NULL, worker, &jobs[t]);
+  }
+  for (int t = 0; t < threads; ++t) pthread_join(tid[t], NULL);
+  free(tid);
+  free(jobs);
+}
+
+/* ------------------------------ exported API ------------------------------ */
+
+void orc_gemm_f16_rcc(int m, int n, int k, const void *A, const void *B, void *C,
+                      float alpha, float beta, int threads) {
+  job_t j = {0};
+  j.kind = 0; j.m = m; j.n = n; j.k = k; j.A = A; j.B = B; j.C = C;
+  j.alpha = alpha; j.beta = beta;
+  run_split(j, n, threads);
+}
+
+void orc_gemm_f16_rcc_f64acc(int m, int n, int k, const void *A, const void *B, void *C,
+                             float alpha, float beta, int threads) {
+  job_t j = {0};
+  j.kind = 4; j.m = m; j.n = n; j.k = k; j.A = A; j.B = B; j.C = C;
+  j.alpha = alpha; j.beta = beta;
+  run_split(j, n, threads);
+}
+
+void orc_gemm_f32_rcc(int m, int n, int k, const float *A, const float *B, float *C,
+                      float alpha, float beta, int threads) {
+  job_t j = {0};
+  j.kind = 1; j.m = m; j.n = n; j.k = k; j.A = A; j.B = B; j.C = C;
+  j.alpha = alpha; j.beta = beta;
+  run_split(j, n, threads);
+}
+
+void orc_gemm_i8_rcc(int m, int n, int k, const int8_t *A, const int8_t *B, int32_t *C,
+                     int ialpha, int ibeta, int threads) {
+  job_t j = {0};
+  j.kind = 2; j.m = m; j.n = n; j.k = k; j.A = A; j.B = B; j.C = C;
+  j.ialpha = ialpha; j.ibeta = ibeta;
+  run_split(j, n, threads);
+}
+
+void orc_scaled_mm_i8(int m, int n, int k, const int8_t *A, const int8_t *B_nk,
+                      const float *a_scales, int a_scalar, const float *b_scales,
+                      int b_scalar, const void *bias, void *out, int out_bf16,
+                      int threads) {
+  job_t j = {0};
+  j.kind = 3; j.m = m; j.n = n; j.k = k; j.A = A; j.B = B_nk; j.C = out;
+  j.a_scales = a_scales; j.b_scales = b_scales;
+  j.a_scalar = a_scalar; j.b_scalar = b_scalar;
+  j.bias = bias; j.out_bf16 = out_bf16;
+  run_split(j, m, threads);
+}
+
+/* Linear(X[M,K], W[N,K]) -> Y[M,N] row-major, restating the remap of
+ * moonpoly/core/moonpoly_gemm.cu:41-44: RCC m = N, n = M, A = W, B = X. */
+void orc_linear_f16(int M, int N, int K, const void *X, const void *W, void *Y, int threads) {
+  orc_gemm_f16_rcc(N, M, K, W, X, Y, 1.0f, 0.0f, threads);
+}
+
+/* Pattern-2 twin GEMM restated from moonpoly/core/fp16/fp16_rcc.cu:97-104:
+ * region 0 = columns [0,split_n), region 1 = [split_n,n) with B + split_n*k and
+ * C + split_n*m.  Arithmetic per element is that of the plain GEMM. */
+void orc_twin_gemm_f16(int m, int n, int k, int split_n, const void *A, const void *B, void *C,
+                       float alpha, float beta, int threads) {
+  const half_t *Bh = (const half_t *)B;
+  half_t *Ch = (half_t *)C;
+  orc_gemm_f16_rcc(m, split_n, k, A, Bh, Ch, alpha, beta, threads);
+  orc_gemm_f16_rcc(m, n - split_n, k, A, Bh + (size_t)split_n * k, Ch + (size_t)split_n * m,
+                   alpha, beta, threads);
+}

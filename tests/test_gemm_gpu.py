@@ -1,0 +1,313 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (needs a B200)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from moonpoly_b200 import rng
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "rcc_known_answers.npz"))
+DEV = "cuda"
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def close_f16(got, ref, rtol=1e-2, atol=1e-3):
+    """FP16 tolerance of the path: |d| <= atol + rtol*|ref| (relative 1e-2 with an absolute floor)."""
+    got = got.astype(np.float32)
+    ref = ref.astype(np.float32)
+    assert np.isfinite(got).all()
+    bad = np.abs(got - ref) > atol + rtol * np.abs(ref)
+    assert not bad.any(), f"{bad.sum()} of {bad.size} differ; max abs {np.abs(got - ref).max()}"
+
+
+@pytest.fixture(autouse=True)
+def _status(api):
+    yield
+    assert api.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------- FP16
+@pytest.mark.parametrize("name,m,n,k", [("s16x32x64", 16, 32, 64), ("s64x128x128", 64, 128, 128),
+                                         ("s128x256x256", 128, 256, 256)])
+def test_fp16_ctest_shapes_exact(api, name, m, n, k):
+    # shapes and inputs of tests/cpp/fp16/test_fp16_row_col_col.cu: integer-valued, hence exact
+    a = rng.small_ints(1, rng.STREAM_A, (m, k))
+    b = rng.small_ints(1, rng.STREAM_B, (n, k))
+    c = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    assert np.array_equal(c, GOLD[name + "_c"].astype(np.float16))
+
+
+def test_fp16_every_elite_pid_exact(api):
+    m, n, k = 72, 200, 320
+    a = rng.small_ints(11, 0, (m, k))
+    b = rng.small_ints(11, 1, (n, k))
+    ref = (a.astype(np.int64) @ b.astype(np.int64).T).T.astype(np.float16)
+    A, B = dev(a), dev(b)
+    for pid in api.elite_fp16_pids() + [40, 42, 43, 44, 66, 91, 286]:
+        _, align = api.pid_info(api.MP_FP16, pid)
+        assert k % align == 0
+        c = api.gemm_rcc_pid(A, B, pid, 1).cpu().numpy()
+        assert np.array_equal(c, ref), f"pid {pid}"
+
+
+def test_fp16_constant_check(api):
+    # all-ones operands -> every output equals K (moonpoly/core/moonpoly_gemm.cu:1641-1736)
+    a = torch.ones((8, 4096), dtype=torch.float16, device=DEV)
+    b = torch.ones((24, 4096), dtype=torch.float16, device=DEV)
+    for pid, split in ((40, 2), (66, 2), (400, 4), (8, 1)):
+        c = api.gemm_rcc_pid(a, b, pid, split)
+        assert torch.all(c == 4096), (pid, split)
+
+
+@pytest.mark.parametrize("m", [1, 2, 7, 16, 37, 64, 127, 128, 255, 512])
+def test_fp16_sweep_vs_oracle(api, oracle, m):
+    n, k = 1024, 512        # the dynamic-M sweep at a size the CPU oracle finishes in seconds
+    a = rng.normal(1, rng.STREAM_A, (m, k), 0.05)
+    b = rng.normal(1, rng.STREAM_B, (n, k), 0.05)
+    ref = oracle.gemm_f16_rcc(a, b)
+    c = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    close_f16(c, ref)
+
+
+def test_fp16_alpha_beta_and_tails(api, oracle):
+    m, n, k = 133, 77, 264   # odd m and n, k = 4 K-blocks + a tail of 8
+    a = rng.normal(12, 0, (m, k), 0.05)
+    b = rng.normal(12, 1, (n, k), 0.05)
+    c0 = rng.normal(12, 2, (n, m), 1.0)
+    ref = oracle.gemm_f16_rcc(a, b, 0.5, 2.0, c0)
+    for pid in (1, 8, 23, 7):
+        c = api.gemm_rcc_pid(dev(a), dev(b), pid, 1, c_nm=dev(c0), alpha=0.5, beta=2.0).cpu().numpy()
+        close_f16(c, ref)
+
+
+def test_fp16_unaligned_k_uses_cuda_core_tiles(api, oracle):
+    m, n, k = 19, 45, 67     # k*2 bytes is not a multiple of 16: TMA cannot describe the rows
+    a = rng.normal(13, 0, (m, k), 0.05)
+    b = rng.normal(13, 1, (n, k), 0.05)
+    ref = oracle.gemm_f16_rcc(a, b)
+    c = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    close_f16(c, ref)
+    with pytest.raises(api.MoonpolyError) as e:
+        api.gemm_rcc_pid(dev(a), dev(b), 0, 1)       # pid 0 needs k % 8 == 0
+    assert e.value.code == 3
+
+
+@pytest.mark.parametrize("split_k", [1, 2, 4, 8])
+@pytest.mark.parametrize("pid", [400, 407, 413, 425, 439])
+def test_fp16_splitk_pids(api, oracle, pid, split_k):
+    # Linear(M,N,K) through pids 400+ with run-time split-K (tests/python/test_fp16_splitk_runtime.py)
+    M, N, K = 8, 1024, 1024
+    x = rng.normal(2, rng.STREAM_A, (M, K), 0.1)
+    w = rng.normal(2, rng.STREAM_B, (N, K), 0.1)
+    ref = oracle.linear_f16(x, w)
+    y = api.linear_cpp_forced_pid(dev(x), dev(w), pid, split_k).cpu().numpy()
+    close_f16(y, ref, rtol=1e-2, atol=2e-3)
+
+
+def test_fp16_splitk_is_deterministic_and_exact(api):
+    m, n, k = 200, 136, 2048
+    a = rng.small_ints(14, 0, (m, k))
+    b = rng.small_ints(14, 1, (n, k), lo=-1, hi=1)
+    ref = (a.astype(np.int64) @ b.astype(np.int64).T).T
+    assert np.abs(ref).max() < 2048
+    A, B = dev(a), dev(b)
+    first = None
+    for rep in range(3):
+        c = api.gemm_rcc_pid(A, B, 415, 8).cpu().numpy()
+        assert np.array_equal(c, ref.astype(np.float16))
+        first = c if first is None else first
+        assert np.array_equal(first, c)
+
+
+def test_fp16_caller_workspace(api, oracle):
+    M, N, K = 16, 512, 4096
+    x = rng.normal(15, 0, (M, K), 0.05)
+    w = rng.normal(15, 1, (N, K), 0.05)
+    ref = oracle.linear_f16(x, w)
+    X, W = dev(x), dev(w)
+    need = api.fp16_workspace_size(X, W, 400, 4)
+    assert need > 0
+    ws = torch.full((need,), 0xAB, dtype=torch.uint8, device=DEV)     # garbage on purpose
+    out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+    api.linear_fp16_pid_ws_out(X, W, out, 400, ws, 4)
+    close_f16(out.cpu().numpy(), ref)
+    api.linear_fp16_pid_ws_out(X, W, out, 400, ws, 4)                 # counters were left clean
+    close_f16(out.cpu().numpy(), ref)
+    with pytest.raises(ValueError):
+        api.linear_fp16_pid_ws_out(X, W, out, 400, ws[: need // 2], 4)
+
+
+def test_fp16_twin_gemm(api):
+    # tests/cpp/fp16/test_fp16_pattern2_twin_gemm.cu: m=128, n=384, k=128, split_n=256
+    m, n, k = 128, 384, 128
+    a = rng.small_ints(1, rng.STREAM_A, (m, k))
+    b = rng.small_ints(1, rng.STREAM_B, (n, k))
+    c = api.twin_gemm_fp16(dev(a), dev(b), 256).cpu().numpy()
+    assert np.array_equal(c, GOLD["twin128x384x128_c"].astype(np.float16))
+    c = api.twin_gemm_fp16(dev(a), dev(b), 0).cpu().numpy()       # auto split: 3/4 of n, 128-aligned
+    assert np.array_equal(c, GOLD["twin128x384x128_c"].astype(np.float16))
+    for bad in (384, 100, 512):
+        with pytest.raises(ValueError):
+            api.twin_gemm_fp16(dev(a), dev(b), bad)
+
+
+def test_fp16_twin_ragged_tail(api, oracle):
+    m, n, k = 200, 530, 192
+    a = rng.normal(16, 0, (m, k), 0.05)
+    b = rng.normal(16, 1, (n, k), 0.05)
+    ref = oracle.gemm_f16_rcc(a, b)
+    c = api.twin_gemm_fp16(dev(a), dev(b), 512).cpu().numpy()
+    close_f16(c, ref)
+
+
+def test_fp16_linear_matches_rcc_remap(api, oracle):
+    M, N, K = 5, 384, 256
+    x = rng.normal(17, 0, (M, K), 0.05)
+    w = rng.normal(17, 1, (N, K), 0.05)
+    y = api.linear(dev(x), dev(w)).cpu().numpy()
+    close_f16(y, oracle.linear_f16(x, w))
+
+
+def test_layout_and_dtype_errors(api):
+    a = torch.zeros((4, 8), dtype=torch.float16, device=DEV)
+    with pytest.raises(ValueError):
+        api.linear(a.to(torch.bfloat16), a.to(torch.bfloat16))
+    L = api.lib()
+    rc = L.mp_gemm(0, 4, 4, 8, a.data_ptr(), 1, a.data_ptr(), 1, a.data_ptr(), 1, 1.0, 0.0, None)
+    assert rc == 2
+    rc = L.mp_gemm(7, 4, 4, 8, a.data_ptr(), 0, a.data_ptr(), 1, a.data_ptr(), 1, 1.0, 0.0, None)
+    assert rc == 1
+    with pytest.raises(api.MoonpolyError) as e:
+        api.gemm_rcc_pid(a, a, 77, 1)
+    assert e.value.code == 4
+
+
+def test_empty_problems(api):
+    a = torch.zeros((0, 64), dtype=torch.float16, device=DEV)
+    b = torch.zeros((8, 64), dtype=torch.float16, device=DEV)
+    assert api.gemm_rcc(a, b).shape == (8, 0)
+    # k == 0: C = beta * C
+    a0 = torch.zeros((4, 0), dtype=torch.float16, device=DEV)
+    b0 = torch.zeros((8, 0), dtype=torch.float16, device=DEV)
+    c = torch.ones((8, 4), dtype=torch.float16, device=DEV)
+    api.gemm_rcc(a0, b0, c_nm=c, alpha=1.0, beta=3.0)
+    assert torch.all(c == 3)
+
+
+# ---------------------------------------------------------------------------------------- FP32
+def test_fp32_config_shape(api, oracle):
+    # FP32 RCC 37 x 1024 x 1024, uniform[-1,1], seed 0; tolerance 1e-4 relative
+    m, n, k = 37, 1024, 1024
+    a = rng.uniform(0, rng.STREAM_A, (m, k), -1.0, 1.0)
+    b = rng.uniform(0, rng.STREAM_B, (n, k), -1.0, 1.0)
+    ref = oracle.gemm_f32_rcc(a, b)
+    c = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    assert np.all(np.abs(c - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref)))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 32, 64), (64, 128, 128), (33, 65, 1100)])
+def test_fp32_ctest_shapes_and_forced_splitk(api, m, n, k, monkeypatch):
+    # tests/cpp/fp32/test_fp32_row_col_col.cu: plain, then with MOONPOLY_FP32_PATTERN3_FORCE_SPLITK=2
+    a = rng.small_ints(1, rng.STREAM_A, (m, k), dtype=np.float32)
+    b = rng.small_ints(1, rng.STREAM_B, (n, k), dtype=np.float32)
+    ref = (a.astype(np.int64) @ b.astype(np.int64).T).T.astype(np.float32)
+    assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
+    monkeypatch.setenv("MOONPOLY_FP32_PATTERN3_FORCE_SPLITK", "2")
+    plan = api.select_plan(api.MP_FP32, m, n, k)
+    assert plan.pattern == 3 and plan.split_k == 2 and plan.pid == -1
+    assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
+    monkeypatch.delenv("MOONPOLY_FP32_PATTERN3_FORCE_SPLITK")
+    assert api.select_plan(api.MP_FP32, m, n, k).pattern == 1
+
+
+def test_fp32_every_pid(api, oracle):
+    m, n, k = 70, 150, 96
+    a = rng.uniform(18, 0, (m, k), -1.0, 1.0)
+    b = rng.uniform(18, 1, (n, k), -1.0, 1.0)
+    ref = oracle.gemm_f32_rcc(a, b)
+    for pid in range(40):
+        c = api.gemm_rcc_pid(dev(a), dev(b), pid, 1).cpu().numpy()
+        assert np.all(np.abs(c - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref))), pid
+
+
+# ---------------------------------------------------------------------------------------- INT8
+@pytest.mark.parametrize("m,n,k", [(16, 32, 64), (64, 128, 128), (128, 256, 256), (37, 200, 4096), (1, 6144, 512)])
+def test_int8_bit_exact(api, oracle, m, n, k, monkeypatch):
+    a = rng.int8_uniform(3, rng.STREAM_A, (m, k))
+    b = rng.int8_uniform(3, rng.STREAM_B, (n, k))
+    ref = oracle.gemm_i8_rcc(a, b)
+    assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
+    # tests/cpp/int8/test_int8_row_col_col.cu: forced split-K 2 must stay bit-exact
+    monkeypatch.setenv("MOONPOLY_INT8_PATTERN3_FORCE_SPLITK", "2")
+    assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
+
+
+def test_int8_every_pid_and_alpha_beta(api, oracle):
+    m, n, k = 150, 70, 512
+    a = rng.int8_uniform(19, 0, (m, k))
+    b = rng.int8_uniform(19, 1, (n, k))
+    c0 = rng.int8_uniform(19, 2, (n, m)).astype(np.int32) * 37
+    ref = oracle.gemm_i8_rcc(a, b)
+    ref_ab = oracle.gemm_i8_rcc(a, b, 2, -3, c0)
+    for pid in range(46):
+        assert np.array_equal(api.gemm_rcc_pid(dev(a), dev(b), pid, 1).cpu().numpy(), ref), pid
+    got = api.gemm_rcc_pid(dev(a), dev(b), 6, 4, c_nm=dev(c0), alpha=2.0, beta=-3.0).cpu().numpy()
+    assert np.array_equal(got, ref_ab)
+
+
+def test_int8_unaligned_k(api, oracle):
+    m, n, k = 9, 33, 100       # k % 16 != 0 -> CUDA-core tiles
+    a = rng.int8_uniform(20, 0, (m, k))
+    b = rng.int8_uniform(20, 1, (n, k))
+    assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), oracle.gemm_i8_rcc(a, b))
+
+
+def test_scaled_mm_known_answer(api):
+    m, n, k = 24, 40, 64
+    a = rng.int8_uniform(3, rng.STREAM_A, (m, k))
+    b = rng.int8_uniform(3, rng.STREAM_B, (n, k))
+    out = api.scaled_int8_mm(dev(a), dev(b).t(), dev(GOLD["scaled_24x40x64_sa"]), dev(GOLD["scaled_24x40x64_sb"]))
+    assert np.array_equal(out.cpu().numpy(), GOLD["scaled_24x40x64_out"])
+
+
+@pytest.mark.parametrize("M", [1, 8, 47, 160, 700])
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("mode", ["tensor", "token_channel", "tensor_channel", "token_tensor"])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_scaled_mm_bit_exact_vs_oracle(api, oracle, M, bf16, mode, with_bias):
+    # the scale modes and dtypes of tests/python/test_int8_scaled_mm_correctness.py
+    N, K = 384, 512
+    a = rng.int8_uniform(3, rng.STREAM_A, (M, K))
+    b = rng.int8_uniform(3, rng.STREAM_B, (N, K))
+    sa = rng.uniform(3, rng.STREAM_A_SCALE, (1 if mode in ("tensor", "tensor_channel") else M,), 0.001, 0.02)
+    sb = rng.uniform(3, rng.STREAM_B_SCALE, (1 if mode in ("tensor", "token_tensor") else N,), 0.001, 0.02)
+    bias = None
+    tb = None
+    if with_bias:
+        bf = rng.uniform(3, rng.STREAM_BIAS, (N,), -1.0, 1.0)
+        if bf16:
+            bias = oracle.bf16_bits_from_f32(bf)
+            tb = dev(bias.view(np.int16)).view(torch.bfloat16)
+        else:
+            bias = bf.astype(np.float16)
+            tb = dev(bias)
+    ref = oracle.scaled_mm_i8(a, b, sa, sb, bias, bf16)
+    out = api.scaled_int8_mm(dev(a), dev(b).t(), dev(sa), dev(sb), tb,
+                             torch.bfloat16 if bf16 else torch.float16)
+    got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, ref.view(np.uint16))
+
+
+def test_scaled_mm_unaligned_k(api, oracle):
+    M, N, K = 5, 48, 40        # K % 16 != 0: the reference falls back to a float matmul here
+    a = rng.int8_uniform(21, 0, (M, K))
+    b = rng.int8_uniform(21, 1, (N, K))
+    sa = rng.uniform(21, 2, (M,), 0.001, 0.02)
+    sb = rng.uniform(21, 3, (N,), 0.001, 0.02)
+    out = api.scaled_int8_mm(dev(a), dev(b).t(), dev(sa), dev(sb)).cpu().numpy()
+    assert np.array_equal(out, oracle.scaled_mm_i8(a, b, sa, sb))
