@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Headline benchmark: FP16 row-column-column GEMM, dynamic-M sweep, N = K = 4096.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one pass over the sweep M in {1,2,4,8,16,32,64,127,128,255,512,1023,2048,4096}: every
+shape is launched `reps(M)` times back to back through the C ABI's online-selector entry
+(mp_gemm), rotating through 8 resident copies of the 32 MiB weight matrix (256 MiB > L2) so the
+weight stream comes from HBM.  Per-shape device time comes from CUDA events on the launching
+stream; `value` is the geometric mean over the sweep of 2*M*N*K / time, in TFLOP/s.  With N > 1
+GPUs (torchrun, one rank per GPU) every rank owns its own 4096-column shard of a 4096*N wide
+weight (column-parallel, no data-path collective: weak scaling); per-shape time is the max over
+ranks and `value` counts the FLOPs of all ranks.
+
+`e2e` is the same metric with the activations A copied from pinned host memory and C copied back
+to pinned host memory inside the timed region of every GEMM (the weight stays resident, as a
+model parameter does).  `roofline` describes the dominant kernel (the tcgen05 GEMM at M = 4096)
+and `per_shape` the fraction of max(FLOPs/peak, bytes/HBM) each shape reaches.  `cpu_baseline` is
+the CPU oracle (the reference's host check loop restated, all host threads) on a bounded sample.
+`--impl reference` times that same CPU implementation alone.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "moonpoly-dev_b200", "py")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+
+SWEEP_M = [1, 2, 4, 8, 16, 32, 64, 127, 128, 255, 512, 1023, 2048, 4096]
+N_DIM = K_DIM = 4096
+WEIGHT_COPIES = 8
+METRIC = "FP16/INT8 dynamic-shape GEMM TFLOP/s (geomean over M sweep), % of roofline"
+WORKLOAD = "fp16_rcc_dynamic_m_sweep_n4096_k4096"
+
+
+def reps_for(m: int) -> int:
+    return 16 if m <= 255 else (8 if m <= 1023 else 4)
+
+
+def flops(m: int) -> float:
+    return 2.0 * m * N_DIM * K_DIM
+
+
+def algo_bytes(m: int) -> float:
+    return 2.0 * (m * K_DIM + K_DIM * N_DIM + m * N_DIM)
+
+
+def geomean(xs):
+    return math.exp(sum(math.log(x) for x in xs) / len(xs))
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (the only place outside tests/ and smoke() that touches oracle/)
+# ------------------------------------------------------------------------------------------------
+def cpu_inputs(m_list, seed=1):
+    from moonpoly_b200 import rng
+    b = rng.normal(seed, rng.STREAM_B, (N_DIM, K_DIM), 0.05)
+    a = {m: rng.normal(seed, rng.STREAM_A, (m, K_DIM), 0.05) for m in m_list}
+    return a, b
+
+
+def cpu_time_shapes(m_list, budget_s, a=None, b=None):
+    """Times the oracle on the sweep's shapes in ascending M until `budget_s` is spent."""
+    from oracle import oracle
+    oracle.build()
+    cores = oracle.host_threads()
+    if a is None:
+        a, b = cpu_inputs(m_list)
+    out, spent = [], 0.0
+    for m in m_list:
+        t0 = time.perf_counter()
+        oracle.gemm_f16_rcc(a[m], b, threads=cores)
+        dt = time.perf_counter() - t0
+        out.append((m, dt))
+        spent += dt
+        if spent > budget_s:
+            break
+    return out, cores
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU implementation of the path (its host check loop, restated in
+    oracle/mp_oracle.c) on all host threads; rank 0 only."""
+    if rank != 0:
+        return
+    sample = [m for m in SWEEP_M if m <= 16]
+    a, b = cpu_inputs(sample)
+    for _ in range(args.warmup):
+        cpu_time_shapes(sample[:2], 1e9, a, b)
+    per_shape = {m: 0.0 for m in sample}
+    t0 = time.perf_counter()
+    cores = 1
+    for _ in range(args.steps):
+        res, cores = cpu_time_shapes(sample, 1e9, a, b)
+        for m, dt in res:
+            per_shape[m] += dt
+    total = time.perf_counter() - t0
+    value = geomean([flops(m) / (per_shape[m] / args.steps) / 1e12 for m in sample])
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": "M in {1,2,4,8,16} of the sweep per step"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "sweep shapes M in {1,2,4,8,16}, N=K=4096, every step"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in text.strip().splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_ours(args, rank, world, local_rank):
+    import ctypes
+
+    import torch
+    from moonpoly_b200 import api, rng
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    L = api.lib()
+    stream = torch.cuda.current_stream()
+    st = ctypes.c_void_p(stream.cuda_stream)
+
+    # operands: rank r owns columns [r*4096, (r+1)*4096) of the 4096*world wide weight
+    w0 = torch.from_numpy(rng.normal(1 + 1000 * rank, rng.STREAM_B, (N_DIM, K_DIM), 0.05)).to(dev)
+    weights = [w0] + [torch.roll(w0, shifts=17 * i, dims=0).contiguous() for i in range(1, WEIGHT_COPIES)]
+    a_host = {m: torch.from_numpy(rng.normal(1, rng.STREAM_A, (m, K_DIM), 0.05)).pin_memory() for m in SWEEP_M}
+    a_dev = {m: [a_host[m].to(dev), a_host[m].to(dev).clone()] for m in SWEEP_M}
+    c_dev = {m: torch.empty((N_DIM, m), dtype=torch.float16, device=dev) for m in SWEEP_M}
+    c_host = {m: torch.empty((N_DIM, m), dtype=torch.float16).pin_memory() for m in SWEEP_M}
+    a_stage = {m: torch.empty((m, K_DIM), dtype=torch.float16, device=dev) for m in SWEEP_M}
+
+    def gemm(m, a, w, c):
+        rc = L.mp_gemm(api.MP_FP16, m, N_DIM, K_DIM, ctypes.c_void_p(a.data_ptr()), 0, ctypes.c_void_p(w.data_ptr()), 1,
+                       ctypes.c_void_p(c.data_ptr()), 1, 1.0, 0.0, st)
+        if rc != 0:
+            raise RuntimeError(L.mp_last_error_string().decode())
+
+    counter = [0]
+
+    def sweep_device(events):
+        for m in SWEEP_M:
+            r = reps_for(m)
+            if events is not None:
+                events[m][0].record(stream)
+            for i in range(r):
+                counter[0] += 1
+                gemm(m, a_dev[m][i & 1], weights[counter[0] % WEIGHT_COPIES], c_dev[m])
+            if events is not None:
+                events[m][1].record(stream)
+
+    def sweep_e2e(events):
+        for m in SWEEP_M:
+            r = max(2, reps_for(m) // 4)
+            if events is not None:
+                events[m][0].record(stream)
+            for i in range(r):
+                counter[0] += 1
+                a_stage[m].copy_(a_host[m], non_blocking=True)
+                gemm(m, a_stage[m], weights[counter[0] % WEIGHT_COPIES], c_dev[m])
+                c_host[m].copy_(c_dev[m], non_blocking=True)
+            if events is not None:
+                events[m][1].record(stream)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(sweep_fn, steps):
+        evs = [{m: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for m in SWEEP_M}
+               for _ in range(steps)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        launches0 = api.launch_count()
+        e0.record(stream)
+        for s in range(steps):
+            sweep_fn(evs[s])
+        e1.record(stream)
+        barrier()
+        total_ms = e0.elapsed_time(e1)
+        per = {m: sum(ev[m][0].elapsed_time(ev[m][1]) for ev in evs) / steps for m in SWEEP_M}
+        return total_ms, per, api.launch_count() - launches0
+
+    for _ in range(max(3, args.warmup)):
+        sweep_device(None)
+    sweep_e2e(None)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms, per_ms, launches = timed(sweep_device, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_total_ms, e2e_per_ms, _ = timed(sweep_e2e, max(1, args.steps // 2))
+    code = api.device_status()
+    assert code == 0
+
+    def reduce_max(d):
+        t = torch.tensor([d[m] for m in SWEEP_M], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return {m: float(v) for m, v in zip(SWEEP_M, t.tolist())}
+
+    tot = torch.tensor([total_ms, e2e_total_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
+    total_ms, e2e_total_ms = tot.tolist()
+    per_ms = reduce_max(per_ms)
+    e2e_per_ms = reduce_max(e2e_per_ms)
+
+    if rank == 0:
+        peaks = load_peaks()
+        per_launch_ms = {m: per_ms[m] / reps_for(m) for m in SWEEP_M}
+        e2e_launch_ms = {m: e2e_per_ms[m] / max(2, reps_for(m) // 4) for m in SWEEP_M}
+        tfl = {m: world * flops(m) / (per_launch_ms[m] * 1e-3) / 1e12 for m in SWEEP_M}
+        e2e_tfl = {m: world * flops(m) / (e2e_launch_ms[m] * 1e-3) / 1e12 for m in SWEEP_M}
+        per_shape = []
+        for m in SWEEP_M:
+            t_c = flops(m) / (peaks["tflops"] * 1e12)
+            t_m = algo_bytes(m) / (peaks["hbm_gbs"] * 1e9)
+            bound = "tensor" if t_c >= t_m else "hbm"
+            per_shape.append({"M": m, "us": round(per_launch_ms[m] * 1e3, 3), "tflops": round(tfl[m] / world, 3),
+                              "gbs": round(algo_bytes(m) / (per_launch_ms[m] * 1e-3) / 1e9, 1), "bound": bound,
+                              "frac": round(max(t_c, t_m) / (per_launch_ms[m] * 1e-3), 4),
+                              "plan": repr(api.select_plan(api.MP_FP16, m, N_DIM, K_DIM))})
+        dom = SWEEP_M[-1]
+        achieved = flops(dom) / (per_launch_ms[dom] * 1e-3) / 1e12
+        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        traffic = None
+        if os.path.exists(traffic_path):
+            with open(traffic_path) as fh:
+                traffic = json.load(fh).get("umma_gemm_f16_m4096_dram_bytes_per_launch")
+        # CPU baseline: the oracle on this box's host cores, bounded sample
+        cpu_res, cores = cpu_time_shapes([m for m in SWEEP_M if m <= 128], args.cpu_budget)
+        cpu_val = geomean([flops(m) / dt / 1e12 for m, dt in cpu_res])
+        h2d = sum(max(2, reps_for(m) // 4) * m * K_DIM * 2 for m in SWEEP_M)
+        d2h = sum(max(2, reps_for(m) // 4) * m * N_DIM * 2 for m in SWEEP_M)
+        line = {
+            "metric": METRIC, "value": geomean([tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sweep_m": SWEEP_M, "n": N_DIM, "k": K_DIM,
+                       "reps_per_shape": {str(m): reps_for(m) for m in SWEEP_M},
+                       "l2": f"inputs larger than L2: {WEIGHT_COPIES} rotating copies of the 32 MiB weight (256 MiB)",
+                       "entry": "mp_gemm (online selector)", "parallelism": f"column-parallel x{world}, no collective",
+                       "peaks": peaks},
+            "roofline_geomean_frac": geomean([p["frac"] for p in per_shape]),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops"], "traffic": traffic,
+                         "kernel": "umma_gemm_kernel<f16> at M=4096", "peak_source": peaks["source"] + " burst"},
+            "per_shape": per_shape,
+            "cpu_baseline": {"value": cpu_val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                             "sample": "sweep shapes M in {%s}, N=K=4096, one run each" %
+                                       ",".join(str(m) for m, _ in cpu_res)},
+            "e2e": {"value": geomean([e2e_tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "note": "A copied from pinned host and C copied back per GEMM; weight resident"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-budget", type=float, default=15.0, dest="cpu_budget")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -320,7 +320,14 @@ def linear_cpp_forced_pid(x: torch.Tensor, w: torch.Tensor, pid: int, split_k: i
     if (x.dtype != torch.float16 or w.dtype != torch.float16 or x.dim() != 2 or w.dim() != 2
             or not x.is_contiguous() or not w.is_contiguous()):
         return linear(x, w)
-    return linear_fp16_pid_ws(x, w, pid, None, split_k)
+    S = 2 if split_k <= 0 else split_k
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    # no caller workspace here: the library uses its own per-stream scratch
+    _check(lib().mp_gemm_rcc_pid(MP_FP16, pid, S, N, M, K, _ptr(w), _ptr(x), _ptr(out), 1.0, 0.0,
+                                 ctypes.c_void_p(0), 0, _stream(x)))
+    return out
 
 
 def scaled_int8_mm(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tensor, b_scales: torch.Tensor,
