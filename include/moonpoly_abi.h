@@ -76,6 +76,15 @@ int mp_gemm_rcc_pid(int dtype, int pid, int split_k, int m, int n, int k, const 
                     const void* B, void* C, float alpha, float beta, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* Tuning entry (no counterpart in the reference, whose tiles are fixed at compile time by its
+ * CUTLASS template instantiations): run the FP16 / INT8 tensor-core kernel on an RCC problem with
+ * an explicit tile instead of a pid.  orient 0 puts the rows of A on the 128-row UMMA-M side and
+ * tiles n by bn; orient 1 puts the rows of B there and tiles m by bn.  bn: multiple of 16 in
+ * [16,256].  kc: K blocks (of 128 bytes) per pipeline stage, 1, 2 or 4; 0 lets the library choose.
+ * The refit tool (per-tile k_iter sweeps) and the profiling driver use it. */
+int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k,
+                     const void* A, const void* B, void* C, float alpha, float beta, void* stream);
+
 /* get_gemm_workspace_size_fp16_row_col_col (core/fp16/fp16_rcc.cu:3306-3316), extended to every
  * pid and dtype: bytes of scratch mp_gemm_rcc_pid needs for this problem (0 when split_k == 1). */
 int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes);

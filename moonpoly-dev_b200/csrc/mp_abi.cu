@@ -148,20 +148,26 @@ struct Problem {
 
 struct Launch {
   int orient = 0, bn = 128, split_k = 1;
+  int kc = 0;                 // K blocks per stage; 0 = choose
   int split_n = 0, bn1 = 0;   // twin: second region [split_n, n) with its own UMMA-N
   void* workspace = nullptr; size_t workspace_bytes = 0;
 };
 
 int elem_bytes(int dtype) { return dtype == MP_FP16 ? 2 : dtype == MP_INT8 ? 1 : 4; }
 
-int make_tmap(CUtensorMap* tm, int dtype, const void* ptr, long long rows, long long k, long long ld, int box_rows) {
+// kc == 0: 2-D map [rows][k] with a (128 bytes x box_rows) box.  kc > 0 (k a multiple of one
+// 128-byte K block): 3-D map [k/kb][rows][kb] with a (128 bytes x box_rows x kc) box.
+int make_tmap(CUtensorMap* tm, int dtype, const void* ptr, long long rows, long long k, long long ld, int box_rows,
+              int kc) {
   const int eb = elem_bytes(dtype);
-  cuuint64_t gdim[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {(cuuint64_t)(ld * eb)};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / eb), (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
+  const cuuint64_t kb = (cuuint64_t)(128 / eb);
+  cuuint64_t gdim[3] = {(cuuint64_t)k, (cuuint64_t)rows, 1};
+  cuuint64_t gstride[2] = {(cuuint64_t)(ld * eb), 128};
+  cuuint32_t box[3] = {(cuuint32_t)kb, (cuuint32_t)box_rows, (cuuint32_t)kc};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (kc > 0) { gdim[0] = kb; gdim[2] = (cuuint64_t)k / kb; }
   const CUtensorMapDataType dt = dtype == MP_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  const CUresult r = g_encode(tm, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+  const CUresult r = g_encode(tm, dt, kc > 0 ? 3 : 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -242,13 +248,21 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   }
   const int kb_elems = p.dtype == MP_INT8 ? 128 : 64;
   up.kb_total = (p.k + kb_elems - 1) / kb_elems;
+  // K blocks per stage: wide boxes move far more bytes per TMA instruction; keep >= 3 stages
+  const int kb_bytes = kXTileBytes + bn_max * kRowBytes;
+  const int smem_for_stages = kSmemBudget - 1024 - 256;
+  int kc = l.kc;
+  if (kc <= 0) kc = (smem_for_stages / (4 * kb_bytes) >= 3) ? 4 : (smem_for_stages / (2 * kb_bytes) >= 3) ? 2 : 1;
+  while (kc > 1 && smem_for_stages / (kc * kb_bytes) < 2) kc >>= 1;
   int S = std::max(1, std::min(l.split_k, up.kb_total));
-  up.kb_per_slice = (up.kb_total + S - 1) / S;
-  S = (up.kb_total + up.kb_per_slice - 1) / up.kb_per_slice;   // every slice non-empty
+  up.kb_per_slice = ((up.kb_total + S - 1) / S + kc - 1) / kc * kc;     // slices start on a stage boundary
+  S = (up.kb_total + up.kb_per_slice - 1) / up.kb_per_slice;              // every slice non-empty
   up.split_k = S;
   l.split_k = S;
-  up.stage_bytes = kXTileBytes + bn_max * kRowBytes;
-  up.stages = std::min(kMaxStages, (kSmemBudget - 1024 - 256) / up.stage_bytes);
+  up.kc = kc;
+  up.wide = ((long long)p.k * elem_bytes(p.dtype)) % 128 == 0 ? 1 : 0;
+  up.stage_bytes = kc * kb_bytes;
+  up.stages = std::min(kMaxStages, smem_for_stages / up.stage_bytes);
   up.alpha = p.alpha; up.beta = p.beta; up.ialpha = p.ialpha; up.ibeta = p.ibeta;
   up.ws_tile_words = bn_max * kUmmaM;
   up.scale_p = swap ? p.b_scales : p.a_scales;
@@ -279,10 +293,11 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   }
 
   CUtensorMap tx, ty0, ty1;
-  if (int rc = make_tmap(&tx, p.dtype, X, up.P, p.k, ldx, kUmmaM)) return rc;
-  if (int rc = make_tmap(&ty0, p.dtype, Y, up.Q, p.k, ldy, up.reg[0].bn)) return rc;
+  const int map_kc = up.wide ? up.kc : 0;
+  if (int rc = make_tmap(&tx, p.dtype, X, up.P, p.k, ldx, kUmmaM, map_kc)) return rc;
+  if (int rc = make_tmap(&ty0, p.dtype, Y, up.Q, p.k, ldy, up.reg[0].bn, map_kc)) return rc;
   if (up.num_regions == 2) {
-    if (int rc = make_tmap(&ty1, p.dtype, Y, up.Q, p.k, ldy, up.reg[1].bn)) return rc;
+    if (int rc = make_tmap(&ty1, p.dtype, Y, up.Q, p.k, ldy, up.reg[1].bn, map_kc)) return rc;
   } else {
     ty1 = ty0;
   }
@@ -493,6 +508,20 @@ int mp_gemm_rcc_pid(int dtype, int pid, int split_k, int m, int n, int k, const 
     return fail(MP_ERR_UNALIGNED_K, " k is not aligned, please check! (k=%d, pid %d needs k %% %d == 0)", k, pid, c.align);
   const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
   return run_pid(p, pid, split_k, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k, const void* A,
+                     const void* B, void* C, float alpha, float beta, void* stream) {
+  if (int rc = check_rcc_args(dtype, m, n, k, A, B, C)) return rc;
+  if (dtype == MP_FP32) return fail(MP_ERR_UNSUPPORTED, "explicit tiles exist for the tensor-core dtypes only");
+  if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0 || (kc != 0 && kc != 1 && kc != 2 && kc != 4))
+    return fail(MP_ERR_INVALID_ARG, "bad tile: orient=%d bn=%d kc=%d", orient, bn, kc);
+  if (m == 0 || n == 0) return MP_OK;
+  const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+  if (!tma_compatible(p)) return fail(MP_ERR_UNALIGNED_K, "operands do not meet the 16-byte alignment of the tensor path");
+  Launch l;
+  l.orient = orient; l.bn = bn; l.kc = kc; l.split_k = std::max(1, split_k);
+  return run_umma(p, l, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int mp_twin_gemm_fp16(int m, int n, int k, int split_n, const void* A, const void* B, void* C, float alpha,

@@ -55,9 +55,11 @@ struct UmmaParams {
   int total_tiles;
   int split_k;        // K slices per tile (>= 1); every slice is non-empty
   int kb_total;       // ceil(K / elements per K block)
-  int kb_per_slice;
+  int kb_per_slice;   // a multiple of kc
+  int kc;             // K blocks per pipeline stage (1, 2 or 4)
+  int wide;           // 1: tensor maps are 3-D [K/kb][rows][kb] and one load brings kc K blocks
   int stages;
-  int stage_bytes;    // kXTileBytes + bn_max * kRowBytes
+  int stage_bytes;    // kc * (kXTileBytes + bn_max * kRowBytes)
   int group_p;        // raster: tiles are walked in groups of `group_p` rows of tiles
   void* out;
   long long out_stride_p, out_stride_q;   // element strides of `out` along P and Q
@@ -252,17 +254,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const UnitCoord u = decode_unit(p, w);
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
-        const uint32_t tx = (uint32_t)(kXTileBytes + r.bn * kRowBytes);
+        const uint32_t tx = (uint32_t)(p.kc * (kXTileBytes + r.bn * kRowBytes));
+        const uint32_t y_off = (uint32_t)(p.kc * kXTileBytes);
         const int prow = u.tp * kUmmaM;
         const int qrow = r.q_begin + u.tq * r.bn;
-        for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
+        for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
           const int s = (int)(it % (uint32_t)stages);
           const uint32_t ph = (it / (uint32_t)stages) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, status, MP_DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
           const uint32_t a_dst = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
           mbar_arrive_expect_tx(full_bar(s), tx);
-          tma_load_2d(a_dst, &tmX, full_bar(s), kb * kElemsPerKb, prow);
-          tma_load_2d(a_dst + kXTileBytes, tmY, full_bar(s), kb * kElemsPerKb, qrow);
+          if (p.wide) {
+            tma_load_3d(a_dst, &tmX, full_bar(s), 0, prow, kb);
+            tma_load_3d(a_dst + y_off, tmY, full_bar(s), 0, qrow, kb);
+          } else {
+            // 2-D maps (K not a multiple of one K block): one box per K block; boxes past the
+            // end of K are filled with zeros by the TMA unit and still count their bytes
+            for (int c = 0; c < p.kc; ++c) {
+              tma_load_2d(a_dst + (uint32_t)(c * kXTileBytes), &tmX, full_bar(s), (kb + c) * kElemsPerKb, prow);
+              tma_load_2d(a_dst + y_off + (uint32_t)(c * r.bn * kRowBytes), tmY, full_bar(s),
+                          (kb + c) * kElemsPerKb, qrow);
+            }
+          }
         }
       }
       if (!ok) {
@@ -290,20 +303,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t d_tmem = tmem_base + buf * (uint32_t)kMaxBN;
         const uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kUmmaM, (uint32_t)r.bn)
                                                  : umma_idesc(1u, 0u, kUmmaM, (uint32_t)r.bn);
-        for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
+        for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
           const int s = (int)(it % (uint32_t)stages);
           const uint32_t ph = (it / (uint32_t)stages) & 1u;
           if (!mbar_wait(full_bar(s), ph, status, MP_DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
-          const uint32_t b_addr = a_addr + kXTileBytes;
+          const uint32_t b_addr = a_addr + (uint32_t)(p.kc * kXTileBytes);
+          const int nc = min(p.kc, u.kb1 - kb);     // K blocks of this stage that lie inside the slice
+          for (int c = 0; c < nc; ++c) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
-            const uint64_t ad = umma_smem_desc_sw128(a_addr + 32u * kk);
-            const uint64_t bd = umma_smem_desc_sw128(b_addr + 32u * kk);
-            const uint32_t acc = (kb > u.kb0 || kk > 0) ? 1u : 0u;
-            if constexpr (KIND == KIND_I8) umma_i8(d_tmem, ad, bd, idesc, acc);
-            else umma_f16(d_tmem, ad, bd, idesc, acc);
+            for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
+              const uint64_t ad = umma_smem_desc_sw128(a_addr + (uint32_t)(c * kXTileBytes) + 32u * kk);
+              const uint64_t bd = umma_smem_desc_sw128(b_addr + (uint32_t)(c * r.bn * kRowBytes) + 32u * kk);
+              const uint32_t acc = (kb > u.kb0 || c > 0 || kk > 0) ? 1u : 0u;
+              if constexpr (KIND == KIND_I8) umma_i8(d_tmem, ad, bd, idesc, acc);
+              else umma_f16(d_tmem, ad, bd, idesc, acc);
+            }
           }
           tc_commit(empty_bar(s));      // stage reusable once these MMAs have read it
         }

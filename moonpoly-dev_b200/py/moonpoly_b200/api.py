@@ -59,6 +59,7 @@ def lib() -> ctypes.CDLL:
         L.mp_linear.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp]
         L.mp_gemm_rcc.argtypes = [ci, ci, ci, ci, vp, vp, vp, cf, cf, vp]
         L.mp_gemm_rcc_pid.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp, vp, cf, cf, vp, sz, vp]
+        L.mp_gemm_rcc_tile.argtypes = [ci, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp, cf, cf, vp]
         L.mp_workspace_size.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(sz)]
         L.mp_select_plan.argtypes = [ci, ci, ci, ci, ctypes.POINTER(Plan)]
         L.mp_pid_info.argtypes = [ci, ci, ctypes.POINTER(ci * 3), ctypes.POINTER(ci)]
@@ -203,6 +204,19 @@ def gemm_rcc_pid(a: torch.Tensor, b_nk: torch.Tensor, pid: int, split_k: int = 1
     ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
     _check(lib().mp_gemm_rcc_pid(dt, pid, split_k, m, n, k, _ptr(a), _ptr(b_nk), _ptr(c_nm), alpha, beta,
                                  _ptr(workspace), ws_bytes, _stream(a)))
+    return c_nm
+
+
+def gemm_rcc_tile(a: torch.Tensor, b_nk: torch.Tensor, orient: int, bn: int, kc: int = 0, split_k: int = 1,
+                  c_nm: Optional[torch.Tensor] = None, alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """Tuning entry: the tensor-core kernel with an explicit tile (see mp_gemm_rcc_tile)."""
+    dt = _dtype_code(a)
+    m, k = a.shape
+    n = b_nk.shape[0]
+    if c_nm is None:
+        c_nm = torch.empty((n, m), dtype=_out_dtype(a), device=a.device)
+    _check(lib().mp_gemm_rcc_tile(dt, orient, bn, kc, split_k, m, n, k, _ptr(a), _ptr(b_nk), _ptr(c_nm), alpha, beta,
+                                  _stream(a)))
     return c_nm
 
 
