@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -20,6 +21,12 @@ namespace {
 using namespace mp;
 
 thread_local char g_err[512] = "";
+// Programmatic dependent launch of the tensor-core kernel (prologue overlaps the previous kernel's
+// tail).  MOONPOLY_DISABLE_PDL=1 turns it off.
+const bool g_use_pdl = [] {
+  const char* v = std::getenv("MOONPOLY_DISABLE_PDL");
+  return !(v && v[0] && v[0] != '0');
+}();
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -208,8 +215,17 @@ int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CU
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     d.attrs[attr_slot] = true;
   }
-  kern<<<grid, kUmmaThreads, smem, stream>>>(tx, ty0, ty1, up);
-  MP_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kUmmaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tx, ty0, ty1, up));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
 }
@@ -261,6 +277,9 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   l.split_k = S;
   up.kc = kc;
   up.wide = ((long long)p.k * elem_bytes(p.dtype)) % 128 == 0 ? 1 : 0;
+  // L2 prefetch ahead of the dependency wait pays when the launch is a short, memory-bound stream
+  // (few K blocks per CTA); cap it at 512 KB per CTA
+  up.prefetch_kb = g_use_pdl ? std::min(up.kb_per_slice, (512 * 1024) / kb_bytes) : 0;
   up.stage_bytes = kc * kb_bytes;
   up.stages = std::min(kMaxStages, smem_for_stages / up.stage_bytes);
   up.alpha = p.alpha; up.beta = p.beta; up.ialpha = p.ialpha; up.ibeta = p.ibeta;
@@ -608,5 +627,14 @@ int mp_device_status(void* stream, int* device_code) {
   }
   return MP_OK;
 }
+
+#ifdef MP_TRACE
+// debugging aid of trace builds: copies the per-CTA phase timestamps (160 x 16 uint64) to `out`
+int mp_debug_trace(unsigned long long* out) {
+  MP_CUDA_TRY(cudaDeviceSynchronize());
+  MP_CUDA_TRY(cudaMemcpyFromSymbol(out, mp::g_mp_trace, sizeof(unsigned long long) * 160 * 16));
+  return MP_OK;
+}
+#endif
 
 }  // extern "C"

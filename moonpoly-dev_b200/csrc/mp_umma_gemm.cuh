@@ -27,6 +27,15 @@ namespace mp {
 
 __device__ int g_mp_status = 0;   // 0 = ok; otherwise the first MP_DEV_* code any kernel recorded
 
+// Optional phase tracing (compile with -DMP_TRACE): per CTA, nanosecond timestamps of the phases
+// of its first work unit.  Off in the shipped library.
+#ifdef MP_TRACE
+__device__ unsigned long long g_mp_trace[160][16];
+#define MP_TRACE_MARK(slot) do { g_mp_trace[blockIdx.x][slot] = globaltimer_ns(); } while (0)
+#else
+#define MP_TRACE_MARK(slot) do { } while (0)
+#endif
+
 constexpr int kUmmaM = 128;            // rows of X per tile
 constexpr int kRowBytes = 128;         // one K block = 128 bytes of K per row (64 fp16 / 128 int8)
 constexpr int kXTileBytes = kUmmaM * kRowBytes;
@@ -61,11 +70,12 @@ struct UmmaParams {
   int stages;
   int stage_bytes;    // kc * (kXTileBytes + bn_max * kRowBytes)
   int group_p;        // raster: tiles are walked in groups of `group_p` rows of tiles
+  int prefetch_kb;    // K blocks of a CTA's first unit to prefetch into L2 before the dependency wait
   void* out;
   long long out_stride_p, out_stride_q;   // element strides of `out` along P and Q
   float alpha, beta;
   int ialpha, ibeta;
-  uint32_t* ws_partials;   // [total_tiles][split_k][bn_max][128] 32-bit words
+  uint32_t* ws_partials;   // [total_tiles][split_k][128 rows][bn of the tile's region] 32-bit words
   unsigned* ws_counters;   // [total_tiles][4], zero on entry, left zero on exit
   int ws_tile_words;       // bn_max * 128
   // scaled int8 matmul epilogue
@@ -220,6 +230,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   int* status = &g_mp_status;
 
   if (threadIdx.x == 0) {
+    MP_TRACE_MARK(0);
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -242,12 +253,42 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Programmatic dependent launch: everything above touched only this CTA's shared memory, TMEM
+  // and kernel parameters, so it may overlap the tail of the previous kernel in the stream.  Let
+  // the next kernel start its own prologue now.  Each role then waits (griddep_wait) before its
+  // first access to global memory that the previous kernel may still produce or use: the
+  // operands, C, the split-K scratch.  The MMA issuer touches only shared memory and TMEM.
+  if (threadIdx.x == 0) MP_TRACE_MARK(1);
+  griddep_launch_dependents();
+
   const int total_units = p.total_tiles * p.split_k;
   constexpr int kElemsPerKb = (KIND == KIND_I8) ? 128 : 64;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one lane)
     if (lane == 0) {
+      // While the previous kernel drains, pull the first unit's operands towards L2 (a hint only;
+      // whatever the previous kernel still writes reaches L2 as well, so this cannot go stale).
+      if ((int)blockIdx.x < total_units) {
+        const UnitCoord u = decode_unit(p, (int)blockIdx.x);
+        const Region& r = p.reg[u.region];
+        const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
+        const int prow = u.tp * kUmmaM, qrow = r.q_begin + u.tq * r.bn;
+        const int kb_lim = min(u.kb1, u.kb0 + p.prefetch_kb);
+        for (int kb = u.kb0; kb < kb_lim; kb += p.kc) {
+          if (p.wide) {
+            tma_prefetch_3d(&tmX, 0, prow, kb);
+            tma_prefetch_3d(tmY, 0, qrow, kb);
+          } else {
+            for (int c = 0; c < p.kc; ++c) {
+              tma_prefetch_2d(&tmX, (kb + c) * kElemsPerKb, prow);
+              tma_prefetch_2d(tmY, (kb + c) * kElemsPerKb, qrow);
+            }
+          }
+        }
+      }
+      griddep_wait();
+      MP_TRACE_MARK(2);
       uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x) {
@@ -307,6 +348,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const int s = (int)(it % (uint32_t)stages);
           const uint32_t ph = (it / (uint32_t)stages) & 1u;
           if (!mbar_wait(full_bar(s), ph, status, MP_DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
+          if (ui == 0 && kb == u.kb0) MP_TRACE_MARK(3);
+          if (ui == 0 && kb + p.kc >= u.kb1) MP_TRACE_MARK(4);
           tc_fence_after();
           const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
           const uint32_t b_addr = a_addr + (uint32_t)(p.kc * kXTileBytes);
@@ -331,12 +374,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int quad = warp & 3;
     uint32_t ui = 0;
     bool ok = true;
+    griddep_wait();
     for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
       const UnitCoord u = decode_unit(p, w);
       const Region& r = p.reg[u.region];
       const uint32_t buf = ui & 1u;
       const uint32_t use = ui >> 1;
       if (!mbar_wait(tfull_bar((int)buf), use & 1u, status, MP_DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
+      if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(5);
       tc_fence_after();
       const uint32_t t_addr = tmem_base + buf * (uint32_t)kMaxBN + ((uint32_t)(quad * 32) << 16);
       const int row_in_tile = quad * 32 + lane;
@@ -355,44 +400,73 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));
       } else {
-        // park this slice's raw accumulators: [tile][slice][column][row]; 32 lanes -> 128 contiguous bytes
-        uint32_t* part = p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words;
+        // park this slice's raw accumulators: [tile][slice][row][column]; every thread owns a
+        // contiguous run of its row and moves it with 16-byte accesses
+        uint32_t* part = p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words +
+                         (size_t)row_in_tile * r.bn;
         for (int c0 = 0; c0 < r.bn; c0 += 16) {
           uint32_t v[16];
           tmem_ld_x16(t_addr + (uint32_t)c0, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) __stcg(part + (size_t)(c0 + j) * kUmmaM + row_in_tile, v[j]);
+          for (int j = 0; j < 4; ++j)
+            __stcg(reinterpret_cast<uint4*>(part + c0) + j, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));   // TMEM buffer is free again
+        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(6);
         __threadfence();
         __syncwarp();
         unsigned prev = 0;
         unsigned* ctr = p.ws_counters + (size_t)u.tile * 4 + quad;
         if (lane == 0) prev = atomicAdd(ctr, 1u);
         prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(7);
         if (prev == (unsigned)(p.split_k - 1)) {
-          // last slice to arrive for this quadrant of the tile: reduce in slice order and finish
+          // last slice to arrive for this quadrant of the tile: sum in slice order s = 0..S-1
+          // (fixed order => bit-identical results from run to run) and finish
           __threadfence();
-          const uint32_t* base = p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words;
-          for (int c0 = 0; c0 < r.bn; c0 += 16) {
-            uint32_t v[16];
+          const uint32_t* base = p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words +
+                                 (size_t)row_in_tile * r.bn;
+          // 32 columns per pass (bn is a multiple of 16: the last pass may be half wide); the loads
+          // of up to four slices are all in flight before the first is consumed
+          for (int c0 = 0; c0 < r.bn; c0 += 32) {
+            const int nq = (r.bn - c0 >= 32) ? 8 : 4;      // 16-byte words in this pass
+            uint32_t v[32];
+            for (int s0 = 0; s0 < p.split_k; s0 += 4) {
+              uint4 x[4][8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __ldcg(base + (size_t)(c0 + j) * kUmmaM + row_in_tile);
-            for (int s = 1; s < p.split_k; ++s) {
-              const uint32_t* ps = base + (size_t)s * p.ws_tile_words;
+              for (int ds = 0; ds < 4; ++ds)
+                if (s0 + ds < p.split_k) {
+                  const uint4* ps = reinterpret_cast<const uint4*>(base + (size_t)(s0 + ds) * p.ws_tile_words + c0);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const uint32_t x = __ldcg(ps + (size_t)(c0 + j) * kUmmaM + row_in_tile);
-                if constexpr (KIND == KIND_I8) v[j] = (uint32_t)((int)v[j] + (int)x);
-                else v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(x)));
-              }
+                  for (int j = 0; j < 8; ++j)
+                    if (j < nq) x[ds][j] = __ldcg(ps + j);
+                }
+#pragma unroll
+              for (int ds = 0; ds < 4; ++ds)
+                if (s0 + ds < p.split_k) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (j < nq) {
+                      const uint32_t w[4] = {x[ds][j].x, x[ds][j].y, x[ds][j].z, x[ds][j].w};
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) {
+                        uint32_t& acc = v[4 * j + e];
+                        if (s0 + ds == 0) acc = w[e];
+                        else if constexpr (KIND == KIND_I8) acc = (uint32_t)((int)acc + (int)w[e]);
+                        else acc = __float_as_uint(__fadd_rn(__uint_as_float(acc), __uint_as_float(w[e])));
+                      }
+                    }
+                }
             }
-            store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end);
+            store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[0]), pi, q_tile0 + c0, q_end);
+            if (nq == 8)
+              store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[16]), pi, q_tile0 + c0 + 16, q_end);
           }
           __syncwarp();
+          if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(8);
           if (lane == 0) *ctr = 0u;   // leave the counter as it was found
         }
       }
@@ -402,6 +476,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) MP_TRACE_MARK(9);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();

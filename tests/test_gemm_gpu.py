@@ -217,12 +217,13 @@ def test_fp32_ctest_shapes_and_forced_splitk(api, m, n, k, monkeypatch):
     b = rng.small_ints(1, rng.STREAM_B, (n, k), dtype=np.float32)
     ref = (a.astype(np.int64) @ b.astype(np.int64).T).T.astype(np.float32)
     assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
+    free_plan = repr(api.select_plan(api.MP_FP32, m, n, k))
     monkeypatch.setenv("MOONPOLY_FP32_PATTERN3_FORCE_SPLITK", "2")
     plan = api.select_plan(api.MP_FP32, m, n, k)
     assert plan.pattern == 3 and plan.split_k == 2 and plan.pid == -1
     assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
     monkeypatch.delenv("MOONPOLY_FP32_PATTERN3_FORCE_SPLITK")
-    assert api.select_plan(api.MP_FP32, m, n, k).pattern == 1
+    assert repr(api.select_plan(api.MP_FP32, m, n, k)) == free_plan     # the flag is re-read on every call
 
 
 def test_fp32_every_pid(api, oracle):
