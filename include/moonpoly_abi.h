@@ -76,6 +76,25 @@ int mp_gemm_rcc_pid(int dtype, int pid, int split_k, int m, int n, int k, const 
                     const void* B, void* C, float alpha, float beta, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  Same contract as mp_gemm_rcc_pid, for callers that must not
+ * allocate device memory while they run: an inference server that commits the whole GPU to its
+ * weights and KV cache at start-up and treats any later allocation as a bug (it could fail, or
+ * stall every stream while the driver maps memory), or a plug-in that lives inside another
+ * runtime's memory budget and is not allowed to call cudaMalloc at all.  mp_gemm_rcc_pid with a
+ * NULL workspace grows a per-stream scratch on demand; this entry point instead keeps the split-K
+ * scratch in an 8 MiB array that is part of the library image on every GPU that loads it.
+ *   - It calls no cudaMalloc / cudaFree and nothing else that allocates.
+ *   - Problems whose scratch need (mp_workspace_size) exceeds 8 MiB are refused with
+ *     MP_ERR_WORKSPACE and a message naming both sizes; nothing is computed.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+ *     make that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which still holds the previous call's data; the
+ *     words that must start at zero are cleared on `stream` before each launch.  Two calls that
+ *     overlap on the GPU (different streams) race on it: keep them on one stream or order them. */
+int mp_gemm_rcc_pid_static_scratch(int dtype, int pid, int split_k, int m, int n, int k,
+                                   const void* A, const void* B, void* C, float alpha, float beta,
+                                   void* stream);
+
 /* Tuning entry (no counterpart in the reference, whose tiles are fixed at compile time by its
  * CUTLASS template instantiations): run the FP16 / INT8 tensor-core kernel on an RCC problem with
  * an explicit tile instead of a pid.  orient 0 puts the rows of A on the 128-row UMMA-M side and

@@ -136,6 +136,15 @@ int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes,
 }
 
 // ------------------------------------------------------------------------------------------------
+// Built-in scratch of mp_gemm_rcc_pid_static_scratch: lives in every GPU that loads the library,
+// from load to exit.  The name is a host-side stand-in; kernels get the address that
+// cudaGetSymbolAddress returns for the current device.
+// ------------------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+// ------------------------------------------------------------------------------------------------
 // problem description shared by all dtypes
 // ------------------------------------------------------------------------------------------------
 struct Problem {
@@ -626,6 +635,41 @@ int mp_device_status(void* stream, int* device_code) {
     return fail(MP_ERR_DEVICE, "a kernel recorded device status %d (bounded wait expired)", code);
   }
   return MP_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Forced-pid GEMM that never allocates: its split-K scratch is a fixed array inside the library.
+// ------------------------------------------------------------------------------------------------
+int mp_gemm_rcc_pid_static_scratch(int dtype, int pid, int split_k, int m, int n, int k, const void* A,
+                                   const void* B, void* C, float alpha, float beta, void* stream) {
+  if (int rc = check_rcc_args(dtype, m, n, k, A, B, C)) return rc;
+  if (split_k <= 0) split_k = 2;
+  const TileCfg c = tile_cfg(dtype, pid);
+  if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, dtype);
+  if (k % c.align != 0)
+    return fail(MP_ERR_UNALIGNED_K, " k is not aligned, please check! (k=%d, pid %d needs k %% %d == 0)", k, pid, c.align);
+  size_t need = 0;
+  if (int rc = mp_workspace_size(dtype, pid, m, n, k, split_k, &need)) return rc;
+  if (need > kStaticScratchBytes)
+    return fail(MP_ERR_WORKSPACE,
+                "this problem needs %zu bytes of split-K scratch but the built-in array holds %zu; "
+                "lower split_k or use mp_gemm_rcc_pid with a workspace of your own",
+                need, (size_t)kStaticScratchBytes);
+  int dev = -1;
+  MP_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(MP_ERR_CUDA, "device index %d out of range", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // set-up, once per device, with that device current: host code only holds a stand-in for the
+    // array's name, so ask the runtime for its address on this device
+    std::lock_guard<std::mutex> g(g_mu);
+    void* ptr = nullptr;
+    MP_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+  // the scratch keeps whatever the previous call left; run_umma clears the counters it needs at
+  // zero (a memset on `stream`, not an allocation) before the launch
+  return run_pid(p, pid, split_k, g_static_scratch_ptr[dev], kStaticScratchBytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 #ifdef MP_TRACE

@@ -59,6 +59,7 @@ def lib() -> ctypes.CDLL:
         L.mp_linear.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp]
         L.mp_gemm_rcc.argtypes = [ci, ci, ci, ci, vp, vp, vp, cf, cf, vp]
         L.mp_gemm_rcc_pid.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp, vp, cf, cf, vp, sz, vp]
+        L.mp_gemm_rcc_pid_static_scratch.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp, vp, cf, cf, vp]
         L.mp_gemm_rcc_tile.argtypes = [ci, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp, cf, cf, vp]
         L.mp_workspace_size.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(sz)]
         L.mp_select_plan.argtypes = [ci, ci, ci, ci, ctypes.POINTER(Plan)]
