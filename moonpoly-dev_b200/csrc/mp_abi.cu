@@ -171,10 +171,31 @@ struct Launch {
 
 int elem_bytes(int dtype) { return dtype == MP_FP16 ? 2 : dtype == MP_INT8 ? 1 : 4; }
 
+// Tensor maps are pure functions of (pointer, extents, pitch, box): a small per-thread cache saves
+// the driver call (about a microsecond each) when a caller reuses its buffers, as serving does.
+struct TmapKey {
+  const void* ptr; long long rows, k, ld; int box_rows, kc, dtype;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows && kc == o.kc &&
+           dtype == o.dtype;
+  }
+};
+struct TmapSlot { TmapKey key; bool valid; CUtensorMap map; };
+constexpr int kTmapSlots = 256;
+thread_local TmapSlot t_tmap_cache[kTmapSlots];
+
 // kc == 0: 2-D map [rows][k] with a (128 bytes x box_rows) box.  kc > 0 (k a multiple of one
 // 128-byte K block): 3-D map [k/kb][rows][kb] with a (128 bytes x box_rows x kc) box.
 int make_tmap(CUtensorMap* tm, int dtype, const void* ptr, long long rows, long long k, long long ld, int box_rows,
               int kc) {
+  const TmapKey key{ptr, rows, k, ld, box_rows, kc, dtype};
+  uint64_t h = reinterpret_cast<uintptr_t>(ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= (uint64_t)rows * 0xBF58476D1CE4E5B9ull + (uint64_t)k * 0x94D049BB133111EBull + (uint64_t)box_rows * 131 + kc;
+  TmapSlot& slot = t_tmap_cache[(h >> 32) & (kTmapSlots - 1)];
+  if (slot.valid && slot.key == key) {
+    *tm = slot.map;
+    return MP_OK;
+  }
   const int eb = elem_bytes(dtype);
   const cuuint64_t kb = (cuuint64_t)(128 / eb);
   cuuint64_t gdim[3] = {(cuuint64_t)k, (cuuint64_t)rows, 1};
@@ -187,6 +208,9 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* ptr, long long rows, long 
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  slot.key = key;
+  slot.map = *tm;
+  slot.valid = true;
   return MP_OK;
 }
 

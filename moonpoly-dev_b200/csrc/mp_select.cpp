@@ -153,7 +153,7 @@ struct LiveFlags {
            ((unsigned)(int8_force & 0xff)) << 16;
   }
 };
-LiveFlags live_flags(int dtype) {
+LiveFlags read_live_flags(int dtype) {
   LiveFlags f{};
   if (dtype == MP_FP16) {
     f.p2 = env_flag("MOONPOLY_ENABLE_PATTERN2", true);
@@ -170,6 +170,29 @@ LiveFlags live_flags(int dtype) {
     f.int8_force = env_int("MOONPOLY_INT8_PATTERN3_FORCE_SPLITK", 0);
   }
   return f;
+}
+
+// One pass over the environment block per call: a hash of every MOONPOLY_* entry.  As long as the
+// hash is unchanged the flag values parsed last time are still right, so the per-call cost is a
+// single scan instead of one getenv per flag.
+extern "C" char** environ;
+uint64_t moonpoly_env_hash() {
+  uint64_t h = 1469598103934665603ull;
+  for (char** e = environ; e != nullptr && *e != nullptr; ++e) {
+    const char* s = *e;
+    if (s[0] != 'M' || s[1] != 'O' || s[2] != 'O' || s[3] != 'N' || std::strncmp(s, "MOONPOLY_", 9) != 0) continue;
+    for (; *s; ++s) h = (h ^ (unsigned char)*s) * 1099511628211ull;
+    h = (h ^ 0xffu) * 1099511628211ull;
+  }
+  return h;
+}
+LiveFlags live_flags(int dtype) {
+  struct Cached { uint64_t hash; bool valid; LiveFlags f; };
+  thread_local Cached cache[3] = {};
+  const uint64_t h = moonpoly_env_hash();
+  Cached& c = cache[dtype == MP_FP16 ? 0 : dtype == MP_FP32 ? 1 : 2];
+  if (!c.valid || c.hash != h) { c.f = read_live_flags(dtype); c.hash = h; c.valid = true; }
+  return c.f;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -318,15 +341,37 @@ void pid_tile_meta(int dtype, int pid, int out[3]) {
   out[2] = dtype == MP_INT8 ? 128 : 64;
 }
 
+namespace {
+// pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
+struct PidMeta { TileCfg cfg; int meta[3]; };
+struct MetaTables {
+  PidMeta fp16[440], int8[46], fp32[40];
+  MetaTables() {
+    for (int p = 0; p < 440; ++p) { fp16[p].cfg = tile_cfg(MP_FP16, p); pid_tile_meta(MP_FP16, p, fp16[p].meta); }
+    for (int p = 0; p < 46; ++p) { int8[p].cfg = tile_cfg(MP_INT8, p); pid_tile_meta(MP_INT8, p, int8[p].meta); }
+    for (int p = 0; p < 40; ++p) { fp32[p].cfg = tile_cfg(MP_FP32, p); pid_tile_meta(MP_FP32, p, fp32[p].meta); }
+  }
+};
+const PidMeta* pid_meta(int dtype, int pid) {
+  static const MetaTables t;
+  if (pid < 0) return nullptr;
+  if (dtype == MP_FP16) return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
+  if (dtype == MP_INT8) return pid < 46 ? &t.int8[pid] : nullptr;
+  if (dtype == MP_FP32) return pid < 40 ? &t.fp32[pid] : nullptr;
+  return nullptr;
+}
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+}  // namespace
+
 float cost_ms(int dtype, int pid, int split_k, int m, int n, int k) {
-  const TileCfg c = tile_cfg(dtype, pid);
-  if (!c.valid || m <= 0 || n <= 0 || k <= 0) return kInf;
-  int meta[3];
-  pid_tile_meta(dtype, pid, meta);
+  const PidMeta* pm = pid_meta(dtype, pid);
+  if (pm == nullptr || m <= 0 || n <= 0 || k <= 0) return kInf;
+  const TileCfg& c = pm->cfg;
+  const int* meta = pm->meta;
   const int S = std::max(1, split_k);
-  const int lm = std::max(1, ceil_div(n, meta[0]));   // feature_m = n
-  const int ln = std::max(1, ceil_div(m, meta[1]));   // feature_n = m
-  const int k_iter = std::max(1, ceil_div(k, (long long)meta[2] * S));
+  const int lm = std::max(1, cdiv(n, meta[0]));   // feature_m = n
+  const int ln = std::max(1, cdiv(m, meta[1]));   // feature_n = m
+  const int k_iter = std::max(1, cdiv(k, meta[2] * S));
   const long long units = (long long)lm * ln * S;
   const int sms = g_num_sms.load(std::memory_order_relaxed);
   const int waves = std::max(1, ceil_div(units, sms));

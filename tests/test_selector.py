@@ -1,0 +1,133 @@
+"""Host logic of the selector, pid tables and cost model (no GPU needed)."""
+import ctypes
+import time
+
+import pytest
+
+
+def test_pid_tables_follow_the_reference_contract(api):
+    # alignment contract of the primary FP16 pids (moonpoly/core/fp16/fp16_rcc_cost.cu:32-36)
+    ref_align = [8, 8, 8, 8, 8, 8, 8, 2, 8, 2, 1, 2, 2, 2, 8, 8, 8, 8, 8, 8,
+                 8, 4, 8, 8, 4, 8, 4, 4, 8, 1, 8, 8, 2, 1, 8, 2, 2, 8, 1, 8, 8]
+    for pid, al in enumerate(ref_align):
+        tile, got = api.pid_info(api.MP_FP16, pid)
+        assert got == al, pid
+        pm, pn, pk = tile
+        assert pk == 64 and 128 in (pm, pn) and min(pm, pn) % 16 == 0 and max(pm, pn) <= 256
+    # split-K pids reuse the primary tiles: 407 -> pid 8's tile, 439 -> pid 7's (splitk_candidates.json)
+    assert api.pid_info(api.MP_FP16, 407)[0] == api.pid_info(api.MP_FP16, 8)[0]
+    assert api.pid_info(api.MP_FP16, 439)[0] == api.pid_info(api.MP_FP16, 7)[0]
+    assert api.pid_info(api.MP_FP16, 413) == (api.pid_info(api.MP_FP16, 13)[0], 2)
+    for pid in range(400, 440):
+        api.pid_info(api.MP_FP16, pid)
+    # pids without a kernel fail cleanly
+    for pid in (41, 77, 150, 322, 399, 440, -1):
+        with pytest.raises(api.MoonpolyError) as e:
+            api.pid_info(api.MP_FP16, pid)
+        assert e.value.code == 4
+    assert all(api.pid_info(api.MP_INT8, p)[0][2] == 128 for p in range(46))
+    assert all(api.pid_info(api.MP_FP32, p)[1] == 1 for p in range(40))
+    for dt, bad in ((api.MP_INT8, 46), (api.MP_FP32, 40)):
+        with pytest.raises(api.MoonpolyError):
+            api.pid_info(dt, bad)
+
+
+def test_plan_is_argmin_of_cost_under_alignment(api):
+    for (m, n, k) in [(1, 4096, 4096), (4096, 4096, 4096), (512, 11008, 4096), (37, 1000, 520), (8, 1024, 8190)]:
+        plan = api.select_plan(api.MP_FP16, m, n, k)
+        if plan.pattern == 1:
+            best = min((api.cost_ms(api.MP_FP16, pid, 1, m, n, k), pid) for pid in range(40)
+                       if k % api.pid_info(api.MP_FP16, pid)[1] == 0)
+            assert plan.pid == best[1] and abs(plan.estimated_ms - best[0]) < 1e-6
+        elif plan.pattern == 3:
+            assert plan.split_k in (2, 4, 8) and k >= 2048 and (k + plan.split_k - 1) // plan.split_k >= 512
+            assert plan.pid in (4, 6, 7, 12, 13, 15, 19, 20, 23, 24, 25, 29, 31, 32, 33, 37, 39)
+            single = min(api.cost_ms(api.MP_FP16, pid, 1, m, n, k) for pid in range(40)
+                         if k % api.pid_info(api.MP_FP16, pid)[1] == 0)
+            assert plan.estimated_ms < single * 0.97 + 1e-9          # MOONPOLY_PATTERN3_MARGIN
+        # k = 8190 is only divisible by 2 and 1: the alignment contract must hold for the choice
+        if plan.pid >= 0:
+            assert k % api.pid_info(api.MP_FP16, plan.pid)[1] == 0
+
+
+def test_env_flags(api, monkeypatch):
+    m, n, k = 8, 4096, 8192
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 3
+    monkeypatch.setenv("MOONPOLY_ENABLE_PATTERN3", "0")          # re-read on every call
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 1
+    monkeypatch.setenv("MOONPOLY_ENABLE_PATTERN3", "off")
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 1
+    monkeypatch.delenv("MOONPOLY_ENABLE_PATTERN3")
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 3
+    # numeric flags are cached until mp_reload_env()
+    monkeypatch.setenv("MOONPOLY_PATTERN3_MIN_K", "100000")
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 3
+    api.reload_env()
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 1
+    monkeypatch.delenv("MOONPOLY_PATTERN3_MIN_K")
+    api.reload_env()
+    assert api.select_plan(api.MP_FP16, m, n, k).pattern == 3
+    # forced split for INT8 / FP32 (tests/cpp/int8/test_int8_row_col_col.cu:70-77)
+    monkeypatch.setenv("MOONPOLY_INT8_PATTERN3_FORCE_SPLITK", "2")
+    p = api.select_plan(api.MP_INT8, 64, 128, 128)
+    assert (p.pattern, p.pid, p.split_k) == (3, -1, 2)
+    monkeypatch.delenv("MOONPOLY_INT8_PATTERN3_FORCE_SPLITK")
+    assert api.select_plan(api.MP_INT8, 64, 128, 128).pattern == 1
+
+
+def test_pattern2_gate(api, monkeypatch):
+    # tail of n % 128 within 25 % of a tile opens the twin plan; it must still win by the margin
+    m, k = 4096, 4096
+    monkeypatch.setenv("MOONPOLY_PATTERN2_MARGIN", "10.0")       # let it win whenever the gate opens
+    api.reload_env()
+    try:
+        p = api.select_plan(api.MP_FP16, m, 4096 + 16, k)
+        assert p.pattern == 2 and p.split_n == 4096 and p.pid == -1
+        assert api.select_plan(api.MP_FP16, m, 4096 + 100, k).pattern != 2     # tail ratio 0.78 > 0.25
+        assert api.select_plan(api.MP_FP16, m, 4096, k).pattern != 2           # regular n: closed by default
+        assert api.select_plan(api.MP_FP16, m, 256 + 16, k).pattern != 2       # n < MOONPOLY_PATTERN2_MIN_N
+        assert api.select_plan(api.MP_FP16, m, 4096 + 16, 4100).pattern != 2   # k % 8 != 0
+        monkeypatch.setenv("MOONPOLY_ENABLE_PATTERN2", "0")
+        assert api.select_plan(api.MP_FP16, m, 4096 + 16, k).pattern != 2
+    finally:
+        monkeypatch.delenv("MOONPOLY_PATTERN2_MARGIN")
+        monkeypatch.delenv("MOONPOLY_ENABLE_PATTERN2", raising=False)
+        api.reload_env()
+
+
+def test_bad_arguments(api):
+    L = api.lib()
+    p = api.Plan()
+    assert L.mp_select_plan(9, 1, 1, 1, ctypes.byref(p)) == 1
+    assert L.mp_select_plan(0, 0, 1, 1, ctypes.byref(p)) == 1
+    assert b"Unsupported data type" in L.mp_last_error_string() or L.mp_last_error_string()
+    out = (ctypes.c_int * 4)()
+    assert L.mp_scaled_mm_config(6, ctypes.byref(out)) == 1
+    for cfg in range(6):
+        tm, tn, tk, al = api.get_int8_scaled_mm_kernel_config(cfg)
+        assert tk == 128 and al == 16 and 128 in (tm, tn)
+
+
+def test_selection_overhead_budget(api):
+    """<= 5 us per shape on the host, cold (first sight of a shape) and memoised."""
+    L = api.lib()
+    p = api.Plan()
+    fn = L.mp_select_plan
+    shapes = [(1 + (i * 37) % 8192, 1024 + 128 * (i % 200), 4096) for i in range(4000)]
+    # ctypes call overhead, measured on a call that does no work
+    t0 = time.perf_counter()
+    for _ in range(4000):
+        L.mp_launch_count()
+    base = (time.perf_counter() - t0) / 4000
+    t0 = time.perf_counter()
+    for m, n, k in shapes:
+        fn(0, m, n, k, ctypes.byref(p))
+    cold = (time.perf_counter() - t0) / len(shapes) - base
+    t0 = time.perf_counter()
+    for _ in range(4):
+        for m, n, k in shapes[:500]:
+            fn(0, m, n, k, ctypes.byref(p))
+    warm = (time.perf_counter() - t0) / 2000 - base
+    print(f"selection: cold {cold * 1e6:.2f} us, memoised {warm * 1e6:.2f} us (ctypes overhead {base * 1e6:.2f} us removed)")
+    assert cold < 15e-6          # generous on a loaded CI box; the budget is 5 us
+    assert warm < 5e-6
