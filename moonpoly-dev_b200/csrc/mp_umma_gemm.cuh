@@ -197,6 +197,67 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
 
   float sp = 0.0f;
   if constexpr (EPI == EPI_SCALED) sp = p.scale_p[p.scale_p_scalar ? 0 : pi];
+  if constexpr (EPI == EPI_SCALED) {
+    // fast path: this thread's 16 outputs are contiguous and 16-byte aligned; scales and bias of
+    // the 16 columns come in with vector loads and the result leaves as two 16-byte stores
+    uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (long long)pi * p.out_stride_p + q0;
+    const bool vec_ok = p.out_stride_q == 1 && valid == 16 && (reinterpret_cast<uintptr_t>(o) & 15) == 0 &&
+                        (p.scale_q_scalar || (reinterpret_cast<uintptr_t>(p.scale_q + q0) & 15) == 0) &&
+                        (p.bias == nullptr || p.n_on_p ||
+                         (reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(p.bias) + q0) & 15) == 0);
+    if (vec_ok) {
+      float sq[16];
+      if (p.scale_q_scalar) {
+        const float s0 = p.scale_q[0];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sq[j] = s0;
+      } else {
+        const float4* s4 = reinterpret_cast<const float4*>(p.scale_q + q0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 t = __ldg(s4 + j);
+          sq[4 * j] = t.x; sq[4 * j + 1] = t.y; sq[4 * j + 2] = t.z; sq[4 * j + 3] = t.w;
+        }
+      }
+      uint16_t bq[16];
+      const bool has_bias = p.bias != nullptr;
+      if (has_bias) {
+        if (p.n_on_p) {
+          const uint16_t b0 = reinterpret_cast<const uint16_t*>(p.bias)[pi];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) bq[j] = b0;
+        } else {
+          const uint4* b4 = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + q0);
+          const uint4 t0 = __ldg(b4), t1 = __ldg(b4 + 1);
+          const uint32_t w[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { bq[2 * j] = (uint16_t)(w[j] & 0xffffu); bq[2 * j + 1] = (uint16_t)(w[j] >> 16); }
+        }
+      }
+      uint32_t packed[8];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float bs = p.n_on_p ? sp : sq[j];
+        const float as = p.n_on_p ? sq[j] : sp;
+        const float t1 = __fmul_rn(as, __fmul_rn(__int2float_rn((int)r[j]), bs));
+        uint16_t h = f32_to_out16(t1, p.out_bf16);
+        if (has_bias) {
+          if (p.out_bf16) {
+            const float s = __bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(bq[j]));
+            h = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+          } else {
+            const float s = __half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(bq[j]));
+            h = __half_as_ushort(__float2half_rn(s));
+          }
+        }
+        if (j & 1) packed[j >> 1] |= (uint32_t)h << 16;
+        else packed[j >> 1] = h;
+      }
+      reinterpret_cast<uint4*>(o)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      reinterpret_cast<uint4*>(o)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      return;
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     if (j < valid) {

@@ -144,5 +144,6 @@ def test_scaled_int8_mm_vs_float_reference(moonpoly, M, N, K, out_dtype, mode, w
     if bias is not None:
         ref = ref + bias.float()
     # two roundings to the output type (product, then the bias sum): a few ulp of the output dtype
-    rtol = 4e-3 if out_dtype == torch.float16 else 3e-2
-    torch.testing.assert_close(out.float(), ref, rtol=rtol, atol=1e-2)
+    # (the product is rounded before the bias is added, so a cancelling bias keeps the product's ulp)
+    rtol, atol = (4e-3, 1e-2) if out_dtype == torch.float16 else (3e-2, 6e-2)
+    torch.testing.assert_close(out.float(), ref, rtol=rtol, atol=atol)
