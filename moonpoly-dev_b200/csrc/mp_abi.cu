@@ -27,12 +27,6 @@ const bool g_use_pdl = [] {
   const char* v = std::getenv("MOONPOLY_DISABLE_PDL");
   return !(v && v[0] && v[0] != '0');
 }();
-// Split-K reduction inside a thread-block cluster.  MOONPOLY_DISABLE_CLUSTER_SPLITK=1 forces the
-// scratch-based reduction.
-const bool g_use_cluster = [] {
-  const char* v = std::getenv("MOONPOLY_DISABLE_CLUSTER_SPLITK");
-  return !(v && v[0] && v[0] != '0');
-}();
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -64,8 +58,6 @@ struct DeviceState {
   int sms = 0;
   int cc = 0;
   bool attrs[3] = {false, false, false};
-  int max_clusters[3][9];     // co-resident clusters per kernel variant and cluster size; -1 = not asked yet
-  DeviceState() { for (auto& row : max_clusters) for (int& v : row) v = -1; }
 };
 constexpr int kMaxDevices = 32;
 DeviceState g_dev[kMaxDevices];
@@ -250,54 +242,22 @@ size_t umma_workspace_bytes(const Problem& p, const Launch& l, size_t* counter_b
 
 template <int KIND, int EPI>
 int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CUtensorMap& ty0,
-                  const CUtensorMap& ty1, UmmaParams& up, long long units, size_t smem, cudaStream_t stream) {
+                  const CUtensorMap& ty1, const UmmaParams& up, int grid, size_t smem, cudaStream_t stream) {
   auto kern = umma_gemm_kernel<KIND, EPI>;
   if (!d.attrs[attr_slot]) {
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     d.attrs[attr_slot] = true;
   }
   cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(kUmmaThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  int na = 0;
-  if (g_use_pdl) {
-    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  int grid = (int)std::min<long long>(units, d.sms);
-  if (up.cluster_split) {
-    // The split_k CTAs of a tile are one cluster.  How many such clusters fit on the device at
-    // once depends on the GPC layout: ask the occupancy API once per (kernel, cluster size).
-    const int S = up.split_k;
-    int& cached = d.max_clusters[attr_slot][S];
-    if (cached < 0) {
-      cudaLaunchConfig_t q = cfg;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = (unsigned)S; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
-      q.attrs = qa; q.numAttrs = 1;
-      q.gridDim = dim3((unsigned)(d.sms / S * S));
-      int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
-      cached = n;
-    }
-    if (cached <= 0) {
-      up.cluster_split = 0;                         // clusters of this size cannot be placed: use the scratch path
-    } else {
-      attr[na].id = cudaLaunchAttributeClusterDimension;
-      attr[na].val.clusterDim.x = (unsigned)S; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
-      ++na;
-      grid = (int)std::min<long long>(up.total_tiles, cached) * S;
-    }
-  }
-  if (!up.cluster_split && up.split_k > 1 && up.ws_partials == nullptr)
-    return fail(MP_ERR_WORKSPACE, "internal: split-K without scratch");
-  cfg.gridDim = dim3((unsigned)grid);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = na;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
   MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tx, ty0, ty1, up));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
@@ -365,15 +325,6 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.bias = p.bias;
   up.out_bf16 = p.out_bf16;
 
-  // Split-K through a cluster (distributed shared memory) when the slice count is a legal cluster
-  // size and every CTA's share of the tile's columns has a shape the exchange code handles.
-  {
-    bool ok = g_use_cluster && up.num_regions == 1 && (S == 2 || S == 4 || S == 8) && l.bn % S == 0;
-    const int cw = ok ? l.bn / S : 0;
-    ok = ok && cw % 16 == 0;    // narrower shares gain nothing over the scratch path
-    up.cluster_split = ok ? 1 : 0;
-  }
-  // The scratch is still set up: the launch falls back to it if clusters of S CTAs cannot be placed.
   if (S > 1) {
     size_t cb = 0;
     const size_t need = umma_workspace_bytes(p, l, &cb);
@@ -404,10 +355,11 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   }
 
   const long long units = (long long)up.total_tiles * up.split_k;
-  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 7) + 16 + 1024;
-  if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16>(*d, 0, tx, ty0, ty1, up, units, smem, stream);
-  if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32>(*d, 1, tx, ty0, ty1, up, units, smem, stream);
-  return launch_umma_t<KIND_I8, EPI_SCALED>(*d, 2, tx, ty0, ty1, up, units, smem, stream);
+  const int grid = (int)std::min<long long>(units, d->sms);
+  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024;
+  if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
+  if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32>(*d, 1, tx, ty0, ty1, up, grid, smem, stream);
+  return launch_umma_t<KIND_I8, EPI_SCALED>(*d, 2, tx, ty0, ty1, up, grid, smem, stream);
 }
 
 // CUDA-core path (FP32 always; FP16 / INT8 when TMA's alignment rules are not met).

@@ -18,8 +18,6 @@ enum : int {
   MP_DEV_TIMEOUT_EPILOGUE = 104,   // epilogue waited too long for a finished accumulator
   MP_DEV_TIMEOUT_DRAIN = 105,      // teardown waited too long for copies in flight
   MP_DEV_BAD_CONFIG = 106,
-  MP_DEV_TIMEOUT_CLUSTER_EXPORT = 107,   // waited too long for the cluster's partial tiles
-  MP_DEV_TIMEOUT_CLUSTER_READS = 108,    // waited too long for the cluster to finish reading this CTA's tile
 };
 
 static constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
@@ -90,71 +88,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
       }
     }
   }
-}
-
-// ----------------------------------------------------------------------------- thread-block clusters
-// Used by the split-K path: the CTAs that share an output tile form one cluster and exchange their
-// partial accumulators through distributed shared memory instead of a round trip through L2.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Hardware cluster barrier; every thread of every CTA of the cluster must call it.
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
-__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ uint4 ld_cluster_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared::cluster.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint2 ld_cluster_v2(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared::cluster.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr) : "memory");
-  return v;
-}
-// arrive (release at cluster scope) on an mbarrier that may live in another CTA of the cluster
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-// Bounded wait with cluster-scope acquire (see mbar_wait).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  unsigned long long t0 = 0;
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((it & 0xffu) == 0) {
-      const unsigned long long now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (now - t0 > kWaitLimitNs) {
-        if (status != nullptr) atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 // ----------------------------------------------------------------------------- TMA

@@ -71,8 +71,6 @@ struct UmmaParams {
   int stage_bytes;    // kc * (kXTileBytes + bn_max * kRowBytes)
   int group_p;        // raster: tiles are walked in groups of `group_p` rows of tiles
   int prefetch_kb;    // K blocks of a CTA's first unit to prefetch into L2 before the dependency wait
-  int cluster_split;  // 1: the split_k CTAs of a tile form one cluster (launched with cluster size split_k)
-                      // and reduce through distributed shared memory; the scratch is not used
   void* out;
   long long out_stride_p, out_stride_q;   // element strides of `out` along P and Q
   float alpha, beta;
@@ -280,16 +278,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   const uint32_t smem_base = smem_u32(smem);
   const int stages = p.stages;
   const uint32_t bar_base = smem_base + (uint32_t)stages * (uint32_t)p.stage_bytes;
-  // barrier slots (8 bytes each): full[stages] | empty[stages] | tfull[2] | tempty[2] | tmem slot |
-  // xready | rdone (cluster split-K: partial tiles exported / this CTA's tile read by all)
+  // barrier slots (8 bytes each): full[stages] | empty[stages] | tfull[2] | tempty[2] | tmem slot
   auto full_bar = [&](int s) { return bar_base + 8u * (uint32_t)s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (uint32_t)(stages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * stages + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * stages + 2 + b); };
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4));
-  const uint32_t xready_bar = bar_base + 8u * (uint32_t)(2 * stages + 5);
-  const uint32_t rdone_bar = bar_base + 8u * (uint32_t)(2 * stages + 6);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -305,18 +300,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), 4);
     }
-    // one arrival per epilogue warp of every CTA of the cluster
-    mbar_init(xready_bar, 4u * (uint32_t)p.split_k);
-    mbar_init(rdone_bar, 4u * (uint32_t)p.split_k);
     mbar_fence_init();
     tma_prefetch_desc(&tmX);
     tma_prefetch_desc(&tmY0);
     if (p.num_regions == 2) tma_prefetch_desc(&tmY1);
-  }
-  // peers arrive on this CTA's barriers: they must see them initialised
-  if (p.cluster_split) {
-    __syncthreads();
-    cluster_sync_all();
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
@@ -326,8 +313,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int unit_first = (int)blockIdx.x;
-  const int unit_stride = (int)gridDim.x;
 
   // Programmatic dependent launch: everything above touched only this CTA's shared memory, TMEM
   // and kernel parameters, so it may overlap the tail of the previous kernel in the stream.  Let
@@ -345,8 +330,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (lane == 0) {
       // While the previous kernel drains, pull the first unit's operands towards L2 (a hint only;
       // whatever the previous kernel still writes reaches L2 as well, so this cannot go stale).
-      if (unit_first < total_units) {
-        const UnitCoord u = decode_unit(p, unit_first);
+      if ((int)blockIdx.x < total_units) {
+        const UnitCoord u = decode_unit(p, (int)blockIdx.x);
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
         const int prow = u.tp * kUmmaM, qrow = r.q_begin + u.tq * r.bn;
@@ -367,7 +352,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       MP_TRACE_MARK(2);
       uint32_t it = 0;
       bool ok = true;
-      for (int w = unit_first; w < total_units && ok; w += unit_stride) {
+      for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x) {
         const UnitCoord u = decode_unit(p, w);
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
@@ -375,13 +360,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t y_off = (uint32_t)(p.kc * kXTileBytes);
         const int prow = u.tp * kUmmaM;
         const int qrow = r.q_begin + u.tq * r.bn;
-        if (p.cluster_split && w != unit_first) {
-          // the stage memory doubles as the exported partial tile of the previous unit: it may be
-          // refilled only after every CTA of the cluster has read it
-          const uint32_t prev_unit = (uint32_t)((w - unit_first) / unit_stride) - 1u;
-          if (!mbar_wait_cluster(rdone_bar, prev_unit & 1u, status, MP_DEV_TIMEOUT_CLUSTER_READS)) { ok = false; break; }
-          fence_proxy_async_smem();
-        }
         for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
           const int s = (int)(it % (uint32_t)stages);
           const uint32_t ph = (it / (uint32_t)stages) & 1u;
@@ -417,7 +395,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0, ui = 0;
       bool ok = true;
-      for (int w = unit_first; w < total_units && ok; w += unit_stride, ++ui) {
+      for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
         const UnitCoord u = decode_unit(p, w);
         const Region& r = p.reg[u.region];
         const uint32_t buf = ui & 1u;
@@ -427,7 +405,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t d_tmem = tmem_base + buf * (uint32_t)kMaxBN;
         const uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kUmmaM, (uint32_t)r.bn)
                                                  : umma_idesc(1u, 0u, kUmmaM, (uint32_t)r.bn);
-        const int y_tile_bytes = r.bn * kRowBytes;
         for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
           const int s = (int)(it % (uint32_t)stages);
           const uint32_t ph = (it / (uint32_t)stages) & 1u;
@@ -442,7 +419,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
               const uint64_t ad = umma_smem_desc_sw128(a_addr + (uint32_t)(c * kXTileBytes) + 32u * kk);
-              const uint64_t bd = umma_smem_desc_sw128(b_addr + (uint32_t)(c * y_tile_bytes) + 32u * kk);
+              const uint64_t bd = umma_smem_desc_sw128(b_addr + (uint32_t)(c * r.bn * kRowBytes) + 32u * kk);
               const uint32_t acc = (kb > u.kb0 || c > 0 || kk > 0) ? 1u : 0u;
               if constexpr (KIND == KIND_I8) umma_i8(d_tmem, ad, bd, idesc, acc);
               else umma_f16(d_tmem, ad, bd, idesc, acc);
@@ -459,7 +436,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     uint32_t ui = 0;
     bool ok = true;
     griddep_wait();
-    for (int w = unit_first; w < total_units && ok; w += unit_stride, ++ui) {
+    for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
       const UnitCoord u = decode_unit(p, w);
       const Region& r = p.reg[u.region];
       const uint32_t buf = ui & 1u;
@@ -483,83 +460,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));
-      } else if (p.cluster_split) {
-        // ---- split-K inside a cluster.  Every CTA exports its raw accumulators to its own shared
-        // memory as [column chunk][row][cw words] (cw = bn / split_k); CTA `rank` then sums chunk
-        // `rank` of all exports in slice order 0..S-1 (same fixed order as the scratch path, hence
-        // the same bits) and writes those columns of C.
-        const int S = p.split_k;
-        const int cw = r.bn / S;                        // >= 2: bn is a multiple of 16, S <= 8
-        const uint32_t rank = cluster_ctarank();
-        for (int c0 = 0; c0 < r.bn; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(t_addr + (uint32_t)c0, v);
-          tmem_ld_wait();
-          if (cw >= 16) {
-            const uint32_t dst = smem_base + 4u * (uint32_t)(((c0 / cw) * kUmmaM + row_in_tile) * cw + (c0 % cw));
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16u * j), "r"(v[4 * j]), "r"(v[4 * j + 1]),
-                           "r"(v[4 * j + 2]), "r"(v[4 * j + 3]) : "memory");
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; j += 2) {           // cw in {2,4,8}: pairs never straddle a chunk
-              const int c = c0 + j;
-              const uint32_t dst = smem_base + 4u * (uint32_t)(((c / cw) * kUmmaM + row_in_tile) * cw + (c % cw));
-              asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(dst), "r"(v[j]), "r"(v[j + 1]) : "memory");
-            }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar((int)buf));            // TMEM buffer is free again
-        // one lane per peer: the S release-arrives travel in parallel instead of one after another
-        if (lane < S) mbar_arrive_cluster(cluster_map(xready_bar, (uint32_t)lane));
-        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(6);
-        if (!mbar_wait_cluster(xready_bar, ui & 1u, status, MP_DEV_TIMEOUT_CLUSTER_EXPORT)) { ok = false; break; }
-        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(7);
-        const uint32_t my_chunk = smem_base + 4u * (uint32_t)(((int)rank * kUmmaM + row_in_tile) * cw);
-        const int q_chunk0 = q_tile0 + (int)rank * cw;
-        for (int g0 = 0; g0 < cw; g0 += 16) {
-          const int gw = min(16, cw - g0);              // 2, 4, 8 or 16 columns in this pass
-          uint32_t v[16];
-          for (int s0 = 0; s0 < S; s0 += 4) {
-            uint32_t x[4][16];
-#pragma unroll
-            for (int ds = 0; ds < 4; ++ds)
-              if (s0 + ds < S) {
-                const uint32_t src = cluster_map(my_chunk + 4u * (uint32_t)g0, (uint32_t)(s0 + ds));
-                if (gw == 2) {
-                  const uint2 t = ld_cluster_v2(src);
-                  x[ds][0] = t.x; x[ds][1] = t.y;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 4; ++j)
-                    if (4 * j < gw) {
-                      const uint4 t = ld_cluster_v4(src + 16u * j);
-                      x[ds][4 * j] = t.x; x[ds][4 * j + 1] = t.y; x[ds][4 * j + 2] = t.z; x[ds][4 * j + 3] = t.w;
-                    }
-                }
-              }
-#pragma unroll
-            for (int ds = 0; ds < 4; ++ds)
-              if (s0 + ds < S) {
-#pragma unroll
-                for (int e = 0; e < 16; ++e)
-                  if (e < gw) {
-                    if (s0 + ds == 0) v[e] = x[ds][e];
-                    else if constexpr (KIND == KIND_I8) v[e] = (uint32_t)((int)v[e] + (int)x[ds][e]);
-                    else v[e] = __float_as_uint(__fadd_rn(__uint_as_float(v[e]), __uint_as_float(x[ds][e])));
-                  }
-              }
-          }
-          // store_chunk16 takes the vector path for a full, aligned run of 16 and the scalar
-          // path otherwise; columns past gw are cut off through its q_end argument
-          store_chunk16<EPI>(p, v, pi, q_chunk0 + g0, min(q_end, q_chunk0 + g0 + gw));
-        }
-        __syncwarp();
-        if (lane < S) mbar_arrive_cluster(cluster_map(rdone_bar, (uint32_t)lane));
-        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(8);
       } else {
         // park this slice's raw accumulators: [tile][slice][row][column]; every thread owns a
         // contiguous run of its row and moves it with 16-byte accesses
@@ -591,14 +491,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const uint32_t* base = p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words +
                                  (size_t)row_in_tile * r.bn;
           // 32 columns per pass (bn is a multiple of 16: the last pass may be half wide); the loads
-          // of two slices are in flight before the first is consumed
+          // of up to four slices are all in flight before the first is consumed
           for (int c0 = 0; c0 < r.bn; c0 += 32) {
             const int nq = (r.bn - c0 >= 32) ? 8 : 4;      // 16-byte words in this pass
             uint32_t v[32];
-            for (int s0 = 0; s0 < p.split_k; s0 += 2) {
-              uint4 x[2][8];
+            for (int s0 = 0; s0 < p.split_k; s0 += 4) {
+              uint4 x[4][8];
 #pragma unroll
-              for (int ds = 0; ds < 2; ++ds)
+              for (int ds = 0; ds < 4; ++ds)
                 if (s0 + ds < p.split_k) {
                   const uint4* ps = reinterpret_cast<const uint4*>(base + (size_t)(s0 + ds) * p.ws_tile_words + c0);
 #pragma unroll
@@ -606,7 +506,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     if (j < nq) x[ds][j] = __ldcg(ps + j);
                 }
 #pragma unroll
-              for (int ds = 0; ds < 2; ++ds)
+              for (int ds = 0; ds < 4; ++ds)
                 if (s0 + ds < p.split_k) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j)
@@ -637,9 +537,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  // no CTA of a cluster may retire while a peer can still read its shared memory or arrive on its
-  // barriers; every wait above is bounded, so every thread of the cluster gets here
-  if (p.cluster_split) cluster_sync_all();
   if (threadIdx.x == 0) MP_TRACE_MARK(9);
   if (warp == 1) {
     __syncwarp();
