@@ -304,6 +304,12 @@ TileCfg tile_cfg(int dtype, int pid) {
       base = 9; split = true;      // 64x16 class
     } else if (pid == 44) {
       base = 37; split = true;     // 64x32 class
+    } else if (pid >= 1000 && pid < 1064) {
+      // library-native tiles (no counterpart in the reference's pid space): pid = 1000 + 32*orient + bn/16
+      const int bn = ((pid - 1000) & 31) * 16;
+      if (bn < 16 || bn > 256) return c;
+      c.valid = true; c.orient = (pid - 1000) >> 5; c.bn = bn; c.align = 8; c.split_capable = true;
+      return c;
     } else if (in_list(kFp16Explicit, 12, pid)) {
       c.valid = true; c.orient = 0; c.bn = 16; c.align = 8; c.split_capable = true;
       return c;
@@ -345,8 +351,9 @@ namespace {
 // pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
 struct PidMeta { TileCfg cfg; int meta[3]; };
 struct MetaTables {
-  PidMeta fp16[440], int8[46], fp32[40];
+  PidMeta fp16[440], int8[46], fp32[40], native[64];
   MetaTables() {
+    for (int p = 0; p < 64; ++p) { native[p].cfg = tile_cfg(MP_FP16, 1000 + p); pid_tile_meta(MP_FP16, 1000 + p, native[p].meta); }
     for (int p = 0; p < 440; ++p) { fp16[p].cfg = tile_cfg(MP_FP16, p); pid_tile_meta(MP_FP16, p, fp16[p].meta); }
     for (int p = 0; p < 46; ++p) { int8[p].cfg = tile_cfg(MP_INT8, p); pid_tile_meta(MP_INT8, p, int8[p].meta); }
     for (int p = 0; p < 40; ++p) { fp32[p].cfg = tile_cfg(MP_FP32, p); pid_tile_meta(MP_FP32, p, fp32[p].meta); }
@@ -355,7 +362,10 @@ struct MetaTables {
 const PidMeta* pid_meta(int dtype, int pid) {
   static const MetaTables t;
   if (pid < 0) return nullptr;
-  if (dtype == MP_FP16) return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
+  if (dtype == MP_FP16) {
+    if (pid >= 1000 && pid < 1064) return t.native[pid - 1000].cfg.valid ? &t.native[pid - 1000] : nullptr;
+    return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
+  }
   if (dtype == MP_INT8) return pid < 46 ? &t.int8[pid] : nullptr;
   if (dtype == MP_FP32) return pid < 40 ? &t.fp32[pid] : nullptr;
   return nullptr;
@@ -403,6 +413,10 @@ namespace {
 // Measured decode plans for Linear(M,N,K) shapes: same record layout as the reference's
 // generated/fp16/rcc/llm_decode_selector.inc (m, n, k, pid, split_k); values measured on B200.
 struct DecodeEntry { int m, n, k, pid, split_k; };
+// Measured plans for RCC shapes, bucketed over the dynamic dimension: a row applies when
+// m_lo <= m <= m_hi, n_lo <= n <= n_hi, k matches and m has the row's alignment class
+// (0 any, 1 m % 8 == 0, 2 m % 8 != 0: C columns are then not 16-byte aligned).
+struct PlanRow { int m_lo, m_hi, n_lo, n_hi, k, align_class, pid, split_k; float ms; };
 #include "generated/mp_decode_selector.inc"
 
 inline void consider(mp_plan& best, int pattern, int pid, int split_k, int split_n, float ms, float margin) {
@@ -449,6 +463,16 @@ mp_plan select_fp16(int m, int n, int k, const LiveFlags& lf) {
                  cost_ms(MP_FP16, d.pid, S, m, n, k), e.gen_margin);
         matched = true;
       }
+    }
+    for (int i = 0; i < kMeasuredPlanCount; ++i) {
+      const PlanRow& r = kMeasuredPlans[i];
+      if (r.k != k || m < r.m_lo || m > r.m_hi || n < r.n_lo || n > r.n_hi) continue;
+      if ((r.align_class == 1 && m % 8 != 0) || (r.align_class == 2 && m % 8 == 0)) continue;
+      const int S = std::max(1, r.split_k);
+      const TileCfg c = tile_cfg(MP_FP16, r.pid);
+      if (!c.valid || k % c.align != 0) continue;
+      consider(best, S > 1 ? MP_PATTERN_SPLITK : MP_PATTERN_SINGLE, r.pid, S, 0, r.ms, e.gen_margin);
+      matched = true;
     }
     if (matched && (lf.decode_strict || lf.gen_strict)) return best;
   }

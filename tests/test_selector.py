@@ -32,7 +32,9 @@ def test_pid_tables_follow_the_reference_contract(api):
             api.pid_info(dt, bad)
 
 
-def test_plan_is_argmin_of_cost_under_alignment(api):
+def test_plan_is_argmin_of_cost_under_alignment(api, monkeypatch):
+    # the cost-model path proper: measured plans off (MOONPOLY_ENABLE_GENERATED_SELECTOR, re-read per call)
+    monkeypatch.setenv("MOONPOLY_ENABLE_GENERATED_SELECTOR", "0")
     for (m, n, k) in [(1, 4096, 4096), (4096, 4096, 4096), (512, 11008, 4096), (37, 1000, 520), (8, 1024, 8190)]:
         plan = api.select_plan(api.MP_FP16, m, n, k)
         if plan.pattern == 1:
@@ -50,7 +52,33 @@ def test_plan_is_argmin_of_cost_under_alignment(api):
             assert k % api.pid_info(api.MP_FP16, plan.pid)[1] == 0
 
 
+def test_measured_plan_table(api, monkeypatch):
+    """Bucketed measured plans short-circuit the cost model (MOONPOLY_LLM_DECODE_SELECTOR_STRICT=1 by
+    default, as the reference's decode selector does) and name library-native tiles (pid >= 1000)."""
+    for (m, n, k) in [(1, 4096, 4096), (3, 4096, 4096), (4096, 5, 4096), (600, 4096, 4096), (599, 4096, 4096)]:
+        plan = api.select_plan(api.MP_FP16, m, n, k)
+        assert 1000 <= plan.pid < 1064, (m, n, k, plan)
+        tile, align = api.pid_info(api.MP_FP16, plan.pid)
+        assert align == 8 and 128 in tile[:2]
+        assert plan.estimated_ms > 0
+    # aligned and unaligned m land in different rows of the same bucket
+    a = api.select_plan(api.MP_FP16, 1024, 4096, 4096)
+    b = api.select_plan(api.MP_FP16, 1023, 4096, 4096)
+    assert (a.pid, a.split_k) != (b.pid, b.split_k) or a.estimated_ms != b.estimated_ms
+    # a shape outside the table goes through the cost model
+    assert api.select_plan(api.MP_FP16, 500, 3000, 4096).pid < 1000
+    # switching the table off is honoured on the next call
+    monkeypatch.setenv("MOONPOLY_ENABLE_GENERATED_SELECTOR", "0")
+    assert api.select_plan(api.MP_FP16, 1, 4096, 4096).pid < 1000
+    monkeypatch.delenv("MOONPOLY_ENABLE_GENERATED_SELECTOR")
+    # non-strict: the measured plan competes with the cost model instead of short-circuiting it
+    monkeypatch.setenv("MOONPOLY_LLM_DECODE_SELECTOR_STRICT", "0")
+    p = api.select_plan(api.MP_FP16, 1, 4096, 4096)
+    assert p.estimated_ms <= api.select_plan(api.MP_FP16, 1, 4096, 4096).estimated_ms
+
+
 def test_env_flags(api, monkeypatch):
+    monkeypatch.setenv("MOONPOLY_ENABLE_GENERATED_SELECTOR", "0")
     m, n, k = 8, 4096, 8192
     assert api.select_plan(api.MP_FP16, m, n, k).pattern == 3
     monkeypatch.setenv("MOONPOLY_ENABLE_PATTERN3", "0")          # re-read on every call
@@ -76,6 +104,7 @@ def test_env_flags(api, monkeypatch):
 
 
 def test_pattern2_gate(api, monkeypatch):
+    monkeypatch.setenv("MOONPOLY_ENABLE_GENERATED_SELECTOR", "0")
     # tail of n % 128 within 25 % of a tile opens the twin plan; it must still win by the margin
     m, k = 4096, 4096
     monkeypatch.setenv("MOONPOLY_PATTERN2_MARGIN", "10.0")       # let it win whenever the gate opens
