@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "../../include/moonpoly_abi.h"
+#include "mp_gemv.cuh"
 #include "mp_select.h"
 #include "mp_simt_gemm.cuh"
 #include "mp_umma_gemm.cuh"
@@ -428,6 +429,57 @@ int run_simt(const Problem& p, int ti, int tj, int split_k, void* workspace, siz
   return launch_simt_t<int8_t, SEPI_SCALED, 64, 64>(sp, stream);
 }
 
+// Skinny FP16 path: one side of the problem has at most 8 rows; the other operand is streamed once.
+template <int T>
+int launch_gemv_t(const GemvParams& gp, cudaStream_t stream) {
+  const int rows_per_cta = kGemvWarps * kGemvRowsPerWarp;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((gp.R + rows_per_cta - 1) / rows_per_cta));
+  cfg.blockDim = dim3(kGemvWarps * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_f16_kernel<T>, gp));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
+bool gemv_compatible(const Problem& p) {
+  return p.dtype == MP_FP16 && p.epi == EPI_F16 && std::min(p.m, p.n) <= 8 && std::min(p.m, p.n) >= 1 && p.k >= 8 &&
+         tma_compatible(p);      // same rule: 16-byte aligned rows
+}
+
+int run_gemv(const Problem& p, cudaStream_t stream) {
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+  GemvParams gp{};
+  const bool narrow_is_a = p.m <= p.n;          // direct mapping: few rows of A against the rows of B
+  gp.W = reinterpret_cast<const __half*>(narrow_is_a ? p.B : p.A);
+  gp.ldw = narrow_is_a ? p.ldb : p.lda;
+  gp.X = reinterpret_cast<const __half*>(narrow_is_a ? p.A : p.B);
+  gp.ldx = narrow_is_a ? p.lda : p.ldb;
+  gp.R = narrow_is_a ? p.n : p.m;
+  gp.T = narrow_is_a ? p.m : p.n;
+  gp.K = p.k;
+  gp.out = reinterpret_cast<__half*>(p.C);
+  gp.stride_r = narrow_is_a ? p.c_stride_n : p.c_stride_m;
+  gp.stride_t = narrow_is_a ? p.c_stride_m : p.c_stride_n;
+  gp.alpha = p.alpha; gp.beta = p.beta;
+  switch (gp.T) {
+    case 1: return launch_gemv_t<1>(gp, stream);
+    case 2: return launch_gemv_t<2>(gp, stream);
+    case 3: return launch_gemv_t<3>(gp, stream);
+    case 4: return launch_gemv_t<4>(gp, stream);
+    case 5: return launch_gemv_t<5>(gp, stream);
+    case 6: return launch_gemv_t<6>(gp, stream);
+    case 7: return launch_gemv_t<7>(gp, stream);
+    default: return launch_gemv_t<8>(gp, stream);
+  }
+}
+
 int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {
   if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
     return fail(MP_ERR_INVALID_ARG, "Unsupported data type %d", dtype);
@@ -457,6 +509,13 @@ int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, c
   if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, p.dtype);
   if (p.dtype == MP_FP32) return run_simt(p, c.ti, c.tj, split_k, ws, ws_bytes, stream);
   if (!tma_compatible(p)) return run_simt(p, 64, 64, split_k, ws, ws_bytes, stream);
+  if (c.orient == 2) {          // the skinny streaming kernel; shapes it does not cover take the 128x16 tile
+    if (gemv_compatible(p)) return run_gemv(p, stream);
+    Launch lf;
+    lf.orient = p.m <= p.n ? 1 : 0; lf.bn = 16; lf.split_k = std::max(1, split_k);
+    lf.workspace = ws; lf.workspace_bytes = ws_bytes;
+    return run_umma(p, lf, stream);
+  }
   Launch l;
   l.orient = c.orient; l.bn = c.bn; l.split_k = std::max(1, split_k);
   l.workspace = ws; l.workspace_bytes = ws_bytes;
@@ -566,6 +625,11 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
                      const void* B, void* C, float alpha, float beta, void* stream) {
   if (int rc = check_rcc_args(dtype, m, n, k, A, B, C)) return rc;
   if (dtype == MP_FP32) return fail(MP_ERR_UNSUPPORTED, "explicit tiles exist for the tensor-core dtypes only");
+  if (orient == 2) {            // the skinny streaming kernel (bn, kc, split_k unused)
+    const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+    if (!gemv_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the skinny kernel needs FP16, min(m,n) <= 8 and 16-byte aligned rows");
+    return run_gemv(pg, reinterpret_cast<cudaStream_t>(stream));
+  }
   if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0 || (kc != 0 && kc != 1 && kc != 2 && kc != 4))
     return fail(MP_ERR_INVALID_ARG, "bad tile: orient=%d bn=%d kc=%d", orient, bn, kc);
   if (m == 0 || n == 0) return MP_OK;

@@ -313,3 +313,26 @@ def test_scaled_mm_unaligned_k(api, oracle):
     out = api.scaled_int8_mm(dev(a), dev(b).t(), dev(sa), dev(sb)).cpu().numpy()
     assert np.array_equal(out, oracle.scaled_mm_i8(a, b, sa, sb))
 
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (2, 300, 520), (5, 1000, 1024), (8, 64, 8192), (777, 3, 2048),
+                                    (4096, 1, 4096)])
+def test_fp16_skinny_kernel_vs_oracle(api, oracle, m, n, k):
+    """pid 1100: the streaming kernel for problems with at most 8 rows on one side (both mappings)."""
+    a = rng.normal(23, 0, (m, k), 0.05)
+    b = rng.normal(23, 1, (n, k), 0.05)
+    c0 = rng.normal(23, 2, (n, m), 1.0)
+    ref = oracle.gemm_f16_rcc(a, b)
+    close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1100, 1).cpu().numpy(), ref)
+    ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
+    close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1100, 1, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
+    ai = rng.small_ints(24, 0, (m, k), lo=-1, hi=1)
+    bi = rng.small_ints(24, 1, (n, k))
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T.astype(np.float16)
+    assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), 1100, 1).cpu().numpy(), exact)
+
+
+def test_fp16_skinny_pid_on_wide_problem_uses_tensor_tiles(api, oracle):
+    a = rng.normal(25, 0, (40, 512), 0.05)
+    b = rng.normal(25, 1, (200, 512), 0.05)
+    close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1100, 1).cpu().numpy(), oracle.gemm_f16_rcc(a, b))
