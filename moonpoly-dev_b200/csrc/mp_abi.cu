@@ -13,6 +13,7 @@
 
 #include "../../include/moonpoly_abi.h"
 #include "mp_gemv.cuh"
+#include "mp_stream_mma.cuh"
 #include "mp_select.h"
 #include "mp_simt_gemm.cuh"
 #include "mp_umma_gemm.cuh"
@@ -480,6 +481,53 @@ int run_gemv(const Problem& p, cudaStream_t stream) {
   }
 }
 
+// Streaming warp-MMA path: one side of the problem has at most 64 rows; the other operand is streamed once.
+template <int NT, int UNROLL, int MINB>
+int launch_stream_t(const StreamParams& sp, int sms, cudaStream_t stream) {
+  // a whole multiple of the SM count when the rows allow it, else one CTA per 8 rows
+  const int per_sm = std::min(MINB, sp.R / (8 * sms));
+  const int grid = per_sm >= 1 ? per_sm * sms : std::max(1, (sp.R + 7) / 8);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kStreamWarps * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, stream_mma_f16_kernel<NT, UNROLL, MINB>, sp));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
+bool stream_compatible(const Problem& p) {
+  return p.dtype == MP_FP16 && p.epi == EPI_F16 && std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 8 &&
+         tma_compatible(p);      // same rule: 16-byte aligned rows
+}
+
+int run_stream(const Problem& p, cudaStream_t stream) {
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+  StreamParams sp{};
+  const bool narrow_is_a = p.m <= p.n;
+  sp.W = reinterpret_cast<const __half*>(narrow_is_a ? p.B : p.A);
+  sp.ldw = narrow_is_a ? p.ldb : p.lda;
+  sp.X = reinterpret_cast<const __half*>(narrow_is_a ? p.A : p.B);
+  sp.ldx = narrow_is_a ? p.lda : p.ldb;
+  sp.R = narrow_is_a ? p.n : p.m;
+  sp.T = narrow_is_a ? p.m : p.n;
+  sp.K = p.k;
+  sp.out = reinterpret_cast<__half*>(p.C);
+  sp.stride_r = narrow_is_a ? p.c_stride_n : p.c_stride_m;
+  sp.stride_t = narrow_is_a ? p.c_stride_m : p.c_stride_n;
+  sp.alpha = p.alpha; sp.beta = p.beta;
+  if (sp.T <= 8) return launch_stream_t<1, 8, 2>(sp, d->sms, stream);
+  if (sp.T <= 16) return launch_stream_t<2, 8, 2>(sp, d->sms, stream);
+  if (sp.T <= 32) return launch_stream_t<4, 8, 2>(sp, d->sms, stream);
+  return launch_stream_t<8, 4, 2>(sp, d->sms, stream);
+}
+
 int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {
   if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
     return fail(MP_ERR_INVALID_ARG, "Unsupported data type %d", dtype);
@@ -513,6 +561,14 @@ int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, c
     if (gemv_compatible(p)) return run_gemv(p, stream);
     Launch lf;
     lf.orient = p.m <= p.n ? 1 : 0; lf.bn = 16; lf.split_k = std::max(1, split_k);
+    lf.workspace = ws; lf.workspace_bytes = ws_bytes;
+    return run_umma(p, lf, stream);
+  }
+  if (c.orient == 3) {          // the streaming warp-MMA kernel, with the same fallback
+    if (stream_compatible(p)) return run_stream(p, stream);
+    Launch lf;
+    lf.orient = p.m <= p.n ? 1 : 0; lf.bn = std::min(64, std::max(16, (std::min(p.m, p.n) + 15) / 16 * 16));
+    lf.split_k = std::max(1, split_k);
     lf.workspace = ws; lf.workspace_bytes = ws_bytes;
     return run_umma(p, lf, stream);
   }
@@ -629,6 +685,11 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
     const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
     if (!gemv_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the skinny kernel needs FP16, min(m,n) <= 8 and 16-byte aligned rows");
     return run_gemv(pg, reinterpret_cast<cudaStream_t>(stream));
+  }
+  if (orient == 3) {            // the streaming warp-MMA kernel (bn, kc, split_k unused)
+    const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+    if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16, min(m,n) <= 64 and 16-byte aligned rows");
+    return run_stream(pg, reinterpret_cast<cudaStream_t>(stream));
   }
   if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0 || (kc != 0 && kc != 1 && kc != 2 && kc != 4))
     return fail(MP_ERR_INVALID_ARG, "bad tile: orient=%d bn=%d kc=%d", orient, bn, kc);

@@ -308,6 +308,10 @@ TileCfg tile_cfg(int dtype, int pid) {
       // library-native skinny streaming kernel (min(m,n) <= 8): orient 2, no tile in the UMMA sense
       c.valid = true; c.orient = 2; c.bn = 16; c.align = 8; c.split_capable = false;
       return c;
+    } else if (pid == 1101) {
+      // library-native streaming warp-MMA kernel (min(m,n) <= 64): orient 3
+      c.valid = true; c.orient = 3; c.bn = 64; c.align = 8; c.split_capable = false;
+      return c;
     } else if (pid >= 1000 && pid < 1064) {
       // library-native tiles (no counterpart in the reference's pid space): pid = 1000 + 32*orient + bn/16
       const int bn = ((pid - 1000) & 31) * 16;
@@ -346,6 +350,7 @@ void pid_tile_meta(int dtype, int pid, int out[3]) {
   const TileCfg c = tile_cfg(dtype, pid);
   if (!c.valid) { out[0] = out[1] = out[2] = 0; return; }
   if (dtype == MP_FP32) { out[0] = c.tj; out[1] = c.ti; out[2] = 16; return; }
+  if (c.orient == 3) { out[0] = 16; out[1] = 64; out[2] = 32; return; }     // streaming kernel: 16 streamed rows per CTA x up to 64 rows
   if (c.orient == 2) { out[0] = 16; out[1] = 8; out[2] = 1024; return; }   // skinny kernel: 16 streamed rows per CTA x up to 8 rows
   out[0] = c.orient == 0 ? c.bn : 128;    // pm: tile over RCC n
   out[1] = c.orient == 0 ? 128 : c.bn;    // pn: tile over RCC m
@@ -356,9 +361,10 @@ namespace {
 // pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
 struct PidMeta { TileCfg cfg; int meta[3]; };
 struct MetaTables {
-  PidMeta fp16[440], int8[46], fp32[40], native[64], skinny;
+  PidMeta fp16[440], int8[46], fp32[40], native[64], skinny, streaming;
   MetaTables() {
     skinny.cfg = tile_cfg(MP_FP16, 1100); pid_tile_meta(MP_FP16, 1100, skinny.meta);
+    streaming.cfg = tile_cfg(MP_FP16, 1101); pid_tile_meta(MP_FP16, 1101, streaming.meta);
     for (int p = 0; p < 64; ++p) { native[p].cfg = tile_cfg(MP_FP16, 1000 + p); pid_tile_meta(MP_FP16, 1000 + p, native[p].meta); }
     for (int p = 0; p < 440; ++p) { fp16[p].cfg = tile_cfg(MP_FP16, p); pid_tile_meta(MP_FP16, p, fp16[p].meta); }
     for (int p = 0; p < 46; ++p) { int8[p].cfg = tile_cfg(MP_INT8, p); pid_tile_meta(MP_INT8, p, int8[p].meta); }
@@ -370,6 +376,7 @@ const PidMeta* pid_meta(int dtype, int pid) {
   if (pid < 0) return nullptr;
   if (dtype == MP_FP16) {
     if (pid == 1100) return &t.skinny;
+    if (pid == 1101) return &t.streaming;
     if (pid >= 1000 && pid < 1064) return t.native[pid - 1000].cfg.valid ? &t.native[pid - 1000] : nullptr;
     return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
   }

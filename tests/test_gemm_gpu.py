@@ -336,3 +336,27 @@ def test_fp16_skinny_pid_on_wide_problem_uses_tensor_tiles(api, oracle):
     a = rng.normal(25, 0, (40, 512), 0.05)
     b = rng.normal(25, 1, (200, 512), 0.05)
     close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1100, 1).cpu().numpy(), oracle.gemm_f16_rcc(a, b))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (2, 300, 520), (8, 1000, 1024), (9, 64, 8192), (16, 4096, 4096),
+                                    (31, 513, 2048), (64, 1024, 4096), (777, 3, 2048), (4096, 24, 4096),
+                                    (130, 57, 72)])
+def test_fp16_streaming_kernel_vs_oracle(api, oracle, m, n, k):
+    """pid 1101: the streaming warp-MMA kernel for problems with at most 64 rows on one side (both mappings)."""
+    a = rng.normal(26, 0, (m, k), 0.05)
+    b = rng.normal(26, 1, (n, k), 0.05)
+    c0 = rng.normal(26, 2, (n, m), 1.0)
+    ref = oracle.gemm_f16_rcc(a, b)
+    close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1101, 1).cpu().numpy(), ref)
+    ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
+    close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1101, 1, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
+    ai = rng.small_ints(27, 0, (m, k), lo=-1, hi=1)
+    bi = rng.small_ints(27, 1, (n, k))
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T.astype(np.float16)
+    assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1).cpu().numpy(), exact)
+
+
+def test_fp16_streaming_pid_on_wide_problem_uses_tensor_tiles(api, oracle):
+    a = rng.normal(28, 0, (100, 512), 0.05)
+    b = rng.normal(28, 1, (200, 512), 0.05)
+    close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1101, 1).cpu().numpy(), oracle.gemm_f16_rcc(a, b))
