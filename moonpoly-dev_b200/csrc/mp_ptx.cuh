@@ -90,6 +90,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   }
 }
 
+// Short bounded wait until a global counter reaches `target` (acquire semantics); running out of
+// time is not an error here, the caller just carries on without what it waited for.
+constexpr unsigned long long kHelpWaitNs = 50000ull;
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool counter_wait_ge_for(const unsigned* ctr, unsigned target, unsigned long long limit_ns) {
+  if (ld_acquire_u32(ctr) >= target) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (ld_acquire_u32(ctr) >= target) return true;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
+  }
+}
+
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");

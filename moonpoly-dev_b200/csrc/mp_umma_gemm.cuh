@@ -75,8 +75,8 @@ struct UmmaParams {
   long long out_stride_p, out_stride_q;   // element strides of `out` along P and Q
   float alpha, beta;
   int ialpha, ibeta;
-  uint32_t* ws_partials;   // [total_tiles][split_k][128 rows][bn of the tile's region] 32-bit words
-  unsigned* ws_counters;   // [total_tiles][4], zero on entry, left zero on exit
+  uint32_t* ws_partials;   // [total_tiles][split_k][bn_max / 4][128 rows] 16-byte words
+  unsigned* ws_counters;   // [total_tiles][4 quadrants][arrived, claimed, left, -], zero on entry, left zero on exit
   int ws_tile_words;       // bn_max * 128
   // scaled int8 matmul epilogue
   const float* scale_p; const float* scale_q;   // scales indexed along P / along Q
@@ -461,17 +461,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));
       } else {
-        // park this slice's raw accumulators: [tile][slice][row][column]; every thread owns a
-        // contiguous run of its row and moves it with 16-byte accesses
-        uint32_t* part = p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words +
-                         (size_t)row_in_tile * r.bn;
+        // park this slice's raw accumulators as [tile][slice][column / 4][row] 16-byte words: the 32
+        // lanes of a warp (32 consecutive rows) then touch 512 contiguous bytes per access, both here
+        // and in the reduction below (row-major scratch would scatter each access over 32 lines)
+        uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words) +
+                      row_in_tile;
         for (int c0 = 0; c0 < r.bn; c0 += 16) {
           uint32_t v[16];
           tmem_ld_x16(t_addr + (uint32_t)c0, v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            __stcg(reinterpret_cast<uint4*>(part + c0) + j, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+            __stcg(part + (size_t)((c0 >> 2) + j) * kUmmaM, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
         }
         tc_fence_before();
         __syncwarp();
@@ -479,31 +480,62 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(6);
         __threadfence();
         __syncwarp();
-        unsigned prev = 0;
-        unsigned* ctr = p.ws_counters + (size_t)u.tile * 4 + quad;
-        if (lane == 0) prev = atomicAdd(ctr, 1u);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
+        // Reduction of this quadrant of the tile.  Share i is the run of 16-column chunks
+        // [i*chunks/S, (i+1)*chunks/S).  The warp that arrives last (ticket S-1) knows all S slices are
+        // parked: it sums its own share at once and afterwards takes every share nobody has claimed.
+        // A warp that arrived earlier may help with the share of its ticket: it waits a short, bounded
+        // time for the last arrival and claims the share with an atomic OR; if the wait runs out it
+        // simply leaves, and the last arriver picks the share up.  Nothing therefore ever depends on
+        // a waiting warp (no deadlock when kernels of several streams compete for the SMs), and
+        // helping is only tried when all work units run concurrently (one unit per CTA).  Every column
+        // is summed in slice order s = 0..S-1 whoever sums it: results are bit-identical run to run.
+        unsigned* ctr = p.ws_counters + ((size_t)u.tile * 4 + quad) * 4;   // arrived, claimed mask, left, unused
+        unsigned ticket = 0;
+        if (lane == 0) ticket = atomicAdd(ctr, 1u);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
         if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(7);
-        if (prev == (unsigned)(p.split_k - 1)) {
-          // last slice to arrive for this quadrant of the tile: sum in slice order s = 0..S-1
-          // (fixed order => bit-identical results from run to run) and finish
-          __threadfence();
-          const uint32_t* base = p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words +
-                                 (size_t)row_in_tile * r.bn;
-          // 32 columns per pass (bn is a multiple of 16: the last pass may be half wide); the loads
-          // of up to four slices are all in flight before the first is consumed
-          for (int c0 = 0; c0 < r.bn; c0 += 32) {
-            const int nq = (r.bn - c0 >= 32) ? 8 : 4;      // 16-byte words in this pass
+        const int chunks = r.bn >> 4;
+        const bool last = ticket == (unsigned)(p.split_k - 1);
+        const unsigned all_shares = p.split_k >= 32 ? 0xffffffffu : ((1u << p.split_k) - 1u);
+        unsigned mine = 0;                      // shares this warp sums
+        if (last) {
+          mine = 1u << ticket;
+        } else if (total_units <= (int)gridDim.x && ((int)ticket + 1) * chunks / p.split_k > (int)ticket * chunks / p.split_k) {
+          unsigned got = 0;
+          if (lane == 0 && counter_wait_ge_for(ctr, (unsigned)p.split_k, kHelpWaitNs))
+            got = (atomicOr(ctr + 1, 1u << ticket) & (1u << ticket)) ? 0u : (1u << ticket);
+          mine = __shfl_sync(0xffffffffu, got, 0);
+        }
+        for (int round = 0; round < 2; ++round) {
+          if (round == 1) {
+            if (!last) break;
+            unsigned rest = 0;
+            if (lane == 0) rest = all_shares & ~atomicOr(ctr + 1, all_shares) & ~(1u << ticket);
+            mine = __shfl_sync(0xffffffffu, rest, 0);
+          }
+          if (mine != 0) __threadfence();
+          while (mine != 0) {
+            const int share = __ffs((int)mine) - 1;
+            mine &= mine - 1;
+            const int c_begin = (share * chunks / p.split_k) << 4;
+            const int c_end = ((share + 1) * chunks / p.split_k) << 4;
+          const uint4* base = reinterpret_cast<const uint4*>(p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words) +
+                              row_in_tile;
+          const size_t slice_words16 = (size_t)p.ws_tile_words >> 2;
+          // 32 columns per pass (the last pass may be half wide); the loads of up to four slices are
+          // all in flight before the first is consumed
+          for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+            const int nq = (c_end - c0 >= 32) ? 8 : 4;      // 16-byte words in this pass
             uint32_t v[32];
             for (int s0 = 0; s0 < p.split_k; s0 += 4) {
               uint4 x[4][8];
 #pragma unroll
               for (int ds = 0; ds < 4; ++ds)
                 if (s0 + ds < p.split_k) {
-                  const uint4* ps = reinterpret_cast<const uint4*>(base + (size_t)(s0 + ds) * p.ws_tile_words + c0);
+                  const uint4* ps = base + (size_t)(s0 + ds) * slice_words16 + (size_t)(c0 >> 2) * kUmmaM;
 #pragma unroll
                   for (int j = 0; j < 8; ++j)
-                    if (j < nq) x[ds][j] = __ldcg(ps + j);
+                    if (j < nq) x[ds][j] = __ldcg(ps + (size_t)j * kUmmaM);
                 }
 #pragma unroll
               for (int ds = 0; ds < 4; ++ds)
@@ -526,9 +558,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             if (nq == 8)
               store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[16]), pi, q_tile0 + c0 + 16, q_end);
           }
-          __syncwarp();
-          if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(8);
-          if (lane == 0) *ctr = 0u;   // leave the counter as it was found
+          }
+        }
+        __syncwarp();
+        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(8);
+        if (lane == 0) {
+          // the last warp to leave restores the counters (nobody polls or claims any more)
+          if (atomicAdd(ctr + 2, 1u) == (unsigned)(p.split_k - 1)) { ctr[0] = 0u; ctr[1] = 0u; ctr[2] = 0u; }
         }
       }
     }
