@@ -305,8 +305,8 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   int kc = l.kc;
   if (kc <= 0) kc = (smem_for_stages / (4 * kb_bytes) >= 3) ? 4 : (smem_for_stages / (2 * kb_bytes) >= 3) ? 2 : 1;
   while (kc > 1 && smem_for_stages / (kc * kb_bytes) < 2) kc >>= 1;
-  // at most 32 slices: the reduction tracks claimed shares in one 32-bit mask
-  int S = std::max(1, std::min(std::min(l.split_k, 32), up.kb_total));
+  // at most 31 slices: the reduction tracks claimed shares in one 32-bit mask (one bit seals it)
+  int S = std::max(1, std::min(std::min(l.split_k, 31), up.kb_total));
   up.kb_per_slice = ((up.kb_total + S - 1) / S + kc - 1) / kc * kc;     // slices start on a stage boundary
   S = (up.kb_total + up.kb_per_slice - 1) / up.kb_per_slice;              // every slice non-empty
   up.split_k = S;

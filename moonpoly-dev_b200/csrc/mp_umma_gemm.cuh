@@ -451,11 +451,25 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const int q_end = min(r.q_end, q_tile0 + r.bn);
 
       if (p.split_k == 1) {
-        for (int c0 = 0; c0 < r.bn; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(t_addr + (uint32_t)c0, v);
-          tmem_ld_wait();
-          store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end);
+        // two 16-column TMEM loads are in flight before the wait: the round trip, not the data,
+        // is what a load costs
+        if constexpr (EPI == EPI_SCALED) {        // the scaled epilogue has no registers to spare
+          for (int c0 = 0; c0 < r.bn; c0 += 16) {
+            uint32_t v[16];
+            tmem_ld_x16(t_addr + (uint32_t)c0, v);
+            tmem_ld_wait();
+            store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end);
+          }
+        } else {
+          for (int c0 = 0; c0 < r.bn; c0 += 32) {
+            uint32_t v[2][16];
+            const bool two = c0 + 16 < r.bn;
+            tmem_ld_x16(t_addr + (uint32_t)c0, v[0]);
+            if (two) tmem_ld_x16(t_addr + (uint32_t)c0 + 16u, v[1]);
+            tmem_ld_wait();
+            store_chunk16<EPI>(p, v[0], pi, q_tile0 + c0, q_end);
+            if (two) store_chunk16<EPI>(p, v[1], pi, q_tile0 + c0 + 16, q_end);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -466,13 +480,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // and in the reduction below (row-major scratch would scatter each access over 32 lines)
         uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words) +
                       row_in_tile;
-        for (int c0 = 0; c0 < r.bn; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld_x16(t_addr + (uint32_t)c0, v);
+        for (int c0 = 0; c0 < r.bn; c0 += (EPI == EPI_SCALED ? 16 : 32)) {
+          uint32_t v[2][16];
+          const bool two = EPI != EPI_SCALED && c0 + 16 < r.bn;   // two TMEM loads in flight per wait
+          tmem_ld_x16(t_addr + (uint32_t)c0, v[0]);
+          if (two) tmem_ld_x16(t_addr + (uint32_t)c0 + 16u, v[1]);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            __stcg(part + (size_t)((c0 >> 2) + j) * kUmmaM, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+          for (int h = 0; h < 2; ++h)
+            if (h == 0 || two) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                __stcg(part + (size_t)(((c0 + 16 * h) >> 2) + j) * kUmmaM,
+                       make_uint4(v[h][4 * j], v[h][4 * j + 1], v[h][4 * j + 2], v[h][4 * j + 3]));
+            }
         }
         tc_fence_before();
         __syncwarp();
@@ -482,35 +503,41 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         __syncwarp();
         // Reduction of this quadrant of the tile.  Share i is the run of 16-column chunks
         // [i*chunks/S, (i+1)*chunks/S).  The warp that arrives last (ticket S-1) knows all S slices are
-        // parked: it sums its own share at once and afterwards takes every share nobody has claimed.
-        // A warp that arrived earlier may help with the share of its ticket: it waits a short, bounded
-        // time for the last arrival and claims the share with an atomic OR; if the wait runs out it
-        // simply leaves, and the last arriver picks the share up.  Nothing therefore ever depends on
-        // a waiting warp (no deadlock when kernels of several streams compete for the SMs), and
-        // helping is only tried when all work units run concurrently (one unit per CTA).  Every column
-        // is summed in slice order s = 0..S-1 whoever sums it: results are bit-identical run to run.
-        unsigned* ctr = p.ws_counters + ((size_t)u.tile * 4 + quad) * 4;   // arrived, claimed mask, left, unused
+        // parked: it sums its own share at once, then seals the claim mask and takes every share
+        // nobody has registered for.  A warp that arrived earlier may help with the share of its
+        // ticket: it registers (a fire-and-forget atomic OR), waits a short, bounded time for the
+        // last arrival and then sums the share; if the wait runs out it withdraws the registration --
+        // unless the mask is already sealed, which tells it that everything has arrived and that the
+        // share has been left to it.  Nothing therefore ever depends on a warp that is waiting (no
+        // deadlock when kernels of several streams compete for the SMs), and helping is only tried
+        // when all work units run concurrently (one unit per CTA).  Every column is summed in slice
+        // order s = 0..S-1 whoever sums it: results are bit-identical from run to run.
+        constexpr unsigned kSealed = 0x80000000u;
+        unsigned* ctr = p.ws_counters + ((size_t)u.tile * 4 + quad) * 4;   // arrived, claim mask, left, unused
         unsigned ticket = 0;
         if (lane == 0) ticket = atomicAdd(ctr, 1u);
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(7);
         const int chunks = r.bn >> 4;
         const bool last = ticket == (unsigned)(p.split_k - 1);
-        const unsigned all_shares = p.split_k >= 32 ? 0xffffffffu : ((1u << p.split_k) - 1u);
+        const unsigned all_shares = (1u << p.split_k) - 1u;      // split_k <= 31
         unsigned mine = 0;                      // shares this warp sums
         if (last) {
           mine = 1u << ticket;
         } else if (total_units <= (int)gridDim.x && ((int)ticket + 1) * chunks / p.split_k > (int)ticket * chunks / p.split_k) {
           unsigned got = 0;
-          if (lane == 0 && counter_wait_ge_for(ctr, (unsigned)p.split_k, kHelpWaitNs))
-            got = (atomicOr(ctr + 1, 1u << ticket) & (1u << ticket)) ? 0u : (1u << ticket);
+          if (lane == 0) {
+            atomicOr(ctr + 1, 1u << ticket);
+            if (counter_wait_ge_for(ctr, (unsigned)p.split_k, kHelpWaitNs)) got = 1u << ticket;
+            else if (atomicAnd(ctr + 1, ~(1u << ticket)) & kSealed) got = 1u << ticket;
+          }
           mine = __shfl_sync(0xffffffffu, got, 0);
         }
         for (int round = 0; round < 2; ++round) {
           if (round == 1) {
             if (!last) break;
             unsigned rest = 0;
-            if (lane == 0) rest = all_shares & ~atomicOr(ctr + 1, all_shares) & ~(1u << ticket);
+            if (lane == 0) rest = all_shares & ~atomicOr(ctr + 1, all_shares | kSealed) & ~(1u << ticket);
             mine = __shfl_sync(0xffffffffu, rest, 0);
           }
           if (mine != 0) __threadfence();
