@@ -360,3 +360,50 @@ def test_fp16_streaming_pid_on_wide_problem_uses_tensor_tiles(api, oracle):
     a = rng.normal(28, 0, (100, 512), 0.05)
     b = rng.normal(28, 1, (200, 512), 0.05)
     close_f16(api.gemm_rcc_pid(dev(a), dev(b), 1101, 1).cpu().numpy(), oracle.gemm_f16_rcc(a, b))
+
+
+def test_launches_are_capturable_in_a_cuda_graph(api):
+    """The three kernel families (streaming, tcgen05 with split-K, tcgen05 single slice) recorded into one CUDA
+    graph and replayed on fresh inputs: the library allocates nothing and synchronises nothing once warm."""
+    k = 2048
+    shapes = [(4, 512, None, 1), (200, 136, 415, 4), (300, 264, None, 1)]      # (m, n, pid or selector, split_k)
+    A = [torch.empty((m, k), dtype=torch.float16, device="cuda") for m, _, _, _ in shapes]
+    B = [torch.empty((n, k), dtype=torch.float16, device="cuda") for _, n, _, _ in shapes]
+    C = [torch.empty((n, m), dtype=torch.float16, device="cuda") for m, n, _, _ in shapes]
+
+    def fill(seed):
+        refs = []
+        for i, (m, n, _, _) in enumerate(shapes):
+            a = rng.small_ints(seed, 2 * i, (m, k))
+            b = rng.small_ints(seed, 2 * i + 1, (n, k), lo=-1, hi=1)
+            A[i].copy_(dev(a))
+            B[i].copy_(dev(b))
+            refs.append((a.astype(np.int64) @ b.astype(np.int64).T).T.astype(np.float16))
+        return refs
+
+    def launch_all():
+        for i, (_, _, pid, split_k) in enumerate(shapes):
+            if pid is None:
+                api.gemm_rcc(A[i], B[i], c_nm=C[i])
+            else:
+                api.gemm_rcc_pid(A[i], B[i], pid, split_k, c_nm=C[i])
+
+    fill(40)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launch_all()                      # warm-up on the capture stream: scratch and plans exist afterwards
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        launch_all()
+    for seed in (41, 42):
+        refs = fill(seed)
+        for c in C:
+            c.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        for c, ref in zip(C, refs):
+            assert np.array_equal(c.cpu().numpy(), ref)
+    assert api.device_status() == 0
