@@ -29,6 +29,13 @@ const bool g_use_pdl = [] {
   const char* v = std::getenv("MOONPOLY_DISABLE_PDL");
   return !(v && v[0] && v[0] != '0');
 }();
+// Stream-K head for tile counts that are not a multiple of the grid (see run_umma).
+// MOONPOLY_DISABLE_STREAMK=1 turns it off (read at load and again by mp_reload_env).
+bool streamk_from_env() {
+  const char* v = std::getenv("MOONPOLY_DISABLE_STREAMK");
+  return !(v && v[0] && v[0] != '0');
+}
+std::atomic<bool> g_use_streamk{streamk_from_env()};
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -328,9 +335,39 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.bias = p.bias;
   up.out_bf16 = p.out_bf16;
 
-  if (S > 1) {
-    size_t cb = 0;
-    const size_t need = umma_workspace_bytes(p, l, &cb);
+  up.ws_slices = S;
+  const long long units = (long long)up.total_tiles * up.split_k;
+  const int grid = (int)std::min<long long>(units, d->sms);
+  up.helpers_ok = units <= grid ? 1 : 0;
+
+  // Stream-K head.  With T tiles on G persistent CTAs, T mod G tiles are left for a last, partly
+  // empty wave.  Instead, those r tiles go first and are cut along K into contiguous runs of
+  // sk_ipc K blocks, one run per CTA (a run may end one tile and begin the next); the tiles are
+  // completed through the split-K scratch, and the other T - r tiles follow as whole waves.  Runs
+  // are never shorter than a quarter of K, so a tile has at most ~5 contributors.
+  size_t sk_cb = 0, sk_pb = 0;
+  if (g_use_streamk.load(std::memory_order_relaxed) && S == 1 && up.num_regions == 1 && up.total_tiles > grid && grid == d->sms) {
+    const int r = up.total_tiles % grid;
+    // measured on B200: pays while the remainder is at most half a wave (r/G = 0.30: -17 %, 0.46: -5 %,
+    // 0.59 and above: the completion traffic costs more than the idle SMs did)
+    if (r > 0 && 2 * r <= grid && up.kb_total >= 8 * kc) {
+      long long ipc = ((long long)r * up.kb_total + grid - 1) / grid;
+      ipc = std::max<long long>(ipc, (up.kb_total + 3) / 4);
+      ipc = (ipc + kc - 1) / kc * kc;
+      const int max_slices = (int)((up.kb_total + ipc - 2) / ipc + 1);
+      sk_cb = round_up((size_t)r * 16 * sizeof(unsigned), 256);
+      sk_pb = (size_t)r * max_slices * bn_max * kUmmaM * 4;
+      if (l.workspace == nullptr || l.workspace_bytes >= sk_cb + sk_pb) {
+        up.sk_tiles = r;
+        up.sk_ipc = (int)ipc;
+        up.ws_slices = max_slices;
+      }
+    }
+  }
+
+  if (S > 1 || up.sk_tiles > 0) {
+    size_t cb = sk_cb;
+    const size_t need = up.sk_tiles > 0 ? sk_cb + sk_pb : umma_workspace_bytes(p, l, &cb);
     uint8_t *counters = nullptr, *partials = nullptr;
     if (l.workspace != nullptr) {
       if (l.workspace_bytes < need)
@@ -357,8 +394,6 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
     ty1 = ty0;
   }
 
-  const long long units = (long long)up.total_tiles * up.split_k;
-  const int grid = (int)std::min<long long>(units, d->sms);
   const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024;
   if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
   if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32>(*d, 1, tx, ty0, ty1, up, grid, smem, stream);
@@ -619,6 +654,7 @@ int mp_num_sms(void) {
 
 int mp_reload_env(void) {
   mp::reload_env();
+  g_use_streamk.store(streamk_from_env(), std::memory_order_relaxed);
   return MP_OK;
 }
 

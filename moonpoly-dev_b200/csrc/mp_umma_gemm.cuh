@@ -78,6 +78,11 @@ struct UmmaParams {
   uint32_t* ws_partials;   // [total_tiles][split_k][bn_max / 4][128 rows] 16-byte words
   unsigned* ws_counters;   // [total_tiles][4 quadrants][arrived, claimed, left, -], zero on entry, left zero on exit
   int ws_tile_words;       // bn_max * 128
+  int ws_slices;           // slices per tile in the scratch numbering (split_k, or sk_max_slices for stream-K tiles)
+  int helpers_ok;          // 1: all units run concurrently, early slices may help with the reduction
+  // stream-K head: the first sk_tiles tiles (single region, split_k == 1) are cut into contiguous runs of
+  // sk_ipc K blocks, one run per CTA, so that the remainder of total_tiles / grid does not cost a whole wave
+  int sk_tiles, sk_ipc;
   // scaled int8 matmul epilogue
   const float* scale_p; const float* scale_q;   // scales indexed along P / along Q
   int scale_p_scalar, scale_q_scalar;
@@ -87,13 +92,10 @@ struct UmmaParams {
 };
 
 struct UnitCoord {
-  int region, tile, tp, tq, kb0, kb1, slice;
+  int region, tile, tp, tq, kb0, kb1, slice, nslices;
 };
 
-__device__ __forceinline__ UnitCoord decode_unit(const UmmaParams& p, int w) {
-  UnitCoord u;
-  u.tile = w / p.split_k;
-  u.slice = w - u.tile * p.split_k;
+__device__ __forceinline__ void tile_coords(const UmmaParams& p, UnitCoord& u) {
   u.region = (p.num_regions == 2 && u.tile >= p.reg[1].tile_base) ? 1 : 0;
   const Region& r = p.reg[u.region];
   const int t = u.tile - r.tile_base;
@@ -104,10 +106,48 @@ __device__ __forceinline__ UnitCoord decode_unit(const UmmaParams& p, int w) {
   const int in_g = t - g * group_sz;
   u.tq = in_g / rows;
   u.tp = first_p + (in_g - u.tq * rows);
-  u.kb0 = u.slice * p.kb_per_slice;
-  u.kb1 = min(p.kb_total, u.kb0 + p.kb_per_slice);
-  return u;
 }
+
+// The work units of one CTA, in the order every role of the CTA walks them: first its run of the
+// stream-K head (if any), which may cover the tail of one tile and the head of the next, then the
+// uniform units  w = blockIdx.x, blockIdx.x + grid, ...  where unit w is slice w % split_k of tile
+// sk_tiles + w / split_k.
+struct UnitWalk {
+  int sk_cur, sk_end, w;
+  __device__ __forceinline__ explicit UnitWalk(const UmmaParams& p) {
+    const long long total = (long long)p.sk_tiles * p.kb_total;
+    const long long b = (long long)blockIdx.x * p.sk_ipc;
+    sk_cur = (int)(b < total ? b : total);
+    sk_end = (int)(b + p.sk_ipc < total ? b + p.sk_ipc : total);
+    w = (int)blockIdx.x;
+  }
+  __device__ __forceinline__ bool next(const UmmaParams& p, UnitCoord& u) {
+    if (sk_cur < sk_end) {
+      u.tile = sk_cur / p.kb_total;
+      u.kb0 = sk_cur - u.tile * p.kb_total;
+      const int len = min(p.kb_total - u.kb0, sk_end - sk_cur);
+      u.kb1 = u.kb0 + len;
+      const int first_cta = (u.tile * p.kb_total) / p.sk_ipc;
+      const int last_cta = ((u.tile + 1) * p.kb_total - 1) / p.sk_ipc;
+      u.slice = (int)blockIdx.x - first_cta;
+      u.nslices = last_cta - first_cta + 1;
+      sk_cur += len;
+      tile_coords(p, u);
+      return true;
+    }
+    const int uniform_units = (p.total_tiles - p.sk_tiles) * p.split_k;
+    if (w >= uniform_units) return false;
+    const int t = w / p.split_k;
+    u.tile = p.sk_tiles + t;
+    u.slice = w - t * p.split_k;
+    u.nslices = p.split_k;
+    u.kb0 = u.slice * p.kb_per_slice;
+    u.kb1 = min(p.kb_total, u.kb0 + p.kb_per_slice);
+    tile_coords(p, u);
+    w += (int)gridDim.x;
+    return true;
+  }
+};
 
 // ------------------------------------------------------------------------------------ epilogue math
 template <int EPI>
@@ -322,7 +362,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   if (threadIdx.x == 0) MP_TRACE_MARK(1);
   griddep_launch_dependents();
 
-  const int total_units = p.total_tiles * p.split_k;
   constexpr int kElemsPerKb = (KIND == KIND_I8) ? 128 : 64;
 
   if (warp == 0) {
@@ -330,8 +369,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (lane == 0) {
       // While the previous kernel drains, pull the first unit's operands towards L2 (a hint only;
       // whatever the previous kernel still writes reaches L2 as well, so this cannot go stale).
-      if ((int)blockIdx.x < total_units) {
-        const UnitCoord u = decode_unit(p, (int)blockIdx.x);
+      UnitCoord u;
+      if (UnitWalk(p).next(p, u)) {
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
         const int prow = u.tp * kUmmaM, qrow = r.q_begin + u.tq * r.bn;
@@ -352,8 +391,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       MP_TRACE_MARK(2);
       uint32_t it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x) {
-        const UnitCoord u = decode_unit(p, w);
+      UnitWalk walk(p);
+      while (ok && walk.next(p, u)) {
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
         const uint32_t tx = (uint32_t)(p.kc * (kXTileBytes + r.bn * kRowBytes));
@@ -395,8 +434,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (lane == 0) {
       uint32_t it = 0, ui = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
-        const UnitCoord u = decode_unit(p, w);
+      UnitWalk walk(p);
+      UnitCoord u;
+      for (; ok && walk.next(p, u); ++ui) {
         const Region& r = p.reg[u.region];
         const uint32_t buf = ui & 1u;
         const uint32_t use = ui >> 1;
@@ -436,8 +476,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     uint32_t ui = 0;
     bool ok = true;
     griddep_wait();
-    for (int w = blockIdx.x; w < total_units && ok; w += gridDim.x, ++ui) {
-      const UnitCoord u = decode_unit(p, w);
+    UnitWalk walk(p);
+    UnitCoord u;
+    for (; ok && walk.next(p, u); ++ui) {
       const Region& r = p.reg[u.region];
       const uint32_t buf = ui & 1u;
       const uint32_t use = ui >> 1;
@@ -450,7 +491,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const int q_tile0 = r.q_begin + u.tq * r.bn;
       const int q_end = min(r.q_end, q_tile0 + r.bn);
 
-      if (p.split_k == 1) {
+      const int S = u.nslices;               // slices that make up this unit's tile
+      if (S == 1) {
         // two 16-column TMEM loads are in flight before the wait: the round trip, not the data,
         // is what a load costs
         if constexpr (EPI == EPI_SCALED) {        // the scaled epilogue has no registers to spare
@@ -478,7 +520,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // park this slice's raw accumulators as [tile][slice][column / 4][row] 16-byte words: the 32
         // lanes of a warp (32 consecutive rows) then touch 512 contiguous bytes per access, both here
         // and in the reduction below (row-major scratch would scatter each access over 32 lines)
-        uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.split_k + u.slice) * (size_t)p.ws_tile_words) +
+        uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.ws_slices + u.slice) * (size_t)p.ws_tile_words) +
                       row_in_tile;
         for (int c0 = 0; c0 < r.bn; c0 += (EPI == EPI_SCALED ? 16 : 32)) {
           uint32_t v[2][16];
@@ -519,16 +561,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(7);
         const int chunks = r.bn >> 4;
-        const bool last = ticket == (unsigned)(p.split_k - 1);
-        const unsigned all_shares = (1u << p.split_k) - 1u;      // split_k <= 31
+        const bool last = ticket == (unsigned)(S - 1);
+        const unsigned all_shares = (1u << S) - 1u;      // S <= 31
         unsigned mine = 0;                      // shares this warp sums
         if (last) {
           mine = 1u << ticket;
-        } else if (total_units <= (int)gridDim.x && ((int)ticket + 1) * chunks / p.split_k > (int)ticket * chunks / p.split_k) {
+        } else if (p.helpers_ok && ((int)ticket + 1) * chunks / S > (int)ticket * chunks / S) {
           unsigned got = 0;
           if (lane == 0) {
             atomicOr(ctr + 1, 1u << ticket);
-            if (counter_wait_ge_for(ctr, (unsigned)p.split_k, kHelpWaitNs)) got = 1u << ticket;
+            if (counter_wait_ge_for(ctr, (unsigned)S, kHelpWaitNs)) got = 1u << ticket;
             else if (atomicAnd(ctr + 1, ~(1u << ticket)) & kSealed) got = 1u << ticket;
           }
           mine = __shfl_sync(0xffffffffu, got, 0);
@@ -544,9 +586,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           while (mine != 0) {
             const int share = __ffs((int)mine) - 1;
             mine &= mine - 1;
-            const int c_begin = (share * chunks / p.split_k) << 4;
-            const int c_end = ((share + 1) * chunks / p.split_k) << 4;
-          const uint4* base = reinterpret_cast<const uint4*>(p.ws_partials + (size_t)u.tile * p.split_k * (size_t)p.ws_tile_words) +
+            const int c_begin = (share * chunks / S) << 4;
+            const int c_end = ((share + 1) * chunks / S) << 4;
+          const uint4* base = reinterpret_cast<const uint4*>(p.ws_partials + (size_t)u.tile * p.ws_slices * (size_t)p.ws_tile_words) +
                               row_in_tile;
           const size_t slice_words16 = (size_t)p.ws_tile_words >> 2;
           // 32 columns per pass (the last pass may be half wide); the loads of up to four slices are
@@ -554,11 +596,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             const int nq = (c_end - c0 >= 32) ? 8 : 4;      // 16-byte words in this pass
             uint32_t v[32];
-            for (int s0 = 0; s0 < p.split_k; s0 += 4) {
+            for (int s0 = 0; s0 < S; s0 += 4) {
               uint4 x[4][8];
 #pragma unroll
               for (int ds = 0; ds < 4; ++ds)
-                if (s0 + ds < p.split_k) {
+                if (s0 + ds < S) {
                   const uint4* ps = base + (size_t)(s0 + ds) * slice_words16 + (size_t)(c0 >> 2) * kUmmaM;
 #pragma unroll
                   for (int j = 0; j < 8; ++j)
@@ -566,7 +608,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 }
 #pragma unroll
               for (int ds = 0; ds < 4; ++ds)
-                if (s0 + ds < p.split_k) {
+                if (s0 + ds < S) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j)
                     if (j < nq) {
@@ -591,7 +633,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(8);
         if (lane == 0) {
           // the last warp to leave restores the counters (nobody polls or claims any more)
-          if (atomicAdd(ctr + 2, 1u) == (unsigned)(p.split_k - 1)) { ctr[0] = 0u; ctr[1] = 0u; ctr[2] = 0u; }
+          if (atomicAdd(ctr + 2, 1u) == (unsigned)(S - 1)) { ctr[0] = 0u; ctr[1] = 0u; ctr[2] = 0u; }
         }
       }
     }

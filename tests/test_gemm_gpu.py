@@ -407,3 +407,47 @@ def test_launches_are_capturable_in_a_cuda_graph(api):
         for c, ref in zip(C, refs):
             assert np.array_equal(c.cpu().numpy(), ref)
     assert api.device_status() == 0
+
+
+def _exact_ref(a, b):
+    # small integers: float64 BLAS is exact and fast
+    return (a.astype(np.float64) @ b.astype(np.float64).T).T
+
+
+@pytest.mark.parametrize("orient,bn,m,n,k", [(0, 64, 1280, 1280, 1024), (0, 64, 1275, 1270, 1096),
+                                              (1, 128, 1100, 2500, 2048), (1, 256, 4096, 4096, 512),
+                                              (0, 32, 700, 1000, 4096)])
+def test_fp16_stream_k_head_exact_and_switchable(api, monkeypatch, orient, bn, m, n, k):
+    """Tile counts that are not a multiple of the grid: the first tiles are cut along K over all CTAs and finished
+    through the scratch.  Integer-valued inputs make every summation order exact, so the result must equal the
+    plain schedule's (MOONPOLY_DISABLE_STREAMK=1) and the known answer, with and without alpha/beta."""
+    a = rng.small_ints(50, 0, (m, k), lo=-1, hi=1)
+    b = rng.small_ints(50, 1, (n, k))
+    ref = _exact_ref(a, b)
+    assert np.abs(ref).max() < 2048
+    A, B = dev(a), dev(b)
+    c0 = rng.small_ints(50, 2, (n, m)).astype(np.float16)
+    try:
+        got = api.gemm_rcc_tile(A, B, orient, bn).cpu().numpy()
+        again = api.gemm_rcc_tile(A, B, orient, bn).cpu().numpy()
+        got_ab = api.gemm_rcc_tile(A, B, orient, bn, c_nm=dev(c0).clone(), alpha=2.0, beta=-1.0).cpu().numpy()
+        monkeypatch.setenv("MOONPOLY_DISABLE_STREAMK", "1")
+        api.reload_env()
+        plain = api.gemm_rcc_tile(A, B, orient, bn).cpu().numpy()
+    finally:
+        monkeypatch.delenv("MOONPOLY_DISABLE_STREAMK", raising=False)
+        api.reload_env()
+    assert np.array_equal(got, ref.astype(np.float16))
+    assert np.array_equal(got, again)
+    assert np.array_equal(got, plain)
+    assert np.array_equal(got_ab, (2.0 * ref - c0.astype(np.float64)).astype(np.float16))
+    assert api.device_status() == 0
+
+
+def test_int8_stream_k_head_bit_exact(api):
+    m, n, k = 1300, 2100, 2048
+    a = rng.int8_uniform(51, 0, (m, k))
+    b = rng.int8_uniform(51, 1, (n, k))
+    ref = (a.astype(np.float64) @ b.astype(np.float64).T).T.astype(np.int64)
+    got = api.gemm_rcc_tile(dev(a), dev(b), 1, 128).cpu().numpy()
+    assert np.array_equal(got.astype(np.int64), ref)
