@@ -142,6 +142,17 @@ int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t*
                     const float* a_scales, int a_scalar, const float* b_scales, int b_scalar,
                     const void* bias, void* out, int ldc, int out_dtype, void* stream);
 
+/* Tuning entry for the scaled matmul (no counterpart in the reference, whose six configurations are
+ * fixed CUTLASS instantiations): same arguments as mp_scaled_mm_i8 behind an explicit kernel choice.
+ * orient 0 puts the tokens (rows of A) on the 128-row UMMA-M side and tiles the channels by bn,
+ * orient 1 puts the channels (rows of B_nk) there and tiles the tokens by bn, orient 3 selects the
+ * streaming kernel (narrow side <= 64 rows; bn and split_k ignored).  The refit tool uses it to
+ * measure the scaled-matmul plan table. */
+int mp_scaled_mm_i8_tile(int orient, int bn, int split_k, int M, int N, int K, const int8_t* A, int lda,
+                         const int8_t* B_nk, int ldb, const float* a_scales, int a_scalar,
+                         const float* b_scales, int b_scalar, const void* bias, void* out, int ldc,
+                         int out_dtype, void* stream);
+
 /* predict_best_sm80_evt_config / get_sm80_evt_config
  * (core/int8/scaled_mm/scaled_mm_mikpoly_unified.cu:405-414): tile id the scaled matmul would
  * pick for (M,N,K), and a tile's (tile_m, tile_n, tile_k, alignment). */

@@ -518,7 +518,7 @@ int run_gemv(const Problem& p, cudaStream_t stream) {
 }
 
 // Streaming warp-MMA path: one side of the problem has at most 64 rows; the other operand is streamed once.
-template <int NT, int UNROLL, int MINB>
+template <int KIND, int EPI, int NT, int UNROLL, int MINB>
 int launch_stream_t(const StreamParams& sp, int sms, cudaStream_t stream) {
   // a whole multiple of the SM count when the rows allow it, else one CTA per 8 rows
   const int per_sm = std::min(MINB, sp.R / (8 * sms));
@@ -532,13 +532,22 @@ int launch_stream_t(const StreamParams& sp, int sms, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_use_pdl ? 1 : 0;
-  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, stream_mma_f16_kernel<NT, UNROLL, MINB>, sp));
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, stream_mma_kernel<KIND, EPI, NT, UNROLL, MINB>, sp));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
 }
 
+template <int KIND, int EPI>
+int launch_stream_nt(const StreamParams& sp, int sms, cudaStream_t stream) {
+  if (sp.T <= 8) return launch_stream_t<KIND, EPI, 1, 8, 2>(sp, sms, stream);
+  if (sp.T <= 16) return launch_stream_t<KIND, EPI, 2, 8, 2>(sp, sms, stream);
+  if (sp.T <= 32) return launch_stream_t<KIND, EPI, 4, 8, 2>(sp, sms, stream);
+  return launch_stream_t<KIND, EPI, 8, 4, 2>(sp, sms, stream);
+}
+
 bool stream_compatible(const Problem& p) {
-  return p.dtype == MP_FP16 && p.epi == EPI_F16 && std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 8 &&
+  if (!(p.dtype == MP_FP16 && p.epi == EPI_F16) && p.dtype != MP_INT8) return false;
+  return std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 16 &&
          tma_compatible(p);      // same rule: 16-byte aligned rows
 }
 
@@ -547,21 +556,25 @@ int run_stream(const Problem& p, cudaStream_t stream) {
   if (int rc = device_state(&d)) return rc;
   StreamParams sp{};
   const bool narrow_is_a = p.m <= p.n;
-  sp.W = reinterpret_cast<const __half*>(narrow_is_a ? p.B : p.A);
+  sp.W = narrow_is_a ? p.B : p.A;
   sp.ldw = narrow_is_a ? p.ldb : p.lda;
-  sp.X = reinterpret_cast<const __half*>(narrow_is_a ? p.A : p.B);
+  sp.X = narrow_is_a ? p.A : p.B;
   sp.ldx = narrow_is_a ? p.lda : p.ldb;
   sp.R = narrow_is_a ? p.n : p.m;
   sp.T = narrow_is_a ? p.m : p.n;
   sp.K = p.k;
-  sp.out = reinterpret_cast<__half*>(p.C);
+  sp.out = p.C;
   sp.stride_r = narrow_is_a ? p.c_stride_n : p.c_stride_m;
   sp.stride_t = narrow_is_a ? p.c_stride_m : p.c_stride_n;
-  sp.alpha = p.alpha; sp.beta = p.beta;
-  if (sp.T <= 8) return launch_stream_t<1, 8, 2>(sp, d->sms, stream);
-  if (sp.T <= 16) return launch_stream_t<2, 8, 2>(sp, d->sms, stream);
-  if (sp.T <= 32) return launch_stream_t<4, 8, 2>(sp, d->sms, stream);
-  return launch_stream_t<8, 4, 2>(sp, d->sms, stream);
+  sp.alpha = p.alpha; sp.beta = p.beta; sp.ialpha = p.ialpha; sp.ibeta = p.ibeta;
+  // scaled epilogue: tokens are the rows of A, channels the rows of B
+  sp.chan_scale = p.b_scales; sp.chan_scalar = p.b_scalar;
+  sp.tok_scale = p.a_scales; sp.tok_scalar = p.a_scalar;
+  sp.chan_on_r = narrow_is_a ? 1 : 0;
+  sp.bias = p.bias; sp.out_bf16 = p.out_bf16;
+  if (p.dtype == MP_FP16) return launch_stream_nt<STREAM_F16, STREAM_EPI_F16>(sp, d->sms, stream);
+  if (p.epi == EPI_I32) return launch_stream_nt<STREAM_I8, STREAM_EPI_I32>(sp, d->sms, stream);
+  return launch_stream_nt<STREAM_I8, STREAM_EPI_SCALED>(sp, d->sms, stream);
 }
 
 int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {
@@ -725,7 +738,7 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
   }
   if (orient == 3) {            // the streaming warp-MMA kernel (bn, kc, split_k unused)
     const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
-    if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16, min(m,n) <= 64 and 16-byte aligned rows");
+    if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16 or INT8, min(m,n) <= 64 and 16-byte aligned rows");
     return run_stream(pg, reinterpret_cast<cudaStream_t>(stream));
   }
   if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0 || (kc != 0 && kc != 1 && kc != 2 && kc != 4))
@@ -784,26 +797,59 @@ int mp_scaled_mm_config(int config_id, int out[4]) {
   return MP_OK;
 }
 
-int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t* B_nk, int ldb, const float* a_scales,
-                    int a_scalar, const float* b_scales, int b_scalar, const void* bias, void* out, int ldc,
-                    int out_dtype, void* stream) {
+namespace {
+int scaled_problem(Problem* p, int M, int N, int K, const int8_t* A, int lda, const int8_t* B_nk, int ldb,
+                   const float* a_scales, int a_scalar, const float* b_scales, int b_scalar, const void* bias,
+                   void* out, int ldc, int out_dtype) {
   if (M < 0 || N < 0 || K < 0) return fail(MP_ERR_INVALID_ARG, "negative problem size");
-  if (M == 0 || N == 0) return MP_OK;
+  if (M == 0 || N == 0) return -1;          // nothing to do
   if (!A || !B_nk || !out || !a_scales || !b_scales) return fail(MP_ERR_INVALID_ARG, "null operand pointer");
   if (out_dtype != 0 && out_dtype != 1) return fail(MP_ERR_INVALID_ARG, "Unsupported output dtype %d", out_dtype);
   if (lda < K || ldb < K || ldc < N) return fail(MP_ERR_INVALID_ARG, "leading dimension smaller than the row");
-  Problem p{};
-  p.dtype = MP_INT8; p.epi = EPI_SCALED;
-  p.m = M; p.n = N; p.k = K;
-  p.A = A; p.lda = lda; p.B = B_nk; p.ldb = ldb;
-  p.C = out; p.c_stride_m = ldc; p.c_stride_n = 1;
-  p.a_scales = a_scales; p.b_scales = b_scales; p.a_scalar = a_scalar ? 1 : 0; p.b_scalar = b_scalar ? 1 : 0;
-  p.bias = bias; p.out_bf16 = out_dtype;
+  *p = Problem{};
+  p->dtype = MP_INT8; p->epi = EPI_SCALED;
+  p->m = M; p->n = N; p->k = K;
+  p->A = A; p->lda = lda; p->B = B_nk; p->ldb = ldb;
+  p->C = out; p->c_stride_m = ldc; p->c_stride_n = 1;
+  p->a_scales = a_scales; p->b_scales = b_scales; p->a_scalar = a_scalar ? 1 : 0; p->b_scalar = b_scalar ? 1 : 0;
+  p->bias = bias; p->out_bf16 = out_dtype;
+  return MP_OK;
+}
+}  // namespace
+
+int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t* B_nk, int ldb, const float* a_scales,
+                    int a_scalar, const float* b_scales, int b_scalar, const void* bias, void* out, int ldc,
+                    int out_dtype, void* stream) {
+  Problem p;
+  const int rc = scaled_problem(&p, M, N, K, A, lda, B_nk, ldb, a_scales, a_scalar, b_scales, b_scalar, bias, out, ldc,
+                                out_dtype);
+  if (rc != MP_OK) return rc < 0 ? MP_OK : rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (K == 0 || !tma_compatible(p)) return run_simt(p, 64, 64, 1, nullptr, 0, s);
   const mp::ScaledCfg cfg = mp::scaled_mm_select(M, N, K);
+  if (cfg.stream && stream_compatible(p)) return run_stream(p, s);
   Launch l;
   l.orient = cfg.orient; l.bn = cfg.bn; l.split_k = cfg.split_k;
+  return run_umma(p, l, s);
+}
+
+int mp_scaled_mm_i8_tile(int orient, int bn, int split_k, int M, int N, int K, const int8_t* A, int lda,
+                         const int8_t* B_nk, int ldb, const float* a_scales, int a_scalar, const float* b_scales,
+                         int b_scalar, const void* bias, void* out, int ldc, int out_dtype, void* stream) {
+  Problem p;
+  const int rc = scaled_problem(&p, M, N, K, A, lda, B_nk, ldb, a_scales, a_scalar, b_scales, b_scalar, bias, out, ldc,
+                                out_dtype);
+  if (rc != MP_OK) return rc < 0 ? MP_OK : rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (K == 0 || !tma_compatible(p)) return fail(MP_ERR_INVALID_ARG, "operands miss the 16-byte alignment the tensor-core kernels need");
+  if (orient == 3) {
+    if (!stream_compatible(p)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs min(M,N) <= 64");
+    return run_stream(p, s);
+  }
+  if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0)
+    return fail(MP_ERR_INVALID_ARG, "bad tile: orient=%d bn=%d", orient, bn);
+  Launch l;
+  l.orient = orient; l.bn = bn; l.split_k = std::max(1, split_k);
   return run_umma(p, l, s);
 }
 

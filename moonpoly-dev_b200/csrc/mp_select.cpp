@@ -167,6 +167,7 @@ LiveFlags read_live_flags(int dtype) {
     f.fp32_force = env_int("MOONPOLY_FP32_PATTERN3_FORCE_SPLITK", 0);
   } else {
     f.int8_p3 = env_flag("MOONPOLY_ENABLE_INT8_PATTERN3", true);
+    f.gen = env_flag("MOONPOLY_ENABLE_GENERATED_SELECTOR", true);
     f.int8_force = env_int("MOONPOLY_INT8_PATTERN3_FORCE_SPLITK", 0);
   }
   return f;
@@ -330,6 +331,10 @@ TileCfg tile_cfg(int dtype, int pid) {
     return c;
   }
   if (dtype == MP_INT8) {
+    if (pid == 1101) {            // library-native streaming warp-MMA kernel (min(m,n) <= 64)
+      c.valid = true; c.orient = 3; c.bn = 64; c.align = 16; c.split_capable = false;
+      return c;
+    }
     if (pid < 0 || pid > 45) return c;
     const U& u = kInt8Primary[pid];
     c.valid = true; c.orient = u.orient; c.bn = u.bn; c.align = u.align; c.split_capable = true;
@@ -361,10 +366,11 @@ namespace {
 // pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
 struct PidMeta { TileCfg cfg; int meta[3]; };
 struct MetaTables {
-  PidMeta fp16[440], int8[46], fp32[40], native[64], skinny, streaming;
+  PidMeta fp16[440], int8[46], fp32[40], native[64], skinny, streaming, streaming_i8;
   MetaTables() {
     skinny.cfg = tile_cfg(MP_FP16, 1100); pid_tile_meta(MP_FP16, 1100, skinny.meta);
     streaming.cfg = tile_cfg(MP_FP16, 1101); pid_tile_meta(MP_FP16, 1101, streaming.meta);
+    streaming_i8.cfg = tile_cfg(MP_INT8, 1101); pid_tile_meta(MP_INT8, 1101, streaming_i8.meta);
     for (int p = 0; p < 64; ++p) { native[p].cfg = tile_cfg(MP_FP16, 1000 + p); pid_tile_meta(MP_FP16, 1000 + p, native[p].meta); }
     for (int p = 0; p < 440; ++p) { fp16[p].cfg = tile_cfg(MP_FP16, p); pid_tile_meta(MP_FP16, p, fp16[p].meta); }
     for (int p = 0; p < 46; ++p) { int8[p].cfg = tile_cfg(MP_INT8, p); pid_tile_meta(MP_INT8, p, int8[p].meta); }
@@ -380,7 +386,7 @@ const PidMeta* pid_meta(int dtype, int pid) {
     if (pid >= 1000 && pid < 1064) return t.native[pid - 1000].cfg.valid ? &t.native[pid - 1000] : nullptr;
     return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
   }
-  if (dtype == MP_INT8) return pid < 46 ? &t.int8[pid] : nullptr;
+  if (dtype == MP_INT8) return pid == 1101 ? &t.streaming_i8 : pid < 46 ? &t.int8[pid] : nullptr;
   if (dtype == MP_FP32) return pid < 40 ? &t.fp32[pid] : nullptr;
   return nullptr;
 }
@@ -432,6 +438,22 @@ struct DecodeEntry { int m, n, k, pid, split_k; };
 // (0 any, 1 m % 8 == 0, 2 m % 8 != 0: C columns are then not 16-byte aligned).
 struct PlanRow { int m_lo, m_hi, n_lo, n_hi, k, align_class, pid, split_k; float ms; };
 #include "generated/mp_decode_selector.inc"
+// Measured plans of the INT8 scaled matmul out[M,N] = A[M,K] * B[N,K]^T: a row applies to M in
+// [m_lo, m_hi] with the row's exact (N, K).  orient 0 / 1: tile of the tensor-core kernel (tokens /
+// channels on the 128-row side, the other side tiled by bn); orient 3: the streaming kernel.
+struct ScaledPlanRow { int m_lo, m_hi, n, k, orient, bn, split_k; float ms; };
+#include "generated/mp_scaled_plans.inc"
+
+// Without a measured row: up to how many narrow-side rows the INT8 streaming kernel beats the
+// tiles, by the size of the streamed operand (measured on B200: 4096x4096 ... 28672x4096)
+bool int8_prefers_stream(int narrow, long long wide_rows, int k) {
+  if (narrow < 1 || k < 16 || k % 16 != 0) return false;
+  const long long bytes = wide_rows * (long long)k;
+  if (narrow <= 8) return true;
+  if (narrow <= 16) return bytes <= (64ll << 20);
+  if (narrow <= 32) return bytes <= (32ll << 20);
+  return false;
+}
 
 inline void consider(mp_plan& best, int pattern, int pid, int split_k, int split_n, float ms, float margin) {
   if (!std::isfinite(ms) || ms <= 0.0f) return;
@@ -602,6 +624,12 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
   } else {
     plan = select_simple(MP_INT8, 46, m, n, k, lf.int8_p3, lf.int8_force, 64, e.int8_p3_min_k,
                          e.int8_p3_min_part_k, e.int8_p3_margin, 16);
+    // few rows on the narrow side: the streaming kernel (library-native pid 1101) beats every tile; it is part
+    // of this library's generated plans, so the same flag gates it
+    if (lf.gen && lf.int8_force <= 1 && int8_prefers_stream(std::min(m, n), std::max(m, n), k)) {
+      const double bytes = (double)m * k + (double)n * k + 4.0 * m * n;
+      plan = mp_plan{MP_PATTERN_SINGLE, 1101, 1, 0, (float)(bytes / 6.0e9 + 2.5e-3)};
+    }
   }
   if (std::getenv("MOONPOLY_DEBUG_ONLINE_SELECTOR")) {
     std::fprintf(stdout, "[moonpoly][%s] online m=%d n=%d k=%d -> Pattern%d pid=%d split_k=%d split_n=%d est_ms=%g\n",
@@ -638,7 +666,7 @@ void scaled_mm_config_meta(int id, int out[4]) {
 }
 
 ScaledCfg scaled_mm_select(int M, int N, int K) {
-  ScaledCfg best{0, kScaled[0].orient, kScaled[0].bn, 1};
+  ScaledCfg best{0, kScaled[0].orient, kScaled[0].bn, 1, false};
   float best_ms = kInf;
   const int sms = g_num_sms.load(std::memory_order_relaxed);
   static constexpr int kSplit[4] = {1, 2, 4, 8};
@@ -654,7 +682,18 @@ ScaledCfg scaled_mm_select(int M, int N, int K) {
       float ms = waves * analytic_unit_ms(MP_INT8, c, k_iter, (int)std::min<long long>(units, sms)) +
                  reduction_ms(MP_INT8, -1, c, tiles, S);
       // padded work is wasted tensor time: prefer the tile that fits M
-      if (ms < best_ms) { best_ms = ms; best = ScaledCfg{id, s.orient, s.bn, S}; }
+      if (ms < best_ms) { best_ms = ms; best = ScaledCfg{id, s.orient, s.bn, S, false}; }
+    }
+  }
+  best.stream = int8_prefers_stream(std::min(M, N), std::max(M, N), K);
+  // measured rows win over the model; `id` stays the model's choice among the six public configurations
+  if (env_flag("MOONPOLY_ENABLE_GENERATED_SELECTOR", true)) {
+    for (int i = 0; i < kScaledPlanCount; ++i) {
+      const ScaledPlanRow& r = kScaledPlans[i];
+      if (r.n != N || r.k != K || M < r.m_lo || M > r.m_hi) continue;
+      best.stream = r.orient == 3;
+      if (r.orient != 3) { best.orient = r.orient; best.bn = r.bn; best.split_k = std::max(1, r.split_k); }
+      break;
     }
   }
   return best;

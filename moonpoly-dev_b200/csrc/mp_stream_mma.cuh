@@ -1,72 +1,130 @@
-// Streaming FP16 GEMM for a narrow side of at most 64 rows: the wide operand W[R,K] goes from HBM
-// straight into registers, already in the fragment layout of the warp-level m16n8k16 tensor
-// instruction, and is multiplied against the few rows of X[T,K] that sit in L1/L2.  There is no
-// shared-memory pipeline, no TMEM and no split-K hand-off through global memory, so the kernel has
-// none of the latency chains (barrier round trips, accumulator drain, partial-sum exchange) that
-// bound the tcgen05 kernel when the whole problem is a ~5 us HBM stream.
+// Streaming GEMM for a narrow side of at most 64 rows (FP16, INT8): the wide operand W[R,K] goes
+// from HBM straight into registers, already in the fragment layout of the warp-level tensor
+// instruction (m16n8k16 for FP16, m16n8k32 for INT8), and is multiplied against the few rows of
+// X[T,K] that sit in L1/L2.  There is no shared-memory pipeline, no TMEM and no split-K hand-off
+// through global memory, so the kernel has none of the latency chains (barrier round trips,
+// accumulator drain, partial-sum exchange) that bound the tcgen05 kernel when the whole problem is
+// a ~5 us HBM stream.
 //
-//   out[r * stride_r + t * stride_t] = alpha * sum_k W[r,k] * X[t,k] + beta * out[...]
+//   acc[r][t] = sum_k W[r,k] * X[t,k]          (fp32 for FP16 inputs, exact int32 for INT8)
+//   FP16:        out = alpha * acc + beta * out                       (fp16)
+//   INT8 plain:  out = ialpha * acc + ibeta * out                     (int32)
+//   INT8 scaled: out = RN16(a_s[token] * RN32(b_s[channel] * RN32(acc))) (+ bias in the output type)
 //
-// Work split: one CTA of 8 warps owns up to 16 rows of W at a time; warp w takes the w-th eighth of K for those
-// rows, and the 8 partial 16 x T blocks are added in a fixed order through shared memory
-// (deterministic).  A dot product does not care in which order k is visited as long as both
-// operands agree, so a lane loads 16 contiguous bytes of its row (8 halves) and spreads them over
-// the k-slots of two consecutive MMAs; the X fragment is loaded with the same rule.  Every load of
-// W is a full 16-byte vector and the four lanes of a row cover 64 contiguous bytes.
+// Work split: one CTA of 8 warps owns up to 16 rows of W at a time; warp w takes the w-th eighth
+// of K for those rows, and the 8 partial 16 x T blocks are added in a fixed order through shared
+// memory (deterministic).  A dot product does not care in which order k is visited as long as both
+// operands agree, so a lane loads 16 contiguous bytes of its row and spreads them over the k-slots
+// of two consecutive MMAs; the X fragment is loaded with the same rule.  Every load of W is a full
+// 16-byte vector and the four lanes of a row cover 64 contiguous bytes.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace mp {
 
+enum { STREAM_F16 = 0, STREAM_I8 = 1 };
+enum { STREAM_EPI_F16 = 0, STREAM_EPI_I32 = 1, STREAM_EPI_SCALED = 2 };
+
 struct StreamParams {
-  const __half* W; long long ldw;     // wide operand, R rows
-  const __half* X; long long ldx;     // narrow operand, T rows
-  __half* out; long long stride_r, stride_t;
-  int R, T, K;                         // K % 8 == 0, rows 16-byte aligned
+  const void* W; long long ldw;       // wide operand, R rows (ld in elements)
+  const void* X; long long ldx;       // narrow operand, T rows
+  void* out; long long stride_r, stride_t;
+  int R, T, K;                         // K * element size % 16 == 0, rows 16-byte aligned
   float alpha, beta;
+  int ialpha, ibeta;
+  // scaled epilogue: channel = W row when chan_on_r, else X row; the other index is the token
+  const float* chan_scale; const float* tok_scale;
+  int chan_scalar, tok_scalar, chan_on_r, out_bf16;
+  const void* bias;                    // in the output type, indexed by channel; may be null
 };
 
 constexpr int kStreamWarps = 8;        // K is split eight ways inside a CTA
-constexpr int kStreamRows = 16;        // W rows per CTA (the M of m16n8k16)
+constexpr int kStreamRows = 16;        // W rows per tile (the M of the warp-level MMA)
 
-__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                             uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_m16n8k32_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-// NT = number of 8-row groups of X covered (T <= 8 * NT); UNROLL = 32-element K blocks in flight per
-// warp; MINB = CTAs that must fit on an SM.  The grid is a whole multiple of the SM count whenever
-// there are enough rows, and CTA i takes the contiguous rows [i*R/G, (i+1)*R/G): every SM then
-// streams the same number of bytes (+- one row), which a fixed 16-row tiling cannot give.
-template <int NT, int UNROLL, int MINB>
+template <int EPI>
+__device__ __forceinline__ void stream_finish(const StreamParams& p, uint32_t accw, int r, int t) {
+  const long long off = (long long)r * p.stride_r + (long long)t * p.stride_t;
+  if constexpr (EPI == STREAM_EPI_F16) {
+    __half* o = reinterpret_cast<__half*>(p.out) + off;
+    float v = p.alpha * __uint_as_float(accw);
+    if (p.beta != 0.0f) v += p.beta * __half2float(*o);
+    *o = __float2half_rn(v);
+  } else if constexpr (EPI == STREAM_EPI_I32) {
+    int* o = reinterpret_cast<int*>(p.out) + off;
+    int v = p.ialpha * (int)accw;
+    if (p.ibeta != 0) v += p.ibeta * (*o);
+    *o = v;
+  } else {
+    const int ch = p.chan_on_r ? r : t, tok = p.chan_on_r ? t : r;
+    const float bs = p.chan_scale[p.chan_scalar ? 0 : ch];
+    const float as = p.tok_scale[p.tok_scalar ? 0 : tok];
+    const float t0 = __fmul_rn(__int2float_rn((int)accw), bs);
+    const float t1 = __fmul_rn(as, t0);
+    uint16_t h = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(t1)) : __half_as_ushort(__float2half_rn(t1));
+    if (p.bias != nullptr) {
+      const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[ch];
+      if (p.out_bf16) {
+        const float s = __bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(b));
+        h = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+      } else {
+        const float s = __half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(b));
+        h = __half_as_ushort(__float2half_rn(s));
+      }
+    }
+    reinterpret_cast<uint16_t*>(p.out)[off] = h;
+  }
+}
+
+// NT = number of 8-row groups of X covered (T <= 8 * NT); UNROLL = K blocks (64 bytes of each row)
+// in flight per warp; MINB = CTAs that must fit on an SM.  The grid is a whole multiple of the SM
+// count whenever there are enough rows, and CTA i takes the contiguous rows [i*R/G, (i+1)*R/G):
+// every SM then streams the same number of bytes (+- one row), which a fixed 16-row tiling cannot
+// give.
+template <int KIND, int EPI, int NT, int UNROLL, int MINB>
 __global__ void __launch_bounds__(kStreamWarps * 32, MINB)
-stream_mma_f16_kernel(const StreamParams p) {
-  __shared__ float red[kStreamWarps][kStreamRows][NT * 8 + 1];
+stream_mma_kernel(const StreamParams p) {
+  __shared__ uint32_t red[kStreamWarps][kStreamRows][NT * 8 + 1];
+  constexpr int kElt = KIND == STREAM_I8 ? 1 : 2;          // bytes per element
+  constexpr int kChunkElems = 16 / kElt;                   // elements per 16-byte chunk
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int r_begin = (int)((long long)blockIdx.x * p.R / gridDim.x);
   const int r_end = (int)((long long)(blockIdx.x + 1) * p.R / gridDim.x);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const char* Wb = reinterpret_cast<const char*>(p.W);
+  const char* Xb = reinterpret_cast<const char*>(p.X);
 
   // Before the previous kernel of the stream is complete nothing may be read for real, but pulling
   // this CTA's rows of W towards L2 is harmless and joins back-to-back launches into one stream.
   {
-    const int row_bytes = p.K * 2;
+    const int row_bytes = p.K * kElt;
     const int lines_per_row = (row_bytes + 127) >> 7;
     for (int i = threadIdx.x; i < (r_end - r_begin) * lines_per_row; i += kStreamWarps * 32) {
       const int r = i / lines_per_row, l = i - r * lines_per_row;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.W + (long long)(r_begin + r) * p.ldw) +
-                                                    (size_t)l * 128));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(Wb + (long long)(r_begin + r) * p.ldw * kElt + (size_t)l * 128));
     }
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  const int chunks = p.K >> 3;                          // 16-byte chunks per row
-  const int blocks = (chunks + 3) >> 2;                 // 32-element K blocks
+  const int chunks = p.K / kChunkElems;                 // 16-byte chunks per row
+  const int blocks = (chunks + 3) >> 2;                 // K blocks of 4 chunks
   const int per_warp = (blocks + kStreamWarps - 1) / kStreamWarps;
   const int blk_begin = warp * per_warp;
   const int blk_end = min(blocks, blk_begin + per_warp);
@@ -76,21 +134,22 @@ stream_mma_f16_kernel(const StreamParams p) {
 #pragma unroll
   for (int nb = 0; nb < NT; ++nb) {
     x_ok[nb] = nb * 8 + g < p.T;
-    xr[nb] = reinterpret_cast<const uint4*>(p.X + (long long)(nb * 8 + g) * p.ldx);
+    xr[nb] = reinterpret_cast<const uint4*>(Xb + (long long)(nb * 8 + g) * p.ldx * kElt);
   }
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
   const bool rows_contig = p.stride_r == 1;
 
   for (int row0 = r_begin; row0 < r_end; row0 += kStreamRows) {
     const bool row_lo_ok = row0 + g < r_end, row_hi_ok = row0 + g + 8 < r_end;
-    const uint4* w_lo = reinterpret_cast<const uint4*>(p.W + (long long)(row0 + g) * p.ldw);
-    const uint4* w_hi = reinterpret_cast<const uint4*>(p.W + (long long)(row0 + g + 8) * p.ldw);
+    const uint4* w_lo = reinterpret_cast<const uint4*>(Wb + (long long)(row0 + g) * p.ldw * kElt);
+    const uint4* w_hi = reinterpret_cast<const uint4*>(Wb + (long long)(row0 + g + 8) * p.ldw * kElt);
 
-    float acc[NT][4];
+    float accf[NT][4];
+    int acci[NT][4];
 #pragma unroll
     for (int nb = 0; nb < NT; ++nb)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[nb][i] = 0.0f;
+      for (int i = 0; i < 4; ++i) { accf[nb][i] = 0.0f; acci[nb][i] = 0; }
 
     for (int b0 = blk_begin; b0 < blk_end; b0 += UNROLL) {
       uint4 lo[UNROLL], hi[UNROLL];
@@ -108,8 +167,13 @@ stream_mma_f16_kernel(const StreamParams p) {
 #pragma unroll
         for (int nb = 0; nb < NT; ++nb) {
           const uint4 xv = ok && x_ok[nb] ? __ldg(xr[nb] + c) : zero4;
-          mma_m16n8k16(acc[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
-          mma_m16n8k16(acc[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          if constexpr (KIND == STREAM_I8) {
+            mma_m16n8k32_s8(acci[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+            mma_m16n8k32_s8(acci[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          } else {
+            mma_m16n8k16_f16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+            mma_m16n8k16_f16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          }
         }
       }
     }
@@ -118,10 +182,13 @@ stream_mma_f16_kernel(const StreamParams p) {
     if (row0 != r_begin) __syncthreads();               // the previous tile's sums have been read
 #pragma unroll
     for (int nb = 0; nb < NT; ++nb) {
-      red[warp][g][nb * 8 + 2 * t4] = acc[nb][0];
-      red[warp][g][nb * 8 + 2 * t4 + 1] = acc[nb][1];
-      red[warp][g + 8][nb * 8 + 2 * t4] = acc[nb][2];
-      red[warp][g + 8][nb * 8 + 2 * t4 + 1] = acc[nb][3];
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = KIND == STREAM_I8 ? (uint32_t)acci[nb][i] : __float_as_uint(accf[nb][i]);
+      red[warp][g][nb * 8 + 2 * t4] = w[0];
+      red[warp][g][nb * 8 + 2 * t4 + 1] = w[1];
+      red[warp][g + 8][nb * 8 + 2 * t4] = w[2];
+      red[warp][g + 8][nb * 8 + 2 * t4 + 1] = w[3];
     }
     __syncthreads();
 
@@ -131,13 +198,19 @@ stream_mma_f16_kernel(const StreamParams p) {
       if (rows_contig) { r = i & (kStreamRows - 1); t = i >> 4; }
       else { t = i % p.T; r = i / p.T; }
       if (row0 + r >= r_end) continue;
-      float v = 0.0f;
+      uint32_t accw;
+      if constexpr (KIND == STREAM_I8) {
+        int v = 0;
 #pragma unroll
-      for (int w = 0; w < kStreamWarps; ++w) v += red[w][r][t];
-      __half* o = p.out + (long long)(row0 + r) * p.stride_r + (long long)t * p.stride_t;
-      v *= p.alpha;
-      if (p.beta != 0.0f) v += p.beta * __half2float(*o);
-      *o = __float2half_rn(v);
+        for (int w = 0; w < kStreamWarps; ++w) v += (int)red[w][r][t];
+        accw = (uint32_t)v;
+      } else {
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kStreamWarps; ++w) v += __uint_as_float(red[w][r][t]);
+        accw = __float_as_uint(v);
+      }
+      stream_finish<EPI>(p, accw, row0 + r, t);
     }
   }
 }

@@ -67,6 +67,7 @@ def lib() -> ctypes.CDLL:
         L.mp_cost_ms.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(cf)]
         L.mp_twin_gemm_fp16.argtypes = [ci, ci, ci, ci, vp, vp, vp, cf, cf, vp]
         L.mp_scaled_mm_i8.argtypes = [ci, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, vp, vp, ci, ci, vp]
+        L.mp_scaled_mm_i8_tile.argtypes = [ci, ci, ci, ci, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, vp, vp, ci, ci, vp]
         L.mp_scaled_mm_predict.argtypes = [ci, ci, ci]
         L.mp_scaled_mm_config.argtypes = [ci, ctypes.POINTER(ci * 4)]
         L.mp_elite_fp16_pids.argtypes = [ctypes.POINTER(ci), ci]

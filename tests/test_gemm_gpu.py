@@ -276,7 +276,7 @@ def test_scaled_mm_known_answer(api):
     assert np.array_equal(out.cpu().numpy(), GOLD["scaled_24x40x64_out"])
 
 
-@pytest.mark.parametrize("M", [1, 8, 47, 160, 700])
+@pytest.mark.parametrize("M", [1, 8, 32, 47, 160, 700])
 @pytest.mark.parametrize("bf16", [False, True])
 @pytest.mark.parametrize("mode", ["tensor", "token_channel", "tensor_channel", "token_tensor"])
 @pytest.mark.parametrize("with_bias", [False, True])
@@ -451,3 +451,43 @@ def test_int8_stream_k_head_bit_exact(api):
     ref = (a.astype(np.float64) @ b.astype(np.float64).T).T.astype(np.int64)
     got = api.gemm_rcc_tile(dev(a), dev(b), 1, 128).cpu().numpy()
     assert np.array_equal(got.astype(np.int64), ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (7, 300, 528), (32, 1000, 1024), (64, 130, 2048), (777, 3, 2048),
+                                    (4096, 24, 512)])
+def test_int8_streaming_kernel_bit_exact(api, oracle, m, n, k):
+    """pid 1101 with INT8 operands: exact int32 accumulators through the warp-level s8 MMA, both mappings."""
+    a = rng.int8_uniform(60, 0, (m, k))
+    b = rng.int8_uniform(60, 1, (n, k))
+    c0 = rng.int8_uniform(60, 2, (n, m)).astype(np.int32) * 37
+    ref = (a.astype(np.float64) @ b.astype(np.float64).T).T.astype(np.int64)
+    got = api.gemm_rcc_pid(dev(a), dev(b), 1101, 1).cpu().numpy()
+    assert np.array_equal(got.astype(np.int64), ref)
+    got_ab = api.gemm_rcc_pid(dev(a), dev(b), 1101, 1, c_nm=dev(c0), alpha=2.0, beta=-3.0).cpu().numpy()
+    assert np.array_equal(got_ab.astype(np.int64), 2 * ref - 3 * c0.astype(np.int64))
+    if min(m, n) <= 32:
+        plan = api.select_plan(api.MP_INT8, m, n, k)
+        assert plan.pid == 1101
+        assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), got)
+
+
+@pytest.mark.parametrize("M,N", [(700, 24), (5, 48), (300, 8)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_scaled_mm_few_channels_bit_exact(api, oracle, M, N, bf16):
+    """Few output channels: the tokens become the streamed rows and the channel index moves to the narrow side."""
+    K = 1024
+    a = rng.int8_uniform(61, 0, (M, K))
+    b = rng.int8_uniform(61, 1, (N, K))
+    sa = rng.uniform(61, 2, (M,), 0.001, 0.02)
+    sb = rng.uniform(61, 3, (N,), 0.001, 0.02)
+    bf = rng.uniform(61, 4, (N,), -1.0, 1.0)
+    if bf16:
+        bias = oracle.bf16_bits_from_f32(bf)
+        tb = dev(bias.view(np.int16)).view(torch.bfloat16)
+    else:
+        bias = bf.astype(np.float16)
+        tb = dev(bias)
+    ref = oracle.scaled_mm_i8(a, b, sa, sb, bias, bf16)
+    out = api.scaled_int8_mm(dev(a), dev(b).t(), dev(sa), dev(sb), tb, torch.bfloat16 if bf16 else torch.float16)
+    got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, ref.view(np.uint16))
