@@ -224,7 +224,7 @@ def extra_sections(api, L, st, dev, peaks):
                              "int8_peak_tops_assumed": int8_peak, "shapes": len(rows),
                              "worst": sorted(rows, key=lambda r: r["frac"])[:3], "best": sorted(rows, key=lambda r: -r["frac"])[:3]}
     # ---- FP16 decode-shaped split-K through pids 400+ (Linear mapping), seed 2
-    rows, fr = [], []
+    rows, fr, fr_sel = [], [], []
     for (N, K) in [(1024, 8192), (4096, 14336), (1024, 28672)]:
         copies = max(2, min(8, (300 << 20) // (N * K * 2)))
         ws = [(torch.randn((N, K), device=dev) * 0.05).half() for _ in range(copies)]
@@ -244,10 +244,18 @@ def extra_sections(api, L, st, dev, peaks):
             byts = 2.0 * (M * K + N * K + M * N)
             roof = max(2.0 * M * N * K / (peaks["tflops"] * 1e12), byts / (peaks["hbm_gbs"] * 1e9))
             fr.append(roof / best[0])
+
+            def call_sel(i):       # the same Linear through the online selector (free to leave the pids-400+ family)
+                rc = L.mp_linear(api.MP_FP16, M, N, K, vp(x.data_ptr()), vp(ws[i % copies].data_ptr()), vp(y.data_ptr()), st)
+                assert rc == 0, L.mp_last_error_string()
+            t_sel = ev_time(call_sel, 12)
+            fr_sel.append(roof / t_sel)
             rows.append({"M": M, "N": N, "K": K, "best_us": round(best[0] * 1e6, 2), "pid": best[1], "split_k": best[2],
-                         "gbs": round(byts / best[0] / 1e9, 1), "frac": round(roof / best[0], 4)})
+                         "gbs": round(byts / best[0] / 1e9, 1), "frac": round(roof / best[0], 4),
+                         "selector_us": round(t_sel * 1e6, 2), "selector_frac": round(roof / t_sel, 4)})
         del ws
-    out["fp16_splitk_decode"] = {"roofline_geomean_frac": geomean(fr), "rows": rows}
+    out["fp16_splitk_decode"] = {"roofline_geomean_frac": geomean(fr), "selector_roofline_geomean_frac": geomean(fr_sel),
+                                 "rows": rows}
     return out
 
 
