@@ -1,0 +1,162 @@
+"""Llama-3-70B-shaped FP16 linear stack, N-sharded column-parallel over the GPUs of one box.
+
+80 layers of four Linear projections (hidden 8192): qkv (N=10240, K=8192), o_proj (8192, 8192),
+gate_up (57344, 8192), down (8192, 28672).  Rank r of g owns rows [r*N/g, (r+1)*N/g) of every
+weight; activations are replicated synthetic inputs of each projection's K.  The outputs of o_proj
+and down (the hidden state every rank needs in full) are reassembled with one all-gather each;
+qkv and gate_up outputs stay sharded.  A step draws one token count M (70 % decode, M in [1, 256];
+30 % prefill, M in [512, 8192]) and runs all 320 GEMMs through `mp_linear` (online selector).
+
+    python -m moonpoly_b200.stack --steps 64                               (1 GPU)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \\
+        --master-port 29511 -m moonpoly_b200.stack --steps 64              (2 GPUs)
+
+Rank 0 prints one JSON line: whole-job TFLOP/s (the FLOPs of the full, unsharded stack divided by
+the step time, max over ranks), the roofline fraction (sum over GEMMs of max(FLOPs / tensor peak,
+bytes / HBM bandwidth) per rank, divided by the measured time) and the share of the all-gathers.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import time
+
+PROJECTIONS = [("qkv", 10240, 8192, False), ("o_proj", 8192, 8192, True),
+               ("gate_up", 57344, 8192, False), ("down", 8192, 28672, True)]   # (name, N, K, gather the output)
+LAYERS = 80
+
+
+def draw_tokens(seed: int, steps: int) -> list:
+    """Token count per step: with probability 0.7 uniform in [1, 256], else uniform in [512, 8192]."""
+    from . import rng
+    return [min(8192, m) for m in rng.mixed_batch_sizes(seed, rng.STREAM_SHAPES, steps)]
+
+
+def load_peaks(root: str) -> dict:
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"tflops": float(d["bf16_tflops_sustained"]), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured (sustained)"}
+    return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-gather", action="store_true", help="skip the all-gathers (GEMM time only)")
+    args = ap.parse_args()
+
+    import torch
+    from . import api
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
+        dist.init_process_group("nccl", device_id=dev)
+
+    L = api.lib()
+    vp = ctypes.c_void_p
+    stream = torch.cuda.current_stream()
+    st = vp(stream.cuda_stream)
+
+    # resident layers: as many distinct weight sets as fit in half of the free memory (cycled over the 80 layers)
+    shard = [(name, n // world, k, gather) for (name, n, k, gather) in PROJECTIONS]
+    per_layer = sum(n * k * 2 for (_, n, k, _) in shard)
+    free, _ = torch.cuda.mem_get_info(dev)
+    resident = max(1, min(args.layers, int(0.5 * free / per_layer)))
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4 + 1000 * rank)
+    weights = [[torch.empty((n, k), dtype=torch.float16, device=dev).normal_(0.0, 0.02, generator=gen)
+                for (_, n, k, _) in shard] for _ in range(resident)]
+    max_m = 8192
+    x_in = {k: torch.empty((max_m, k), dtype=torch.float16, device=dev).normal_(0.0, 1.0, generator=gen)
+            for k in sorted({k for (_, _, k, _) in shard})}
+    y_loc = [torch.empty((max_m * n,), dtype=torch.float16, device=dev) for (_, n, _, _) in shard]
+    y_all = [torch.empty((world * max_m * n,), dtype=torch.float16, device=dev) if g else None for (_, n, _, g) in shard]
+
+    tokens = draw_tokens(4, args.warmup + args.steps)
+
+    def step(m: int, gather_events=None) -> None:
+        for layer in range(args.layers):
+            ws = weights[layer % resident]
+            for j, (_, n, k, gather) in enumerate(shard):
+                rc = L.mp_linear(api.MP_FP16, m, n, k, vp(x_in[k].data_ptr()), vp(ws[j].data_ptr()), vp(y_loc[j].data_ptr()), st)
+                if rc:
+                    raise RuntimeError(L.mp_last_error_string().decode())
+                if gather and dist is not None and not args.no_gather:
+                    dist.all_gather_into_tensor(y_all[j][: world * m * n], y_loc[j][: m * n])
+
+    for i in range(args.warmup):
+        step(tokens[i])
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        evs[i][0].record(stream)
+        step(tokens[args.warmup + i])
+        evs[i][1].record(stream)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    if dist is not None:
+        dist.barrier()
+    assert api.device_status() == 0
+    ms = torch.tensor([a.elapsed_time(b) for a, b in evs], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = ms.tolist()
+
+    if rank == 0:
+        root = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", ".."))
+        peaks = load_peaks(root)
+        ms_steps = tokens[args.warmup:]
+        flops_full = [2.0 * m * sum(n * k for (_, n, k, _) in PROJECTIONS) * args.layers for m in ms_steps]
+        roof_ms = []
+        for m in ms_steps:
+            t = 0.0
+            for (_, n, k, _) in shard:
+                f = 2.0 * m * n * k
+                b = 2.0 * (m * k + n * k + m * n)
+                t += max(f / (peaks["tflops"] * 1e12), b / (peaks["hbm_gbs"] * 1e9))
+            roof_ms.append(t * args.layers * 1e3)
+        decode = [i for i, m in enumerate(ms_steps) if m <= 256]
+        prefill = [i for i, m in enumerate(ms_steps) if m > 256]
+
+        def agg(idx):
+            if not idx:
+                return None
+            return {"steps": len(idx), "ms_per_step": sum(ms[i] for i in idx) / len(idx),
+                    "tflops": sum(flops_full[i] for i in idx) / (sum(ms[i] for i in idx) * 1e-3) / 1e12,
+                    "roofline_frac": sum(roof_ms[i] for i in idx) / sum(ms[i] for i in idx)}
+        line = {"metric": "llama70b_fp16_linear_stack_tflops", "value": sum(flops_full) / (sum(ms) * 1e-3) / 1e12,
+                "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": sum(ms) / len(ms), "higher_is_better": True, "scaling": "strong", "dtype": "f16",
+                "data": "synthetic", "roofline_frac": sum(roof_ms) / sum(ms), "decode": agg(decode), "prefill": agg(prefill),
+                "host_wall_ms_per_step": wall / args.steps * 1e3,
+                "config": {"workload": "Llama-3-70B-shaped FP16 linear stack", "layers": args.layers, "resident_layers": resident,
+                           "parallelism": f"column-parallel x{world}, all-gather after o_proj and down" if world > 1 and not args.no_gather
+                           else f"column-parallel x{world}, no collective", "peaks": peaks,
+                           "tokens_min_max": [min(ms_steps), max(ms_steps)]}}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..")))
+    main()

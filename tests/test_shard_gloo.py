@@ -72,3 +72,16 @@ def test_column_parallel_linear_gloo(tmp_path, world, n_total):
     port = _free_port()
     mp.spawn(_worker, args=(world, port, n_total, str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_stack_token_draws_follow_the_decode_prefill_mix():
+    from moonpoly_b200 import stack
+    a = stack.draw_tokens(4, 2000)
+    assert a == stack.draw_tokens(4, 2000) and a != stack.draw_tokens(5, 2000)
+    decode = [m for m in a if m <= 256]
+    prefill = [m for m in a if m >= 512]
+    assert len(decode) + len(prefill) == len(a)
+    assert 0.66 < len(decode) / len(a) < 0.74
+    assert min(a) >= 1 and max(a) <= 8192
+    n_total = sum(n * k for (_, n, k, _) in stack.PROJECTIONS)
+    assert n_total == (10240 + 8192 + 57344) * 8192 + 8192 * 28672
