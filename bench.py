@@ -254,6 +254,25 @@ def extra_sections(api, L, st, dev, peaks):
                          "gbs": round(byts / best[0] / 1e9, 1), "frac": round(roof / best[0], 4),
                          "selector_us": round(t_sel * 1e6, 2), "selector_frac": round(roof / t_sel, 4)})
         del ws
+    # ---- host cost of a selection (mp_select_plan through ctypes; the empty-call cost of ctypes is measured with
+    # mp_num_sms and subtracted): warm = the same shape again (plan cache hit), cold = shapes never seen before
+    plan = api.Plan()
+    pref = ctypes.byref(plan)
+    n_calls = 20000
+    t0 = time.perf_counter()
+    for i in range(n_calls):
+        L.mp_num_sms()
+    t_empty = (time.perf_counter() - t0) / n_calls
+    t0 = time.perf_counter()
+    for i in range(n_calls):
+        L.mp_select_plan(api.MP_FP16, 77, 4096, 4096, pref)
+    t_warm = (time.perf_counter() - t0) / n_calls
+    t0 = time.perf_counter()
+    for i in range(n_calls):
+        L.mp_select_plan(api.MP_FP16, 3 + i, 4104 + 8 * (i % 97), 4096, pref)
+    t_cold = (time.perf_counter() - t0) / n_calls
+    out["selector_host_us"] = {"warm": round(max(0.0, t_warm - t_empty) * 1e6, 3), "cold": round(max(0.0, t_cold - t_empty) * 1e6, 3),
+                               "ctypes_empty_call": round(t_empty * 1e6, 3), "calls": n_calls}
     out["fp16_splitk_decode"] = {"roofline_geomean_frac": geomean(fr), "selector_roofline_geomean_frac": geomean(fr_sel),
                                  "rows": rows}
     return out
