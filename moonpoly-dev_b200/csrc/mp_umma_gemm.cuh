@@ -221,6 +221,33 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
       }
     }
   }
+  if constexpr (EPI == EPI_F16) {
+    // rows of D are the contiguous index of the output (the 32 lanes of a warp write 64 adjacent
+    // bytes per column): one pointer walks the 16 columns, no per-element index arithmetic
+    if (p.out_stride_p == 1 && p.beta == 0.0f) {
+      __half* o = reinterpret_cast<__half*>(p.out) + pi + (long long)q0 * p.out_stride_q;
+      const long long step = p.out_stride_q;
+      if (valid == 16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[(long long)j * step] = __float2half_rn(p.alpha * __uint_as_float(r[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (j < valid) o[(long long)j * step] = __float2half_rn(p.alpha * __uint_as_float(r[j]));
+      }
+      return;
+    }
+  }
+  if constexpr (EPI == EPI_I32) {
+    if (p.out_stride_p == 1 && p.ibeta == 0) {
+      int* o = reinterpret_cast<int*>(p.out) + pi + (long long)q0 * p.out_stride_q;
+      const long long step = p.out_stride_q;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < valid) o[(long long)j * step] = p.ialpha * (int)r[j];
+      return;
+    }
+  }
   if constexpr (EPI == EPI_I32) {
     if (p.out_stride_q == 1 && valid == 16 && p.ibeta == 0) {
       int* o = reinterpret_cast<int*>(p.out) + (long long)pi * p.out_stride_p + q0;
