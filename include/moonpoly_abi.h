@@ -100,9 +100,11 @@ int mp_gemm_rcc_pid_static_scratch(int dtype, int pid, int split_k, int m, int n
  * an explicit tile instead of a pid.  orient 0 puts the rows of A on the 128-row UMMA-M side and
  * tiles n by bn; orient 1 puts the rows of B there and tiles m by bn.  bn: multiple of 16 in
  * [16,256].  kc: K blocks (of 128 bytes) per pipeline stage, 1, 2 or 4; 0 lets the library choose.
- * orient 2 and 3 select the FP16 streaming kernels instead (CUDA-core, narrow side <= 8 rows;
- * warp-MMA, narrow side <= 64 rows); bn, kc and split_k are ignored there and MP_ERR_INVALID_ARG
- * is returned when the problem does not fit the kernel.
+ * orient 2 and 3 select the streaming kernels instead (2: FP16 CUDA-core, narrow side <= 8 rows;
+ * 3: FP16 / INT8 warp-MMA, narrow side <= 64 rows); bn, kc and split_k are ignored there and
+ * MP_ERR_INVALID_ARG is returned when the problem does not fit the kernel.  orient 4 and 5 are
+ * orient 0 and 1 with 256-row tiles (two 128-row halves share every bn-wide tile of the other
+ * operand; single K slice).
  * The refit tool (per-tile k_iter sweeps) and the profiling driver use it. */
 int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k,
                      const void* A, const void* B, void* C, float alpha, float beta, void* stream);

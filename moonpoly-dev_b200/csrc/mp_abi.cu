@@ -173,6 +173,7 @@ struct Problem {
 
 struct Launch {
   int orient = 0, bn = 128, split_k = 1;
+  int xm = 1;            // 2: 256 x bn tiles (two 128-row halves of X share every Y tile); single slice, one region only
   int kc = 0;                 // K blocks per stage; 0 = choose
   int split_n = 0, bn1 = 0;   // twin: second region [split_n, n) with its own UMMA-N
   void* workspace = nullptr; size_t workspace_bytes = 0;
@@ -288,7 +289,9 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.out = p.C;
   up.out_stride_p = swap ? p.c_stride_n : p.c_stride_m;
   up.out_stride_q = swap ? p.c_stride_m : p.c_stride_n;
-  up.tiles_p = (up.P + kUmmaM - 1) / kUmmaM;
+  const int xm = (l.xm == 2 && l.split_n <= 0) ? 2 : 1;
+  up.xm = xm;
+  up.tiles_p = (up.P + kUmmaM * xm - 1) / (kUmmaM * xm);
   up.group_p = 8;
   int bn_max = l.bn;
   if (l.split_n > 0) {
@@ -307,13 +310,13 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   const int kb_elems = p.dtype == MP_INT8 ? 128 : 64;
   up.kb_total = (p.k + kb_elems - 1) / kb_elems;
   // K blocks per stage: wide boxes move far more bytes per TMA instruction; keep >= 3 stages
-  const int kb_bytes = kXTileBytes + bn_max * kRowBytes;
+  const int kb_bytes = xm * kXTileBytes + bn_max * kRowBytes;
   const int smem_for_stages = kSmemBudget - 1024 - 256;
   int kc = l.kc;
   if (kc <= 0) kc = (smem_for_stages / (4 * kb_bytes) >= 3) ? 4 : (smem_for_stages / (2 * kb_bytes) >= 3) ? 2 : 1;
   while (kc > 1 && smem_for_stages / (kc * kb_bytes) < 2) kc >>= 1;
   // at most 31 slices: the reduction tracks claimed shares in one 32-bit mask (one bit seals it)
-  int S = std::max(1, std::min(std::min(l.split_k, 31), up.kb_total));
+  int S = std::max(1, std::min(std::min(xm == 2 ? 1 : l.split_k, 31), up.kb_total));
   up.kb_per_slice = ((up.kb_total + S - 1) / S + kc - 1) / kc * kc;     // slices start on a stage boundary
   S = (up.kb_total + up.kb_per_slice - 1) / up.kb_per_slice;              // every slice non-empty
   up.split_k = S;
@@ -346,7 +349,7 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   // completed through the split-K scratch, and the other T - r tiles follow as whole waves.  Runs
   // are never shorter than a quarter of K, so a tile has at most ~5 contributors.
   size_t sk_cb = 0, sk_pb = 0;
-  if (g_use_streamk.load(std::memory_order_relaxed) && S == 1 && up.num_regions == 1 && up.total_tiles > grid && grid == d->sms) {
+  if (g_use_streamk.load(std::memory_order_relaxed) && xm == 1 && S == 1 && up.num_regions == 1 && up.total_tiles > grid && grid == d->sms) {
     const int r = up.total_tiles % grid;
     // measured on B200: pays while the remainder is at most half a wave (r/G = 0.30: -17 %, 0.46: -5 %,
     // 0.59 and above: the completion traffic costs more than the idle SMs did)
@@ -386,7 +389,7 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
 
   CUtensorMap tx, ty0, ty1;
   const int map_kc = up.wide ? up.kc : 0;
-  if (int rc = make_tmap(&tx, p.dtype, X, up.P, p.k, ldx, kUmmaM, map_kc)) return rc;
+  if (int rc = make_tmap(&tx, p.dtype, X, up.P, p.k, ldx, kUmmaM * xm, map_kc)) return rc;
   if (int rc = make_tmap(&ty0, p.dtype, Y, up.Q, p.k, ldy, up.reg[0].bn, map_kc)) return rc;
   if (up.num_regions == 2) {
     if (int rc = make_tmap(&ty1, p.dtype, Y, up.Q, p.k, ldy, up.reg[1].bn, map_kc)) return rc;
@@ -622,7 +625,7 @@ int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, c
     return run_umma(p, lf, stream);
   }
   Launch l;
-  l.orient = c.orient; l.bn = c.bn; l.split_k = std::max(1, split_k);
+  l.orient = c.orient; l.bn = c.bn; l.split_k = std::max(1, split_k); l.xm = c.xm == 2 ? 2 : 1;
   l.workspace = ws; l.workspace_bytes = ws_bytes;
   return run_umma(p, l, stream);
 }
@@ -741,13 +744,15 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
     if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16 or INT8, min(m,n) <= 64 and 16-byte aligned rows");
     return run_stream(pg, reinterpret_cast<cudaStream_t>(stream));
   }
+  const int xm = (orient == 4 || orient == 5) ? 2 : 1;       // orient 4 / 5: orient 0 / 1 with 256-row tiles
+  if (xm == 2) orient -= 4;
   if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0 || (kc != 0 && kc != 1 && kc != 2 && kc != 4))
     return fail(MP_ERR_INVALID_ARG, "bad tile: orient=%d bn=%d kc=%d", orient, bn, kc);
   if (m == 0 || n == 0) return MP_OK;
   const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
   if (!tma_compatible(p)) return fail(MP_ERR_UNALIGNED_K, "operands do not meet the 16-byte alignment of the tensor path");
   Launch l;
-  l.orient = orient; l.bn = bn; l.kc = kc; l.split_k = std::max(1, split_k);
+  l.orient = orient; l.bn = bn; l.kc = kc; l.split_k = std::max(1, split_k); l.xm = xm;
   return run_umma(p, l, reinterpret_cast<cudaStream_t>(stream));
 }
 

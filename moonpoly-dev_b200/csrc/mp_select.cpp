@@ -319,6 +319,12 @@ TileCfg tile_cfg(int dtype, int pid) {
       if (bn < 16 || bn > 256) return c;
       c.valid = true; c.orient = (pid - 1000) >> 5; c.bn = bn; c.align = 8; c.split_capable = true;
       return c;
+    } else if (pid >= 1200 && pid < 1264) {
+      // library-native 256-row tiles: pid = 1200 + 32*orient + bn/16 (single slice only)
+      const int bn = ((pid - 1200) & 31) * 16;
+      if (bn < 16 || bn > 256) return c;
+      c.valid = true; c.orient = (pid - 1200) >> 5; c.bn = bn; c.align = 8; c.split_capable = false; c.xm = 2;
+      return c;
     } else if (in_list(kFp16Explicit, 12, pid)) {
       c.valid = true; c.orient = 0; c.bn = 16; c.align = 8; c.split_capable = true;
       return c;
@@ -357,8 +363,9 @@ void pid_tile_meta(int dtype, int pid, int out[3]) {
   if (dtype == MP_FP32) { out[0] = c.tj; out[1] = c.ti; out[2] = 16; return; }
   if (c.orient == 3) { out[0] = 16; out[1] = 64; out[2] = 32; return; }     // streaming kernel: 16 streamed rows per CTA x up to 64 rows
   if (c.orient == 2) { out[0] = 16; out[1] = 8; out[2] = 1024; return; }   // skinny kernel: 16 streamed rows per CTA x up to 8 rows
-  out[0] = c.orient == 0 ? c.bn : 128;    // pm: tile over RCC n
-  out[1] = c.orient == 0 ? 128 : c.bn;    // pn: tile over RCC m
+  const int rows = c.xm == 2 ? 256 : 128;
+  out[0] = c.orient == 0 ? c.bn : rows;   // pm: tile over RCC n
+  out[1] = c.orient == 0 ? rows : c.bn;   // pn: tile over RCC m
   out[2] = dtype == MP_INT8 ? 128 : 64;
 }
 
@@ -366,12 +373,13 @@ namespace {
 // pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
 struct PidMeta { TileCfg cfg; int meta[3]; };
 struct MetaTables {
-  PidMeta fp16[440], int8[46], fp32[40], native[64], skinny, streaming, streaming_i8;
+  PidMeta fp16[440], int8[46], fp32[40], native[64], native256[64], skinny, streaming, streaming_i8;
   MetaTables() {
     skinny.cfg = tile_cfg(MP_FP16, 1100); pid_tile_meta(MP_FP16, 1100, skinny.meta);
     streaming.cfg = tile_cfg(MP_FP16, 1101); pid_tile_meta(MP_FP16, 1101, streaming.meta);
     streaming_i8.cfg = tile_cfg(MP_INT8, 1101); pid_tile_meta(MP_INT8, 1101, streaming_i8.meta);
     for (int p = 0; p < 64; ++p) { native[p].cfg = tile_cfg(MP_FP16, 1000 + p); pid_tile_meta(MP_FP16, 1000 + p, native[p].meta); }
+    for (int p = 0; p < 64; ++p) { native256[p].cfg = tile_cfg(MP_FP16, 1200 + p); pid_tile_meta(MP_FP16, 1200 + p, native256[p].meta); }
     for (int p = 0; p < 440; ++p) { fp16[p].cfg = tile_cfg(MP_FP16, p); pid_tile_meta(MP_FP16, p, fp16[p].meta); }
     for (int p = 0; p < 46; ++p) { int8[p].cfg = tile_cfg(MP_INT8, p); pid_tile_meta(MP_INT8, p, int8[p].meta); }
     for (int p = 0; p < 40; ++p) { fp32[p].cfg = tile_cfg(MP_FP32, p); pid_tile_meta(MP_FP32, p, fp32[p].meta); }
@@ -384,6 +392,7 @@ const PidMeta* pid_meta(int dtype, int pid) {
     if (pid == 1100) return &t.skinny;
     if (pid == 1101) return &t.streaming;
     if (pid >= 1000 && pid < 1064) return t.native[pid - 1000].cfg.valid ? &t.native[pid - 1000] : nullptr;
+    if (pid >= 1200 && pid < 1264) return t.native256[pid - 1200].cfg.valid ? &t.native256[pid - 1200] : nullptr;
     return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
   }
   if (dtype == MP_INT8) return pid == 1101 ? &t.streaming_i8 : pid < 46 ? &t.int8[pid] : nullptr;

@@ -23,6 +23,7 @@ struct TileCfg {
   int align;          // k must be a multiple of this (the reference's per-pid contract)
   bool split_capable; // member of the reference's split-K capable set
   int ti, tj;         // FP32 only
+  int xm;             // 2: 256-row tiles (two 128-row halves on the UMMA-M side share each bn-wide tile); else 1
 };
 
 TileCfg tile_cfg(int dtype, int pid);

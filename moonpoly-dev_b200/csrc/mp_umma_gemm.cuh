@@ -68,7 +68,8 @@ struct UmmaParams {
   int kc;             // K blocks per pipeline stage (1, 2 or 4)
   int wide;           // 1: tensor maps are 3-D [K/kb][rows][kb] and one load brings kc K blocks
   int stages;
-  int stage_bytes;    // kc * (kXTileBytes + bn_max * kRowBytes)
+  int xm;             // 128-row halves of X per tile: 1, or 2 = 256 x bn tiles (two accumulators share every Y tile)
+  int stage_bytes;    // kc * (xm * kXTileBytes + bn_max * kRowBytes)
   int group_p;        // raster: tiles are walked in groups of `group_p` rows of tiles
   int prefetch_kb;    // K blocks of a CTA's first unit to prefetch into L2 before the dependency wait
   void* out;
@@ -400,7 +401,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       if (UnitWalk(p).next(p, u)) {
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
-        const int prow = u.tp * kUmmaM, qrow = r.q_begin + u.tq * r.bn;
+        const int prow = u.tp * kUmmaM * p.xm, qrow = r.q_begin + u.tq * r.bn;
         const int kb_lim = min(u.kb1, u.kb0 + p.prefetch_kb);
         for (int kb = u.kb0; kb < kb_lim; kb += p.kc) {
           if (p.wide) {
@@ -422,9 +423,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       while (ok && walk.next(p, u)) {
         const Region& r = p.reg[u.region];
         const CUtensorMap* tmY = u.region ? &tmY1 : &tmY0;
-        const uint32_t tx = (uint32_t)(p.kc * (kXTileBytes + r.bn * kRowBytes));
-        const uint32_t y_off = (uint32_t)(p.kc * kXTileBytes);
-        const int prow = u.tp * kUmmaM;
+        const uint32_t x_bytes = (uint32_t)(p.xm * kXTileBytes);      // X rows of one K block
+        const uint32_t tx = (uint32_t)p.kc * (x_bytes + (uint32_t)(r.bn * kRowBytes));
+        const uint32_t y_off = (uint32_t)p.kc * x_bytes;
+        const int prow = u.tp * kUmmaM * p.xm;
         const int qrow = r.q_begin + u.tq * r.bn;
         for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
           const int s = (int)(it % (uint32_t)stages);
@@ -439,7 +441,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             // 2-D maps (K not a multiple of one K block): one box per K block; boxes past the
             // end of K are filled with zeros by the TMA unit and still count their bytes
             for (int c = 0; c < p.kc; ++c) {
-              tma_load_2d(a_dst + (uint32_t)(c * kXTileBytes), &tmX, full_bar(s), (kb + c) * kElemsPerKb, prow);
+              tma_load_2d(a_dst + (uint32_t)c * x_bytes, &tmX, full_bar(s), (kb + c) * kElemsPerKb, prow);
               tma_load_2d(a_dst + y_off + (uint32_t)(c * r.bn * kRowBytes), tmY, full_bar(s),
                           (kb + c) * kElemsPerKb, qrow);
             }
@@ -465,8 +467,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       UnitCoord u;
       for (; ok && walk.next(p, u); ++ui) {
         const Region& r = p.reg[u.region];
-        const uint32_t buf = ui & 1u;
-        const uint32_t use = ui >> 1;
+        // 256-row tiles keep two accumulators (all 512 TMEM columns): one buffer, no overlap with the drain
+        const uint32_t buf = p.xm == 2 ? 0u : (ui & 1u);
+        const uint32_t use = p.xm == 2 ? ui : (ui >> 1);
         if (!mbar_wait(tempty_bar((int)buf), (use & 1u) ^ 1u, status, MP_DEV_TIMEOUT_MMA_TMEM)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * (uint32_t)kMaxBN;
@@ -480,16 +483,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           if (ui == 0 && kb + p.kc >= u.kb1) MP_TRACE_MARK(4);
           tc_fence_after();
           const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
-          const uint32_t b_addr = a_addr + (uint32_t)(p.kc * kXTileBytes);
+          const uint32_t x_bytes = (uint32_t)(p.xm * kXTileBytes);
+          const uint32_t b_addr = a_addr + (uint32_t)p.kc * x_bytes;
           const int nc = min(p.kc, u.kb1 - kb);     // K blocks of this stage that lie inside the slice
           for (int c = 0; c < nc; ++c) {
+            for (int h = 0; h < p.xm; ++h) {       // the halves of X share the Y tile of this K block
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
-              const uint64_t ad = umma_smem_desc_sw128(a_addr + (uint32_t)(c * kXTileBytes) + 32u * kk);
-              const uint64_t bd = umma_smem_desc_sw128(b_addr + (uint32_t)(c * r.bn * kRowBytes) + 32u * kk);
-              const uint32_t acc = (kb > u.kb0 || c > 0 || kk > 0) ? 1u : 0u;
-              if constexpr (KIND == KIND_I8) umma_i8(d_tmem, ad, bd, idesc, acc);
-              else umma_f16(d_tmem, ad, bd, idesc, acc);
+              for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
+                const uint64_t ad = umma_smem_desc_sw128(a_addr + (uint32_t)c * x_bytes + (uint32_t)(h * kXTileBytes) + 32u * kk);
+                const uint64_t bd = umma_smem_desc_sw128(b_addr + (uint32_t)(c * r.bn * kRowBytes) + 32u * kk);
+                const uint32_t acc = (kb > u.kb0 || c > 0 || kk > 0) ? 1u : 0u;
+                if constexpr (KIND == KIND_I8) umma_i8(d_tmem + (uint32_t)(h * kMaxBN), ad, bd, idesc, acc);
+                else umma_f16(d_tmem + (uint32_t)(h * kMaxBN), ad, bd, idesc, acc);
+              }
             }
           }
           tc_commit(empty_bar(s));      // stage reusable once these MMAs have read it
@@ -507,21 +513,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     UnitCoord u;
     for (; ok && walk.next(p, u); ++ui) {
       const Region& r = p.reg[u.region];
-      const uint32_t buf = ui & 1u;
-      const uint32_t use = ui >> 1;
+      const uint32_t buf = p.xm == 2 ? 0u : (ui & 1u);
+      const uint32_t use = p.xm == 2 ? ui : (ui >> 1);
       if (!mbar_wait(tfull_bar((int)buf), use & 1u, status, MP_DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
       if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(5);
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + buf * (uint32_t)kMaxBN + ((uint32_t)(quad * 32) << 16);
+      uint32_t t_addr = tmem_base + buf * (uint32_t)kMaxBN + ((uint32_t)(quad * 32) << 16);
       const int row_in_tile = quad * 32 + lane;
-      const int pi = u.tp * kUmmaM + row_in_tile;
+      int pi = u.tp * kUmmaM * p.xm + row_in_tile;
       const int q_tile0 = r.q_begin + u.tq * r.bn;
       const int q_end = min(r.q_end, q_tile0 + r.bn);
 
       const int S = u.nslices;               // slices that make up this unit's tile
       if (S == 1) {
         // two 16-column TMEM loads are in flight before the wait: the round trip, not the data,
-        // is what a load costs
+        // is what a load costs.  256-row tiles drain their second accumulator (the tile's rows
+        // 128..255, TMEM columns 256..511) the same way.
+        for (int h = 0; h < p.xm; ++h, t_addr += (uint32_t)kMaxBN, pi += kUmmaM) {
         if constexpr (EPI == EPI_SCALED) {        // the scaled epilogue has no registers to spare
           for (int c0 = 0; c0 < r.bn; c0 += 16) {
             uint32_t v[16];
@@ -539,6 +547,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             store_chunk16<EPI>(p, v[0], pi, q_tile0 + c0, q_end);
             if (two) store_chunk16<EPI>(p, v[1], pi, q_tile0 + c0 + 16, q_end);
           }
+        }
         }
         tc_fence_before();
         __syncwarp();

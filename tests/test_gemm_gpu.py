@@ -491,3 +491,32 @@ def test_scaled_mm_few_channels_bit_exact(api, oracle, M, N, bf16):
     out = api.scaled_int8_mm(dev(a), dev(b).t(), dev(sa), dev(sb), tb, torch.bfloat16 if bf16 else torch.float16)
     got = out.view(torch.int16).cpu().numpy().view(np.uint16)
     assert np.array_equal(got, ref.view(np.uint16))
+
+
+@pytest.mark.parametrize("orient,bn,m,n,k", [(4, 256, 600, 520, 256), (5, 256, 520, 600, 320), (4, 128, 257, 300, 1096),
+                                              (5, 192, 1000, 1300, 512), (4, 64, 2500, 200, 2048)])
+def test_fp16_256_row_tiles_exact(api, orient, bn, m, n, k):
+    """256-row tiles (two 128-row halves share every bn-wide tile of the other operand; orient 4 / 5 of the
+    tuning entry, pids 1200+): exact on integer-valued inputs, ragged edges in both dimensions, alpha/beta."""
+    a = rng.small_ints(70, 0, (m, k), lo=-1, hi=1)
+    b = rng.small_ints(70, 1, (n, k))
+    ref = _exact_ref(a, b)
+    A, B = dev(a), dev(b)
+    got = api.gemm_rcc_tile(A, B, orient, bn).cpu().numpy()
+    assert np.array_equal(got, ref.astype(np.float16))
+    pid = 1200 + 32 * (orient - 4) + bn // 16
+    assert np.array_equal(api.gemm_rcc_pid(A, B, pid, 1).cpu().numpy(), got)
+    c0 = rng.small_ints(70, 2, (n, m)).astype(np.float16)
+    got_ab = api.gemm_rcc_tile(A, B, orient, bn, c_nm=dev(c0).clone(), alpha=2.0, beta=-1.0).cpu().numpy()
+    assert np.array_equal(got_ab, (2.0 * ref - c0.astype(np.float64)).astype(np.float16))
+    assert api.device_status() == 0
+
+
+def test_int8_256_row_tiles_bit_exact(api):
+    m, n, k = 700, 900, 1024
+    a = rng.int8_uniform(71, 0, (m, k))
+    b = rng.int8_uniform(71, 1, (n, k))
+    ref = (a.astype(np.float64) @ b.astype(np.float64).T).T.astype(np.int64)
+    for orient in (4, 5):
+        got = api.gemm_rcc_tile(dev(a), dev(b), orient, 256).cpu().numpy()
+        assert np.array_equal(got.astype(np.int64), ref)

@@ -57,9 +57,9 @@ def test_measured_plan_table(api, monkeypatch):
     default, as the reference's decode selector does) and name library-native tiles (pid >= 1000)."""
     for (m, n, k) in [(1, 4096, 4096), (3, 4096, 4096), (4096, 5, 4096), (600, 4096, 4096), (599, 4096, 4096)]:
         plan = api.select_plan(api.MP_FP16, m, n, k)
-        assert 1000 <= plan.pid < 1064 or plan.pid in (1100, 1101), (m, n, k, plan)
+        assert 1000 <= plan.pid < 1064 or 1200 <= plan.pid < 1264 or plan.pid in (1100, 1101), (m, n, k, plan)
         tile, align = api.pid_info(api.MP_FP16, plan.pid)
-        assert align == 8 and (128 in tile[:2] or plan.pid in (1100, 1101))
+        assert align == 8 and (128 in tile[:2] or 256 in tile[:2] or plan.pid in (1100, 1101))
         assert plan.estimated_ms > 0
     # aligned and unaligned m land in different rows of the same bucket
     a = api.select_plan(api.MP_FP16, 1024, 4096, 4096)
@@ -148,15 +148,19 @@ def test_selection_overhead_budget(api):
     for _ in range(4000):
         L.mp_launch_count()
     base = (time.perf_counter() - t0) / 4000
-    t0 = time.perf_counter()
-    for m, n, k in shapes:
-        fn(0, m, n, k, ctypes.byref(p))
-    cold = (time.perf_counter() - t0) / len(shapes) - base
-    t0 = time.perf_counter()
-    for _ in range(4):
-        for m, n, k in shapes[:500]:
-            fn(0, m, n, k, ctypes.byref(p))
-    warm = (time.perf_counter() - t0) / 2000 - base
+    # 4000 distinct shapes against a 1024-entry plan cache: every pass is (almost) all first sights.  Best of three
+    # passes, so a busy host does not fail the test
+    cold = warm = float("inf")
+    for rep in range(3):
+        t0 = time.perf_counter()
+        for m, n, k in shapes:
+            fn(0, m + rep, n, k, ctypes.byref(p))
+        cold = min(cold, (time.perf_counter() - t0) / len(shapes) - base)
+        t0 = time.perf_counter()
+        for _ in range(4):
+            for m, n, k in shapes[:500]:
+                fn(0, m, n, k, ctypes.byref(p))
+        warm = min(warm, (time.perf_counter() - t0) / 2000 - base)
     print(f"selection: cold {cold * 1e6:.2f} us, memoised {warm * 1e6:.2f} us (ctypes overhead {base * 1e6:.2f} us removed)")
     assert cold < 15e-6          # generous on a loaded CI box; the budget is 5 us
     assert warm < 5e-6
