@@ -148,7 +148,8 @@ int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t*
  * fixed CUTLASS instantiations): same arguments as mp_scaled_mm_i8 behind an explicit kernel choice.
  * orient 0 puts the tokens (rows of A) on the 128-row UMMA-M side and tiles the channels by bn,
  * orient 1 puts the channels (rows of B_nk) there and tiles the tokens by bn, orient 3 selects the
- * streaming kernel (narrow side <= 64 rows; bn and split_k ignored).  The refit tool uses it to
+ * streaming kernel (narrow side <= 64 rows; bn and split_k ignored), orient 4 / 5 are orient 0 / 1
+ * with 256-row tiles.  The refit tool uses it to
  * measure the scaled-matmul plan table. */
 int mp_scaled_mm_i8_tile(int orient, int bn, int split_k, int M, int N, int K, const int8_t* A, int lda,
                          const int8_t* B_nk, int ldb, const float* a_scales, int a_scalar,

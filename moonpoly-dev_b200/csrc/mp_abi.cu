@@ -834,7 +834,7 @@ int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t*
   const mp::ScaledCfg cfg = mp::scaled_mm_select(M, N, K);
   if (cfg.stream && stream_compatible(p)) return run_stream(p, s);
   Launch l;
-  l.orient = cfg.orient; l.bn = cfg.bn; l.split_k = cfg.split_k;
+  l.orient = cfg.orient; l.bn = cfg.bn; l.split_k = cfg.split_k; l.xm = cfg.xm;
   return run_umma(p, l, s);
 }
 
@@ -851,10 +851,12 @@ int mp_scaled_mm_i8_tile(int orient, int bn, int split_k, int M, int N, int K, c
     if (!stream_compatible(p)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs min(M,N) <= 64");
     return run_stream(p, s);
   }
+  const int xm = (orient == 4 || orient == 5) ? 2 : 1;       // orient 4 / 5: orient 0 / 1 with 256-row tiles
+  if (xm == 2) orient -= 4;
   if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0)
     return fail(MP_ERR_INVALID_ARG, "bad tile: orient=%d bn=%d", orient, bn);
   Launch l;
-  l.orient = orient; l.bn = bn; l.split_k = std::max(1, split_k);
+  l.orient = orient; l.bn = bn; l.split_k = std::max(1, split_k); l.xm = xm;
   return run_umma(p, l, s);
 }
 

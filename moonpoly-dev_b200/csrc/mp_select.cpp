@@ -449,7 +449,8 @@ struct PlanRow { int m_lo, m_hi, n_lo, n_hi, k, align_class, pid, split_k; float
 #include "generated/mp_decode_selector.inc"
 // Measured plans of the INT8 scaled matmul out[M,N] = A[M,K] * B[N,K]^T: a row applies to M in
 // [m_lo, m_hi] with the row's exact (N, K).  orient 0 / 1: tile of the tensor-core kernel (tokens /
-// channels on the 128-row side, the other side tiled by bn); orient 3: the streaming kernel.
+// channels on the 128-row side, the other side tiled by bn); orient 3: the streaming kernel; orient 4 / 5:
+// orient 0 / 1 with 256-row tiles.
 struct ScaledPlanRow { int m_lo, m_hi, n, k, orient, bn, split_k; float ms; };
 #include "generated/mp_scaled_plans.inc"
 
@@ -675,7 +676,7 @@ void scaled_mm_config_meta(int id, int out[4]) {
 }
 
 ScaledCfg scaled_mm_select(int M, int N, int K) {
-  ScaledCfg best{0, kScaled[0].orient, kScaled[0].bn, 1, false};
+  ScaledCfg best{0, kScaled[0].orient, kScaled[0].bn, 1, false, 1};
   float best_ms = kInf;
   const int sms = g_num_sms.load(std::memory_order_relaxed);
   static constexpr int kSplit[4] = {1, 2, 4, 8};
@@ -691,7 +692,7 @@ ScaledCfg scaled_mm_select(int M, int N, int K) {
       float ms = waves * analytic_unit_ms(MP_INT8, c, k_iter, (int)std::min<long long>(units, sms)) +
                  reduction_ms(MP_INT8, -1, c, tiles, S);
       // padded work is wasted tensor time: prefer the tile that fits M
-      if (ms < best_ms) { best_ms = ms; best = ScaledCfg{id, s.orient, s.bn, S, false}; }
+      if (ms < best_ms) { best_ms = ms; best = ScaledCfg{id, s.orient, s.bn, S, false, 1}; }
     }
   }
   best.stream = int8_prefers_stream(std::min(M, N), std::max(M, N), K);
@@ -701,7 +702,9 @@ ScaledCfg scaled_mm_select(int M, int N, int K) {
       const ScaledPlanRow& r = kScaledPlans[i];
       if (r.n != N || r.k != K || M < r.m_lo || M > r.m_hi) continue;
       best.stream = r.orient == 3;
-      if (r.orient != 3) { best.orient = r.orient; best.bn = r.bn; best.split_k = std::max(1, r.split_k); }
+      if (r.orient != 3) {
+        best.orient = r.orient & 1; best.xm = r.orient >= 4 ? 2 : 1; best.bn = r.bn; best.split_k = std::max(1, r.split_k);
+      }
       break;
     }
   }

@@ -42,7 +42,7 @@ mp_plan select_plan(int dtype, int m, int n, int k);
 int choose_pattern2_split_n(int n);
 
 // scaled int8 matmul tile choice: config id 0..5, plus a split-K factor for small problems.
-struct ScaledCfg { int id; int orient; int bn; int split_k; bool stream; };   // stream: use the streaming kernel when the problem fits it
+struct ScaledCfg { int id; int orient; int bn; int split_k; bool stream; int xm; };   // stream: use the streaming kernel when the problem fits it; xm 2: 256-row tiles
 ScaledCfg scaled_mm_select(int M, int N, int K);
 void scaled_mm_config_meta(int id, int out[4]);
 constexpr int kScaledConfigCount = 6;

@@ -520,3 +520,4 @@ def test_int8_256_row_tiles_bit_exact(api):
     for orient in (4, 5):
         got = api.gemm_rcc_tile(dev(a), dev(b), orient, 256).cpu().numpy()
         assert np.array_equal(got.astype(np.int64), ref)
+
