@@ -418,6 +418,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       griddep_wait();
       MP_TRACE_MARK(2);
       uint32_t it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       UnitWalk walk(p);
       while (ok && walk.next(p, u)) {
@@ -429,8 +431,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const int prow = u.tp * kUmmaM * p.xm;
         const int qrow = r.q_begin + u.tq * r.bn;
         for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
-          const int s = (int)(it % (uint32_t)stages);
-          const uint32_t ph = (it / (uint32_t)stages) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, status, MP_DEV_TIMEOUT_PRODUCER)) { ok = false; break; }
           const uint32_t a_dst = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
           mbar_arrive_expect_tx(full_bar(s), tx);
@@ -446,6 +446,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                           (kb + c) * kElemsPerKb, qrow);
             }
           }
+          if (++s == stages) { s = 0; ph ^= 1u; }
         }
       }
       if (!ok) {
@@ -461,8 +462,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (one lane)
     if (lane == 0) {
-      uint32_t it = 0, ui = 0;
+      // The issuing thread is on the critical path of narrow tiles (a 128 x 64 x 16 MMA lasts ~32
+      // cycles), so the loop carries its state instead of recomputing it: stage index and phase
+      // are counters, and the operand descriptors of a stage are the descriptor of shared-memory
+      // offset 0 plus byte offsets >> 4 added to its address field.
+      uint32_t ui = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
+      const uint64_t desc0 = umma_smem_desc_sw128(smem_base);
+      const uint32_t x16 = (uint32_t)(p.xm * kXTileBytes) >> 4;        // X rows of one K block, in 16-byte units
+      const uint32_t stage16 = (uint32_t)p.stage_bytes >> 4;
       UnitWalk walk(p);
       UnitCoord u;
       for (; ok && walk.next(p, u); ++ui) {
@@ -475,30 +485,37 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const uint32_t d_tmem = tmem_base + buf * (uint32_t)kMaxBN;
         const uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kUmmaM, (uint32_t)r.bn)
                                                  : umma_idesc(1u, 0u, kUmmaM, (uint32_t)r.bn);
-        for (int kb = u.kb0; kb < u.kb1; kb += p.kc, ++it) {
-          const int s = (int)(it % (uint32_t)stages);
-          const uint32_t ph = (it / (uint32_t)stages) & 1u;
+        const uint32_t y16 = (uint32_t)(r.bn * kRowBytes) >> 4;        // Y rows of one K block
+        uint32_t first = 0u;                                            // 0 until the accumulators hold a product
+        for (int kb = u.kb0; kb < u.kb1; kb += p.kc) {
           if (!mbar_wait(full_bar(s), ph, status, MP_DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
           if (ui == 0 && kb == u.kb0) MP_TRACE_MARK(3);
           if (ui == 0 && kb + p.kc >= u.kb1) MP_TRACE_MARK(4);
           tc_fence_after();
-          const uint32_t a_addr = smem_base + (uint32_t)s * (uint32_t)p.stage_bytes;
-          const uint32_t x_bytes = (uint32_t)(p.xm * kXTileBytes);
-          const uint32_t b_addr = a_addr + (uint32_t)p.kc * x_bytes;
+          uint64_t ad = desc0 + (uint64_t)((uint32_t)s * stage16);
+          uint64_t bd = ad + (uint64_t)((uint32_t)p.kc * x16);
           const int nc = min(p.kc, u.kb1 - kb);     // K blocks of this stage that lie inside the slice
-          for (int c = 0; c < nc; ++c) {
-            for (int h = 0; h < p.xm; ++h) {       // the halves of X share the Y tile of this K block
+          for (int c = 0; c < nc; ++c, ad += x16, bd += y16) {
+            // 4 x 32 bytes of K per 128-byte row; with 256-row tiles both halves of X use the same Y tile
 #pragma unroll
-              for (int kk = 0; kk < 4; ++kk) {   // 4 x 32 bytes of K per 128-byte row
-                const uint64_t ad = umma_smem_desc_sw128(a_addr + (uint32_t)c * x_bytes + (uint32_t)(h * kXTileBytes) + 32u * kk);
-                const uint64_t bd = umma_smem_desc_sw128(b_addr + (uint32_t)(c * r.bn * kRowBytes) + 32u * kk);
-                const uint32_t acc = (kb > u.kb0 || c > 0 || kk > 0) ? 1u : 0u;
-                if constexpr (KIND == KIND_I8) umma_i8(d_tmem + (uint32_t)(h * kMaxBN), ad, bd, idesc, acc);
-                else umma_f16(d_tmem + (uint32_t)(h * kMaxBN), ad, bd, idesc, acc);
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint32_t acc = kk > 0 ? 1u : first;
+              if constexpr (KIND == KIND_I8) umma_i8(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, acc);
+              else umma_f16(d_tmem, ad + 2u * kk, bd + 2u * kk, idesc, acc);
+            }
+            if (p.xm == 2) {
+              const uint64_t ad1 = ad + (uint64_t)(kXTileBytes >> 4);
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk) {
+                const uint32_t acc = kk > 0 ? 1u : first;
+                if constexpr (KIND == KIND_I8) umma_i8(d_tmem + (uint32_t)kMaxBN, ad1 + 2u * kk, bd + 2u * kk, idesc, acc);
+                else umma_f16(d_tmem + (uint32_t)kMaxBN, ad1 + 2u * kk, bd + 2u * kk, idesc, acc);
               }
             }
+            first = 1u;
           }
           tc_commit(empty_bar(s));      // stage reusable once these MMAs have read it
+          if (++s == stages) { s = 0; ph ^= 1u; }
         }
         if (ok) tc_commit(tfull_bar((int)buf));   // accumulator complete
       }
