@@ -325,6 +325,29 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
       reinterpret_cast<uint4*>(o)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       return;
     }
+    // rows of D are the contiguous index of the output (channels on the lanes, tokens on the columns):
+    // the 32 lanes of a warp write 64 adjacent bytes per token; one pointer walks the 16 tokens
+    if (p.out_stride_p == 1 && p.n_on_p) {
+      uint16_t* ow = reinterpret_cast<uint16_t*>(p.out) + pi + (long long)q0 * p.out_stride_q;
+      const long long step = p.out_stride_q;
+      const bool has_bias = p.bias != nullptr;
+      const uint16_t b0 = has_bias ? reinterpret_cast<const uint16_t*>(p.bias)[pi] : (uint16_t)0;
+      const float bias_f = p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(b0)) : __half2float(__ushort_as_half(b0));
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (j < valid) {
+          const float as = p.scale_q[p.scale_q_scalar ? 0 : (q0 + j)];
+          const float t1 = __fmul_rn(as, __fmul_rn(__int2float_rn((int)r[j]), sp));
+          uint16_t h = f32_to_out16(t1, p.out_bf16);
+          if (has_bias) {
+            const float hv = p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(h)) : __half2float(__ushort_as_half(h));
+            h = f32_to_out16(hv + bias_f, p.out_bf16);
+          }
+          ow[(long long)j * step] = h;
+        }
+      }
+      return;
+    }
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
@@ -391,6 +414,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   griddep_launch_dependents();
 
   constexpr int kElemsPerKb = (KIND == KIND_I8) ? 128 : 64;
+  // slices whose partials are in flight together in the split-K reduction; the scaled epilogue needs the
+  // registers for itself
+  constexpr int kSliceBatch = (EPI == EPI_SCALED) ? 2 : 4;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one lane)
@@ -547,14 +573,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // is what a load costs.  256-row tiles drain their second accumulator (the tile's rows
         // 128..255, TMEM columns 256..511) the same way.
         for (int h = 0; h < p.xm; ++h, t_addr += (uint32_t)kMaxBN, pi += kUmmaM) {
-        if constexpr (EPI == EPI_SCALED) {        // the scaled epilogue has no registers to spare
-          for (int c0 = 0; c0 < r.bn; c0 += 16) {
-            uint32_t v[16];
-            tmem_ld_x16(t_addr + (uint32_t)c0, v);
-            tmem_ld_wait();
-            store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end);
-          }
-        } else {
+        {
           for (int c0 = 0; c0 < r.bn; c0 += 32) {
             uint32_t v[2][16];
             const bool two = c0 + 16 < r.bn;
@@ -575,9 +594,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // and in the reduction below (row-major scratch would scatter each access over 32 lines)
         uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.ws_slices + u.slice) * (size_t)p.ws_tile_words) +
                       row_in_tile;
-        for (int c0 = 0; c0 < r.bn; c0 += (EPI == EPI_SCALED ? 16 : 32)) {
+        for (int c0 = 0; c0 < r.bn; c0 += 32) {
           uint32_t v[2][16];
-          const bool two = EPI != EPI_SCALED && c0 + 16 < r.bn;   // two TMEM loads in flight per wait
+          const bool two = c0 + 16 < r.bn;                       // two TMEM loads in flight per wait
           tmem_ld_x16(t_addr + (uint32_t)c0, v[0]);
           if (two) tmem_ld_x16(t_addr + (uint32_t)c0 + 16u, v[1]);
           tmem_ld_wait();
@@ -644,15 +663,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           const uint4* base = reinterpret_cast<const uint4*>(p.ws_partials + (size_t)u.tile * p.ws_slices * (size_t)p.ws_tile_words) +
                               row_in_tile;
           const size_t slice_words16 = (size_t)p.ws_tile_words >> 2;
-          // 32 columns per pass (the last pass may be half wide); the loads of up to four slices are
-          // all in flight before the first is consumed
+          // 32 columns per pass (the last pass may be half wide); the loads of up to kSliceBatch slices
+          // are all in flight before the first is consumed
           for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             const int nq = (c_end - c0 >= 32) ? 8 : 4;      // 16-byte words in this pass
             uint32_t v[32];
-            for (int s0 = 0; s0 < S; s0 += 4) {
-              uint4 x[4][8];
+            for (int s0 = 0; s0 < S; s0 += kSliceBatch) {
+              uint4 x[kSliceBatch][8];
 #pragma unroll
-              for (int ds = 0; ds < 4; ++ds)
+              for (int ds = 0; ds < kSliceBatch; ++ds)
                 if (s0 + ds < S) {
                   const uint4* ps = base + (size_t)(s0 + ds) * slice_words16 + (size_t)(c0 >> 2) * kUmmaM;
 #pragma unroll
@@ -660,7 +679,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     if (j < nq) x[ds][j] = __ldcg(ps + (size_t)j * kUmmaM);
                 }
 #pragma unroll
-              for (int ds = 0; ds < 4; ++ds)
+              for (int ds = 0; ds < kSliceBatch; ++ds)
                 if (s0 + ds < S) {
 #pragma unroll
                   for (int j = 0; j < 8; ++j)
