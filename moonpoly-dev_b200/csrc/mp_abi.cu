@@ -311,7 +311,9 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.kb_total = (p.k + kb_elems - 1) / kb_elems;
   // K blocks per stage: wide boxes move far more bytes per TMA instruction; keep >= 3 stages
   const int kb_bytes = xm * kXTileBytes + bn_max * kRowBytes;
-  const int smem_for_stages = kSmemBudget - 1024 - 256;
+  // the scaled epilogue stages the tile's scales and bias in shared memory (4 warps x 1.5 KB)
+  const int epi_reserve = p.epi == EPI_SCALED ? 8192 : 0;
+  const int smem_for_stages = kSmemBudget - 1024 - 256 - epi_reserve;
   int kc = l.kc;
   if (kc <= 0) kc = (smem_for_stages / (4 * kb_bytes) >= 3) ? 4 : (smem_for_stages / (2 * kb_bytes) >= 3) ? 2 : 1;
   while (kc > 1 && smem_for_stages / (kc * kb_bytes) < 2) kc >>= 1;
@@ -397,7 +399,7 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
     ty1 = ty0;
   }
 
-  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024;
+  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024 + epi_reserve;
   if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
   if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32>(*d, 1, tx, ty0, ty1, up, grid, smem, stream);
   return launch_umma_t<KIND_I8, EPI_SCALED>(*d, 2, tx, ty0, ty1, up, grid, smem, stream);

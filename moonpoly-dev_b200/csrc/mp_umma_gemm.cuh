@@ -151,8 +151,16 @@ struct UnitWalk {
 };
 
 // ------------------------------------------------------------------------------------ epilogue math
-template <int EPI>
-struct EpiCtx {};
+// What the scaled epilogue needs besides the accumulators, fetched once per tile before the
+// accumulator is waited for: with ~200 KB of the SM's L1/shared memory given to the pipeline stages
+// little L1 is left, and a scale load issued per 16-column chunk cost an L2 round trip each time.
+struct ScaledStage {
+  const float* sq;       // shared memory: scale along Q for the tile's columns, index q - q_base
+  const uint16_t* bq;    // shared memory: bias along Q (when the channels are on Q), same index
+  int q_base;
+  float sp;              // scale of this thread's row
+  uint16_t bp;           // bias of this thread's row (when the channels are on P)
+};
 
 __device__ __forceinline__ uint16_t f32_to_out16(float v, int bf16) {
   if (bf16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
@@ -199,7 +207,7 @@ __device__ __forceinline__ void finish_store(const UmmaParams& p, uint32_t accw,
 // Store 16 consecutive Q columns [q0, q0+16) of row `pi` from accumulator words r[0..15].
 template <int EPI>
 __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_t (&r)[16], int pi, int q0,
-                                              int q_end) {
+                                              int q_end, const ScaledStage& st) {
   if (pi >= p.P) return;
   const int valid = min(16, q_end - q0);
   if (valid <= 0) return;
@@ -263,40 +271,28 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
     }
   }
 
-  float sp = 0.0f;
-  if constexpr (EPI == EPI_SCALED) sp = p.scale_p[p.scale_p_scalar ? 0 : pi];
   if constexpr (EPI == EPI_SCALED) {
-    // fast path: this thread's 16 outputs are contiguous and 16-byte aligned; scales and bias of
-    // the 16 columns come in with vector loads and the result leaves as two 16-byte stores
+    const float sp = st.sp;
+    const bool has_bias = p.bias != nullptr;
+    const float* sqs = st.sq + (q0 - st.q_base);
+    // fast path: this thread's 16 outputs are contiguous and 16-byte aligned; the result leaves as
+    // two 16-byte stores
     uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (long long)pi * p.out_stride_p + q0;
-    const bool vec_ok = p.out_stride_q == 1 && valid == 16 && (reinterpret_cast<uintptr_t>(o) & 15) == 0 &&
-                        (p.scale_q_scalar || (reinterpret_cast<uintptr_t>(p.scale_q + q0) & 15) == 0) &&
-                        (p.bias == nullptr || p.n_on_p ||
-                         (reinterpret_cast<uintptr_t>(reinterpret_cast<const uint16_t*>(p.bias) + q0) & 15) == 0);
-    if (vec_ok) {
+    if (p.out_stride_q == 1 && valid == 16 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
       float sq[16];
-      if (p.scale_q_scalar) {
-        const float s0 = p.scale_q[0];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sq[j] = s0;
-      } else {
-        const float4* s4 = reinterpret_cast<const float4*>(p.scale_q + q0);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float4 t = __ldg(s4 + j);
-          sq[4 * j] = t.x; sq[4 * j + 1] = t.y; sq[4 * j + 2] = t.z; sq[4 * j + 3] = t.w;
-        }
+      for (int j = 0; j < 4; ++j) {
+        const float4 t = reinterpret_cast<const float4*>(sqs)[j];
+        sq[4 * j] = t.x; sq[4 * j + 1] = t.y; sq[4 * j + 2] = t.z; sq[4 * j + 3] = t.w;
       }
       uint16_t bq[16];
-      const bool has_bias = p.bias != nullptr;
       if (has_bias) {
         if (p.n_on_p) {
-          const uint16_t b0 = reinterpret_cast<const uint16_t*>(p.bias)[pi];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) bq[j] = b0;
+          for (int j = 0; j < 16; ++j) bq[j] = st.bp;
         } else {
-          const uint4* b4 = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.bias) + q0);
-          const uint4 t0 = __ldg(b4), t1 = __ldg(b4 + 1);
+          const uint4* b4 = reinterpret_cast<const uint4*>(st.bq + (q0 - st.q_base));
+          const uint4 t0 = b4[0], t1 = b4[1];
           const uint32_t w[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
           for (int j = 0; j < 8; ++j) { bq[2 * j] = (uint16_t)(w[j] & 0xffffu); bq[2 * j + 1] = (uint16_t)(w[j] >> 16); }
@@ -311,11 +307,11 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
         uint16_t h = f32_to_out16(t1, p.out_bf16);
         if (has_bias) {
           if (p.out_bf16) {
-            const float s = __bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(bq[j]));
-            h = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+            const float sum = __bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(bq[j]));
+            h = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
           } else {
-            const float s = __half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(bq[j]));
-            h = __half_as_ushort(__float2half_rn(s));
+            const float sum = __half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(bq[j]));
+            h = __half_as_ushort(__float2half_rn(sum));
           }
         }
         if (j & 1) packed[j >> 1] |= (uint32_t)h << 16;
@@ -325,37 +321,35 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
       reinterpret_cast<uint4*>(o)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       return;
     }
-    // rows of D are the contiguous index of the output (channels on the lanes, tokens on the columns):
-    // the 32 lanes of a warp write 64 adjacent bytes per token; one pointer walks the 16 tokens
-    if (p.out_stride_p == 1 && p.n_on_p) {
-      uint16_t* ow = reinterpret_cast<uint16_t*>(p.out) + pi + (long long)q0 * p.out_stride_q;
-      const long long step = p.out_stride_q;
-      const bool has_bias = p.bias != nullptr;
-      const uint16_t b0 = has_bias ? reinterpret_cast<const uint16_t*>(p.bias)[pi] : (uint16_t)0;
-      const float bias_f = p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(b0)) : __half2float(__ushort_as_half(b0));
+    // every other layout: one pointer walks the 16 columns (when the rows of D are the contiguous
+    // index of the output, the 32 lanes of a warp write 64 adjacent bytes per column)
+    uint16_t* ow = reinterpret_cast<uint16_t*>(p.out) + (long long)pi * p.out_stride_p + (long long)q0 * p.out_stride_q;
+    const long long step = p.out_stride_q;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (j < valid) {
-          const float as = p.scale_q[p.scale_q_scalar ? 0 : (q0 + j)];
-          const float t1 = __fmul_rn(as, __fmul_rn(__int2float_rn((int)r[j]), sp));
-          uint16_t h = f32_to_out16(t1, p.out_bf16);
-          if (has_bias) {
-            const float hv = p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(h)) : __half2float(__ushort_as_half(h));
-            h = f32_to_out16(hv + bias_f, p.out_bf16);
+    for (int j = 0; j < 16; ++j) {
+      if (j < valid) {
+        const float bs = p.n_on_p ? sp : sqs[j];
+        const float as = p.n_on_p ? sqs[j] : sp;
+        const float t1 = __fmul_rn(as, __fmul_rn(__int2float_rn((int)r[j]), bs));
+        uint16_t h = f32_to_out16(t1, p.out_bf16);
+        if (has_bias) {
+          const uint16_t b = p.n_on_p ? st.bp : st.bq[q0 - st.q_base + j];
+          if (p.out_bf16) {
+            const float sum = __bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(b));
+            h = __bfloat16_as_ushort(__float2bfloat16_rn(sum));
+          } else {
+            const float sum = __half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(b));
+            h = __half_as_ushort(__float2half_rn(sum));
           }
-          ow[(long long)j * step] = h;
         }
+        ow[(long long)j * step] = h;
       }
-      return;
     }
+    return;
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    if (j < valid) {
-      float sq = 0.0f;
-      if constexpr (EPI == EPI_SCALED) sq = p.scale_q[p.scale_q_scalar ? 0 : (q0 + j)];
-      finish_store<EPI>(p, r[j], pi, q0 + j, sp, sq);
-    }
+    if (j < valid) finish_store<EPI>(p, r[j], pi, q0 + j, 0.0f, 0.0f);
   }
 }
 
@@ -558,6 +552,32 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const Region& r = p.reg[u.region];
       const uint32_t buf = p.xm == 2 ? 0u : (ui & 1u);
       const uint32_t use = p.xm == 2 ? ui : (ui >> 1);
+      // scaled epilogue: fetch the tile's scales and bias while the accumulator is still being produced
+      ScaledStage st{};
+      float sp_h[2] = {0.0f, 0.0f};
+      uint16_t bp_h[2] = {0, 0};
+      if constexpr (EPI == EPI_SCALED) {
+        uint8_t* mine = smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4) + 16 + (size_t)quad * 1536;
+        float* sq_s = reinterpret_cast<float*>(mine);
+        uint16_t* bq_s = reinterpret_cast<uint16_t*>(mine + 1024);
+        const int qb = r.q_begin + u.tq * r.bn;
+        const bool bias_on_q = p.bias != nullptr && !p.n_on_p;
+        __syncwarp();                      // this warp has finished reading the previous tile's values
+        for (int j = lane; j < r.bn; j += 32) {
+          const int q = qb + j;
+          sq_s[j] = q < r.q_end ? p.scale_q[p.scale_q_scalar ? 0 : q] : 0.0f;
+          if (bias_on_q) bq_s[j] = q < r.q_end ? reinterpret_cast<const uint16_t*>(p.bias)[q] : (uint16_t)0;
+        }
+        for (int h = 0; h < p.xm; ++h) {
+          const int row = (u.tp * p.xm + h) * kUmmaM + quad * 32 + lane;
+          if (row < p.P) {
+            sp_h[h] = p.scale_p[p.scale_p_scalar ? 0 : row];
+            if (p.bias != nullptr && p.n_on_p) bp_h[h] = reinterpret_cast<const uint16_t*>(p.bias)[row];
+          }
+        }
+        __syncwarp();
+        st.sq = sq_s; st.bq = bq_s; st.q_base = qb; st.sp = sp_h[0]; st.bp = bp_h[0];
+      }
       if (!mbar_wait(tfull_bar((int)buf), use & 1u, status, MP_DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
       if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(5);
       tc_fence_after();
@@ -573,6 +593,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // is what a load costs.  256-row tiles drain their second accumulator (the tile's rows
         // 128..255, TMEM columns 256..511) the same way.
         for (int h = 0; h < p.xm; ++h, t_addr += (uint32_t)kMaxBN, pi += kUmmaM) {
+        if constexpr (EPI == EPI_SCALED) { st.sp = sp_h[h]; st.bp = bp_h[h]; }
         {
           for (int c0 = 0; c0 < r.bn; c0 += 32) {
             uint32_t v[2][16];
@@ -580,8 +601,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             tmem_ld_x16(t_addr + (uint32_t)c0, v[0]);
             if (two) tmem_ld_x16(t_addr + (uint32_t)c0 + 16u, v[1]);
             tmem_ld_wait();
-            store_chunk16<EPI>(p, v[0], pi, q_tile0 + c0, q_end);
-            if (two) store_chunk16<EPI>(p, v[1], pi, q_tile0 + c0 + 16, q_end);
+            store_chunk16<EPI>(p, v[0], pi, q_tile0 + c0, q_end, st);
+            if (two) store_chunk16<EPI>(p, v[1], pi, q_tile0 + c0 + 16, q_end, st);
           }
         }
         }
@@ -695,9 +716,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     }
                 }
             }
-            store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[0]), pi, q_tile0 + c0, q_end);
+            store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[0]), pi, q_tile0 + c0, q_end, st);
             if (nq == 8)
-              store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[16]), pi, q_tile0 + c0 + 16, q_end);
+              store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[16]), pi, q_tile0 + c0 + 16, q_end, st);
           }
           }
         }
