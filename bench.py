@@ -463,6 +463,40 @@ def run_ours(args, rank, world, local_rank):
         extras = {}
         if not args.no_extras:
             extras = extra_sections(api, L, st, dev, peaks)
+            # the same sweep replayed from a CUDA graph (what a serving engine's decode loop does): per shape, the
+            # launches of one step are captured once and replayed; host launch cost drops out
+            side = torch.cuda.Stream(device=dev)
+            side_st = ctypes.c_void_p(side.cuda_stream)
+            graph_tfl = []
+            for m in SWEEP_M:
+                r = reps_for(m)
+
+                def launch_all():
+                    for i in range(r):
+                        rc = mp_gemm(api.MP_FP16, m, N_DIM, K_DIM, ctypes.c_void_p(a_dev[m][i & 1].data_ptr()), 0,
+                                     ctypes.c_void_p(weights[i % WEIGHT_COPIES].data_ptr()), 1,
+                                     ctypes.c_void_p(c_dev[m].data_ptr()), 1, ctypes.c_float(1.0), ctypes.c_float(0.0), side_st)
+                        if rc != 0:
+                            raise RuntimeError(L.mp_last_error_string().decode())
+                side.wait_stream(stream)
+                with torch.cuda.stream(side):
+                    launch_all()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    launch_all()
+                g.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(3):
+                    g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                graph_tfl.append(flops(m) / (e0.elapsed_time(e1) / (3 * r) * 1e-3) / 1e12)
+            extras["cuda_graph_replay"] = {"value": geomean(graph_tfl), "unit": "TFLOP/s",
+                                           "per_shape_us": {str(m): round(flops(m) / (t * 1e12) * 1e6, 2)
+                                                            for m, t in zip(SWEEP_M, graph_tfl)}}
         line = {
             "metric": METRIC, "value": geomean([tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps,

@@ -109,6 +109,16 @@ int mp_gemm_rcc_pid_static_scratch(int dtype, int pid, int split_k, int m, int n
 int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k,
                      const void* A, const void* B, void* C, float alpha, float beta, void* stream);
 
+/* Test aid (no counterpart in the reference; needs no GPU): the device-side work schedule of the
+ * tensor-core kernel for an RCC problem and an explicit tile, as the kernel's roles walk it.  Every
+ * work unit yields 8 ints in `units` (room for `capacity` units): CTA, tile, tile row, tile column,
+ * first K block, one past the last K block, slice index, slices of the tile.  `count` receives the
+ * number of units; `info` (8 ints, may be NULL): grid, tiles, K blocks, scratch slices per tile,
+ * tiles in the stream-K head, 128-row halves per tile, helpers allowed, split_k.  The SM count is
+ * the one the cost model uses (148 unless a device has been queried). */
+int mp_debug_schedule(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k,
+                      int* units, int capacity, int* count, int* info);
+
 /* get_gemm_workspace_size_fp16_row_col_col (core/fp16/fp16_rcc.cu:3306-3316), extended to every
  * pid and dtype: bytes of scratch mp_gemm_rcc_pid needs for this problem (0 when split_k == 1). */
 int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes);

@@ -177,6 +177,8 @@ struct Launch {
   int kc = 0;                 // K blocks per stage; 0 = choose
   int split_n = 0, bn1 = 0;   // twin: second region [split_n, n) with its own UMMA-N
   void* workspace = nullptr; size_t workspace_bytes = 0;
+  // schedule check (no launch, no device needed): receives 8 ints per work unit, see mp_debug_schedule
+  int* dry_units = nullptr; int dry_capacity = 0; int* dry_count = nullptr; int* dry_grid = nullptr;
 };
 
 int elem_bytes(int dtype) { return dtype == MP_FP16 ? 2 : dtype == MP_INT8 ? 1 : 4; }
@@ -275,8 +277,11 @@ int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CU
 
 // Tensor-core path (FP16 / INT8).
 int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
+  const bool dry = l.dry_count != nullptr;
   DeviceState* d = nullptr;
-  if (int rc = device_state(&d)) return rc;
+  DeviceState model{};                      // schedule checks run without a GPU: the modelled SM count stands in
+  if (dry) { model.sms = mp::num_sms_for_model(); d = &model; }
+  else if (int rc = device_state(&d)) return rc;
 
   UmmaParams up{};
   const bool swap = l.orient == 1;
@@ -368,6 +373,26 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
         up.ws_slices = max_slices;
       }
     }
+  }
+
+  if (dry) {
+    // walk every CTA's units exactly as the kernel's roles do and hand them to the caller
+    int count = 0;
+    for (int cta = 0; cta < grid; ++cta) {
+      UnitWalk walk(up, cta, grid);
+      UnitCoord u;
+      while (walk.next(up, u)) {
+        if (count < l.dry_capacity) {
+          int* o = l.dry_units + 8 * (size_t)count;
+          o[0] = cta; o[1] = u.tile; o[2] = u.tp; o[3] = u.tq; o[4] = u.kb0; o[5] = u.kb1; o[6] = u.slice; o[7] = u.nslices;
+        }
+        ++count;
+      }
+    }
+    *l.dry_count = count;
+    if (l.dry_grid) { l.dry_grid[0] = grid; l.dry_grid[1] = up.total_tiles; l.dry_grid[2] = up.kb_total; l.dry_grid[3] = up.ws_slices;
+                      l.dry_grid[4] = up.sk_tiles; l.dry_grid[5] = up.xm; l.dry_grid[6] = up.helpers_ok; l.dry_grid[7] = up.split_k; }
+    return MP_OK;
   }
 
   if (S > 1 || up.sk_tiles > 0) {
@@ -701,6 +726,21 @@ int mp_cost_ms(int dtype, int pid, int split_k, int m, int n, int k, float* ms) 
 }
 
 int mp_elite_fp16_pids(int* pids, int capacity) { return mp::elite_fp16_pids(pids, capacity); }
+
+int mp_debug_schedule(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k, int* units,
+                      int capacity, int* count, int* info) {
+  if (dtype != MP_FP16 && dtype != MP_INT8) return fail(MP_ERR_INVALID_ARG, "the tile schedule exists for FP16 and INT8");
+  if (count == nullptr || m <= 0 || n <= 0 || k <= 0) return fail(MP_ERR_INVALID_ARG, "bad arguments");
+  const int xm = (orient == 4 || orient == 5) ? 2 : 1;
+  if (xm == 2) orient -= 4;
+  if ((orient != 0 && orient != 1) || bn < 16 || bn > 256 || bn % 16 != 0) return fail(MP_ERR_INVALID_ARG, "bad tile");
+  Problem p = rcc_problem(dtype, m, n, k, reinterpret_cast<const void*>(16), reinterpret_cast<const void*>(16),
+                          reinterpret_cast<void*>(16), 1.0f, 0.0f);
+  Launch l;
+  l.orient = orient; l.bn = bn; l.kc = kc; l.split_k = std::max(1, split_k); l.xm = xm;
+  l.dry_units = units; l.dry_capacity = units ? capacity : 0; l.dry_count = count; l.dry_grid = info;
+  return run_umma(p, l, nullptr);
+}
 
 int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes) {
   if (bytes == nullptr) return fail(MP_ERR_INVALID_ARG, "bytes is null");

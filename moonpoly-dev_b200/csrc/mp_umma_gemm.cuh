@@ -96,14 +96,14 @@ struct UnitCoord {
   int region, tile, tp, tq, kb0, kb1, slice, nslices;
 };
 
-__device__ __forceinline__ void tile_coords(const UmmaParams& p, UnitCoord& u) {
+__host__ __device__ __forceinline__ void tile_coords(const UmmaParams& p, UnitCoord& u) {
   u.region = (p.num_regions == 2 && u.tile >= p.reg[1].tile_base) ? 1 : 0;
   const Region& r = p.reg[u.region];
   const int t = u.tile - r.tile_base;
   const int group_sz = p.group_p * r.tiles_q;
   const int g = t / group_sz;
   const int first_p = g * p.group_p;
-  const int rows = min(p.group_p, p.tiles_p - first_p);
+  const int rows = p.group_p < p.tiles_p - first_p ? p.group_p : p.tiles_p - first_p;
   const int in_g = t - g * group_sz;
   u.tq = in_g / rows;
   u.tp = first_p + (in_g - u.tq * rows);
@@ -114,23 +114,25 @@ __device__ __forceinline__ void tile_coords(const UmmaParams& p, UnitCoord& u) {
 // uniform units  w = blockIdx.x, blockIdx.x + grid, ...  where unit w is slice w % split_k of tile
 // sk_tiles + w / split_k.
 struct UnitWalk {
-  int sk_cur, sk_end, w;
-  __device__ __forceinline__ explicit UnitWalk(const UmmaParams& p) {
+  int sk_cur, sk_end, w, cta, grid;
+  __device__ __forceinline__ explicit UnitWalk(const UmmaParams& p) : UnitWalk(p, (int)blockIdx.x, (int)gridDim.x) {}
+  // the same walk for CTA `cta_` of a grid of `grid_` CTAs; host code uses it to check schedules
+  __host__ __device__ __forceinline__ UnitWalk(const UmmaParams& p, int cta_, int grid_) : cta(cta_), grid(grid_) {
     const long long total = (long long)p.sk_tiles * p.kb_total;
-    const long long b = (long long)blockIdx.x * p.sk_ipc;
+    const long long b = (long long)cta * p.sk_ipc;
     sk_cur = (int)(b < total ? b : total);
     sk_end = (int)(b + p.sk_ipc < total ? b + p.sk_ipc : total);
-    w = (int)blockIdx.x;
+    w = cta;
   }
-  __device__ __forceinline__ bool next(const UmmaParams& p, UnitCoord& u) {
+  __host__ __device__ __forceinline__ bool next(const UmmaParams& p, UnitCoord& u) {
     if (sk_cur < sk_end) {
       u.tile = sk_cur / p.kb_total;
       u.kb0 = sk_cur - u.tile * p.kb_total;
-      const int len = min(p.kb_total - u.kb0, sk_end - sk_cur);
+      const int len = p.kb_total - u.kb0 < sk_end - sk_cur ? p.kb_total - u.kb0 : sk_end - sk_cur;
       u.kb1 = u.kb0 + len;
       const int first_cta = (u.tile * p.kb_total) / p.sk_ipc;
       const int last_cta = ((u.tile + 1) * p.kb_total - 1) / p.sk_ipc;
-      u.slice = (int)blockIdx.x - first_cta;
+      u.slice = cta - first_cta;
       u.nslices = last_cta - first_cta + 1;
       sk_cur += len;
       tile_coords(p, u);
@@ -143,9 +145,9 @@ struct UnitWalk {
     u.slice = w - t * p.split_k;
     u.nslices = p.split_k;
     u.kb0 = u.slice * p.kb_per_slice;
-    u.kb1 = min(p.kb_total, u.kb0 + p.kb_per_slice);
+    u.kb1 = p.kb_total < u.kb0 + p.kb_per_slice ? p.kb_total : u.kb0 + p.kb_per_slice;
     tile_coords(p, u);
-    w += (int)gridDim.x;
+    w += grid;
     return true;
   }
 };
