@@ -444,9 +444,11 @@ def run_ours(args, rank, world, local_rank):
             t_c = flops(m) / (peaks["tflops"] * 1e12)
             t_m = algo_bytes(m) / (peaks["hbm_gbs"] * 1e9)
             bound = "tensor" if t_c >= t_m else "hbm"
+            t_nom = max(flops(m) / 2.25e15, algo_bytes(m) / 8.0e12)     # nominal B200: 2.25 PFLOP/s dense fp16, 8 TB/s
             per_shape.append({"M": m, "us": round(per_launch_ms[m] * 1e3, 3), "tflops": round(tfl[m] / world, 3),
                               "gbs": round(algo_bytes(m) / (per_launch_ms[m] * 1e-3) / 1e9, 1), "bound": bound,
                               "frac": round(max(t_c, t_m) / (per_launch_ms[m] * 1e-3), 4),
+                              "frac_nominal": round(t_nom / (per_launch_ms[m] * 1e-3), 4),
                               "plan": repr(api.select_plan(api.MP_FP16, m, N_DIM, K_DIM))})
         dom = SWEEP_M[-1]
         achieved = flops(dom) / (per_launch_ms[dom] * 1e-3) / 1e12
@@ -507,6 +509,7 @@ def run_ours(args, rank, world, local_rank):
                        "entry": "mp_gemm (online selector)", "parallelism": f"column-parallel x{world}, no collective",
                        "peaks": peaks},
             "roofline_geomean_frac": geomean([p["frac"] for p in per_shape]),
+            "roofline_geomean_frac_nominal": geomean([p["frac_nominal"] for p in per_shape]),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"], "traffic": traffic,
                          "kernel": "umma_gemm_kernel<f16> at M=4096", "peak_source": peaks["source"] + " burst"},
