@@ -66,7 +66,7 @@ struct DeviceState {
   bool ready = false;
   int sms = 0;
   int cc = 0;
-  bool attrs[3] = {false, false, false};
+  bool attrs[6] = {false, false, false, false, false, false};
 };
 constexpr int kMaxDevices = 32;
 DeviceState g_dev[kMaxDevices];
@@ -252,17 +252,17 @@ size_t umma_workspace_bytes(const Problem& p, const Launch& l, size_t* counter_b
   return cb + (size_t)tiles * l.split_k * bn_max * kUmmaM * 4;
 }
 
-template <int KIND, int EPI>
+template <int KIND, int EPI, bool SPLIT>
 int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CUtensorMap& ty0,
                   const CUtensorMap& ty1, const UmmaParams& up, int grid, size_t smem, cudaStream_t stream) {
-  auto kern = umma_gemm_kernel<KIND, EPI>;
+  auto kern = umma_gemm_kernel<KIND, EPI, SPLIT>;
   if (!d.attrs[attr_slot]) {
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     d.attrs[attr_slot] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kUmmaThreads);
+  cfg.blockDim = dim3(SPLIT ? kUmmaThreads : kUmmaThreadsWide);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -316,8 +316,8 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.kb_total = (p.k + kb_elems - 1) / kb_elems;
   // K blocks per stage: wide boxes move far more bytes per TMA instruction; keep >= 3 stages
   const int kb_bytes = xm * kXTileBytes + bn_max * kRowBytes;
-  // the scaled epilogue stages the tile's scales and bias in shared memory (4 warps x 1.5 KB)
-  const int epi_reserve = p.epi == EPI_SCALED ? 8192 : 0;
+  // the scaled epilogue stages the tile's scales and bias in shared memory (up to 8 warps x 1.5 KB)
+  const int epi_reserve = p.epi == EPI_SCALED ? 12288 : 0;
   const int smem_for_stages = kSmemBudget - 1024 - 256 - epi_reserve;
   int kc = l.kc;
   if (kc <= 0) kc = (smem_for_stages / (4 * kb_bytes) >= 3) ? 4 : (smem_for_stages / (2 * kb_bytes) >= 3) ? 2 : 1;
@@ -425,9 +425,15 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   }
 
   const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024 + epi_reserve;
-  if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
-  if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32>(*d, 1, tx, ty0, ty1, up, grid, smem, stream);
-  return launch_umma_t<KIND_I8, EPI_SCALED>(*d, 2, tx, ty0, ty1, up, grid, smem, stream);
+  // kernels whose every unit is a whole tile run the variant without the reduction (8 epilogue warps)
+  if (up.split_k > 1 || up.sk_tiles > 0) {
+    if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16, true>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
+    if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32, true>(*d, 1, tx, ty0, ty1, up, grid, smem, stream);
+    return launch_umma_t<KIND_I8, EPI_SCALED, true>(*d, 2, tx, ty0, ty1, up, grid, smem, stream);
+  }
+  if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16, false>(*d, 3, tx, ty0, ty1, up, grid, smem, stream);
+  if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32, false>(*d, 4, tx, ty0, ty1, up, grid, smem, stream);
+  return launch_umma_t<KIND_I8, EPI_SCALED, false>(*d, 5, tx, ty0, ty1, up, grid, smem, stream);
 }
 
 // CUDA-core path (FP32 always; FP16 / INT8 when TMA's alignment rules are not met).

@@ -42,7 +42,8 @@ constexpr int kXTileBytes = kUmmaM * kRowBytes;
 constexpr int kMaxBN = 256;
 constexpr int kTmemCols = 512;
 constexpr int kMaxStages = 12;
-constexpr int kUmmaThreads = 192;
+constexpr int kUmmaThreads = 192;       // kernels that may split K: producer, MMA issuer, 4 epilogue warps
+constexpr int kUmmaThreadsWide = 320;   // single-slice kernels: 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int kSmemBudget = 232448;    // 227 KB opt-in limit per CTA
 
 enum { KIND_F16 = 0, KIND_I8 = 1 };
@@ -356,8 +357,13 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
 }
 
 // ------------------------------------------------------------------------------------ the kernel
-template <int KIND, int EPI>
-__global__ void __launch_bounds__(kUmmaThreads, 1)
+// SPLIT = true: tiles may be finished through the split-K scratch (uniform slices or a stream-K head); the
+// reduction needs ~130 registers of partial sums in flight, which leaves room for 4 epilogue warps only.
+// SPLIT = false: every unit is a whole tile; the reduction is compiled out and 8 epilogue warps (two per TMEM
+// lane quadrant, taking alternate 32-column groups) halve the time a tile needs to leave TMEM -- that time is
+// exposed whenever a CTA has a single tile, and always with 256-row tiles.
+template <int KIND, int EPI, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? kUmmaThreads : kUmmaThreadsWide, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY0,
                  const __grid_constant__ CUtensorMap tmY1, const UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -385,7 +391,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 4);
+      mbar_init(tempty_bar(b), SPLIT ? 4 : 8);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmX);
@@ -545,6 +551,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quad = warp & 3;
+    const int half = SPLIT ? 0 : ((warp - 2) >> 2);       // which alternate 32-column groups this warp drains
+    constexpr int kColStep = SPLIT ? 32 : 64;
     uint32_t ui = 0;
     bool ok = true;
     griddep_wait();
@@ -559,7 +567,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       float sp_h[2] = {0.0f, 0.0f};
       uint16_t bp_h[2] = {0, 0};
       if constexpr (EPI == EPI_SCALED) {
-        uint8_t* mine = smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4) + 16 + (size_t)quad * 1536;
+        uint8_t* mine = smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4) + 16 + (size_t)(warp - 2) * 1536;
         float* sq_s = reinterpret_cast<float*>(mine);
         uint16_t* bq_s = reinterpret_cast<uint16_t*>(mine + 1024);
         const int qb = r.q_begin + u.tq * r.bn;
@@ -590,14 +598,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const int q_end = min(r.q_end, q_tile0 + r.bn);
 
       const int S = u.nslices;               // slices that make up this unit's tile
-      if (S == 1) {
+      if (!SPLIT || S == 1) {
         // two 16-column TMEM loads are in flight before the wait: the round trip, not the data,
         // is what a load costs.  256-row tiles drain their second accumulator (the tile's rows
         // 128..255, TMEM columns 256..511) the same way.
         for (int h = 0; h < p.xm; ++h, t_addr += (uint32_t)kMaxBN, pi += kUmmaM) {
         if constexpr (EPI == EPI_SCALED) { st.sp = sp_h[h]; st.bp = bp_h[h]; }
         {
-          for (int c0 = 0; c0 < r.bn; c0 += 32) {
+          for (int c0 = 32 * half; c0 < r.bn; c0 += kColStep) {
             uint32_t v[2][16];
             const bool two = c0 + 16 < r.bn;
             tmem_ld_x16(t_addr + (uint32_t)c0, v[0]);
@@ -611,7 +619,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));
-      } else {
+      } else if constexpr (SPLIT) {
         // park this slice's raw accumulators as [tile][slice][column / 4][row] 16-byte words: the 32
         // lanes of a warp (32 consecutive rows) then touch 512 contiguous bytes per access, both here
         // and in the reduction below (row-major scratch would scatter each access over 32 lines)
