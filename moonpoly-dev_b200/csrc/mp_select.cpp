@@ -341,6 +341,15 @@ TileCfg tile_cfg(int dtype, int pid) {
       c.valid = true; c.orient = 3; c.bn = 64; c.align = 16; c.split_capable = false;
       return c;
     }
+    if ((pid >= 1000 && pid < 1064) || (pid >= 1200 && pid < 1264)) {
+      // library-native tiles, same numbering as for FP16: 1000 + 32*orient + bn/16 (128-row), 1200 + ... (256-row)
+      const int base = pid >= 1200 ? 1200 : 1000;
+      const int bn = ((pid - base) & 31) * 16;
+      if (bn < 16 || bn > 256) return c;
+      c.valid = true; c.orient = (pid - base) >> 5; c.bn = bn; c.align = 16; c.split_capable = base == 1000;
+      c.xm = base == 1200 ? 2 : 1;
+      return c;
+    }
     if (pid < 0 || pid > 45) return c;
     const U& u = kInt8Primary[pid];
     c.valid = true; c.orient = u.orient; c.bn = u.bn; c.align = u.align; c.split_capable = true;
@@ -373,13 +382,15 @@ namespace {
 // pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
 struct PidMeta { TileCfg cfg; int meta[3]; };
 struct MetaTables {
-  PidMeta fp16[440], int8[46], fp32[40], native[64], native256[64], skinny, streaming, streaming_i8;
+  PidMeta fp16[440], int8[46], fp32[40], native[64], native256[64], native_i8[64], native256_i8[64], skinny, streaming, streaming_i8;
   MetaTables() {
     skinny.cfg = tile_cfg(MP_FP16, 1100); pid_tile_meta(MP_FP16, 1100, skinny.meta);
     streaming.cfg = tile_cfg(MP_FP16, 1101); pid_tile_meta(MP_FP16, 1101, streaming.meta);
     streaming_i8.cfg = tile_cfg(MP_INT8, 1101); pid_tile_meta(MP_INT8, 1101, streaming_i8.meta);
     for (int p = 0; p < 64; ++p) { native[p].cfg = tile_cfg(MP_FP16, 1000 + p); pid_tile_meta(MP_FP16, 1000 + p, native[p].meta); }
     for (int p = 0; p < 64; ++p) { native256[p].cfg = tile_cfg(MP_FP16, 1200 + p); pid_tile_meta(MP_FP16, 1200 + p, native256[p].meta); }
+    for (int p = 0; p < 64; ++p) { native_i8[p].cfg = tile_cfg(MP_INT8, 1000 + p); pid_tile_meta(MP_INT8, 1000 + p, native_i8[p].meta); }
+    for (int p = 0; p < 64; ++p) { native256_i8[p].cfg = tile_cfg(MP_INT8, 1200 + p); pid_tile_meta(MP_INT8, 1200 + p, native256_i8[p].meta); }
     for (int p = 0; p < 440; ++p) { fp16[p].cfg = tile_cfg(MP_FP16, p); pid_tile_meta(MP_FP16, p, fp16[p].meta); }
     for (int p = 0; p < 46; ++p) { int8[p].cfg = tile_cfg(MP_INT8, p); pid_tile_meta(MP_INT8, p, int8[p].meta); }
     for (int p = 0; p < 40; ++p) { fp32[p].cfg = tile_cfg(MP_FP32, p); pid_tile_meta(MP_FP32, p, fp32[p].meta); }
@@ -395,7 +406,12 @@ const PidMeta* pid_meta(int dtype, int pid) {
     if (pid >= 1200 && pid < 1264) return t.native256[pid - 1200].cfg.valid ? &t.native256[pid - 1200] : nullptr;
     return pid < 440 && t.fp16[pid].cfg.valid ? &t.fp16[pid] : nullptr;
   }
-  if (dtype == MP_INT8) return pid == 1101 ? &t.streaming_i8 : pid < 46 ? &t.int8[pid] : nullptr;
+  if (dtype == MP_INT8) {
+    if (pid == 1101) return &t.streaming_i8;
+    if (pid >= 1000 && pid < 1064) return t.native_i8[pid - 1000].cfg.valid ? &t.native_i8[pid - 1000] : nullptr;
+    if (pid >= 1200 && pid < 1264) return t.native256_i8[pid - 1200].cfg.valid ? &t.native256_i8[pid - 1200] : nullptr;
+    return pid < 46 ? &t.int8[pid] : nullptr;
+  }
   if (dtype == MP_FP32) return pid < 40 ? &t.fp32[pid] : nullptr;
   return nullptr;
 }
@@ -639,6 +655,22 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
     if (lf.gen && lf.int8_force <= 1 && int8_prefers_stream(std::min(m, n), std::max(m, n), k)) {
       const double bytes = (double)m * k + (double)n * k + 4.0 * m * n;
       plan = mp_plan{MP_PATTERN_SINGLE, 1101, 1, 0, (float)(bytes / 6.0e9 + 2.5e-3)};
+    }
+    // the measured scaled-matmul plans describe the same int8 main loop on the same (m, n, k): use them for the
+    // plain int32-output GEMM as well (the epilogues differ, the ranking of the tiles hardly does)
+    if (lf.gen && lf.int8_force <= 1 && k % 16 == 0) {
+      for (int i = 0; i < kScaledPlanCount; ++i) {
+        const ScaledPlanRow& r = kScaledPlans[i];
+        if (r.n != n || r.k != k || m < r.m_lo || m > r.m_hi) continue;
+        if (r.orient == 3) {
+          if (std::min(m, n) <= 64) plan = mp_plan{MP_PATTERN_SINGLE, 1101, 1, 0, r.ms};
+        } else {
+          const int S = std::max(1, r.split_k);
+          const int pid = (r.orient >= 4 ? 1200 : 1000) + 32 * (r.orient & 1) + r.bn / 16;
+          plan = mp_plan{S > 1 ? MP_PATTERN_SPLITK : MP_PATTERN_SINGLE, pid, S, 0, r.ms};
+        }
+        break;
+      }
     }
   }
   if (std::getenv("MOONPOLY_DEBUG_ONLINE_SELECTOR")) {

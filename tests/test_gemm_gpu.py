@@ -521,3 +521,18 @@ def test_int8_256_row_tiles_bit_exact(api):
         got = api.gemm_rcc_tile(dev(a), dev(b), orient, 256).cpu().numpy()
         assert np.array_equal(got.astype(np.int64), ref)
 
+
+
+@pytest.mark.parametrize("m", [5, 100, 300, 2500])
+def test_int8_gemm_follows_measured_plans_bit_exact(api, m):
+    """Plain INT8 GEMM on a shape the measured scaled-matmul table covers: the selector names a library-native
+    kernel (streaming, 128-row or 256-row tile) and the int32 accumulators stay exact."""
+    n, k = 4096, 4096
+    a = rng.int8_uniform(90, 0, (m, k))
+    b = rng.int8_uniform(90, 1, (n, k))
+    plan = api.select_plan(api.MP_INT8, m, n, k)
+    assert plan.pid >= 1000, plan
+    ref = (a.astype(np.float64) @ b.astype(np.float64).T).T.astype(np.int64)
+    got = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    assert np.array_equal(got.astype(np.int64), ref)
+    assert np.array_equal(api.gemm_rcc_pid(dev(a), dev(b), plan.pid, plan.split_k).cpu().numpy(), got)
