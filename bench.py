@@ -254,6 +254,18 @@ def extra_sections(api, L, st, dev, peaks):
                          "gbs": round(byts / best[0] / 1e9, 1), "frac": round(roof / best[0], 4),
                          "selector_us": round(t_sel * 1e6, 2), "selector_frac": round(roof / t_sel, 4)})
         del ws
+    # ---- FP32 config shape (M=37, N=K=1024, seed 0) through mp_gemm: CUDA-core FFMA tiles, launch-latency bound
+    a32 = torch.from_numpy(rng.uniform(0, rng.STREAM_A, (37, 1024), -1.0, 1.0)).to(dev)
+    b32 = [torch.from_numpy(rng.uniform(0, rng.STREAM_B, (1024, 1024), -1.0, 1.0)).to(dev) for _ in range(2)]
+    c32 = torch.empty((1024, 37), dtype=torch.float32, device=dev)
+
+    def call32(i):
+        rc = L.mp_gemm(api.MP_FP32, 37, 1024, 1024, vp(a32.data_ptr()), 0, vp(b32[i & 1].data_ptr()), 1, vp(c32.data_ptr()), 1,
+                       1.0, 0.0, st)
+        assert rc == 0, L.mp_last_error_string()
+    t32 = ev_time(call32, 50)
+    out["fp32_m37_n1024_k1024"] = {"us": round(t32 * 1e6, 2), "gflops": round(2.0 * 37 * 1024 * 1024 / t32 / 1e9, 1),
+                                   "plan": repr(api.select_plan(api.MP_FP32, 37, 1024, 1024))}
     # ---- host cost of a selection (mp_select_plan through ctypes; the empty-call cost of ctypes is measured with
     # mp_num_sms and subtracted): warm = the same shape again (plan cache hit), cold = shapes never seen before
     plan = api.Plan()

@@ -613,6 +613,47 @@ int run_stream(const Problem& p, cudaStream_t stream) {
   return launch_stream_nt<STREAM_I8, STREAM_EPI_SCALED>(sp, d->sms, stream);
 }
 
+// FP32 streaming kernel: one side of the problem has at most 64 rows.
+bool skinny_f32_compatible(const Problem& p) {
+  const auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  return p.dtype == MP_FP32 && std::min(p.m, p.n) >= 1 && std::min(p.m, p.n) <= 64 && p.k >= 4 && p.k % 4 == 0 &&
+         p.lda % 4 == 0 && p.ldb % 4 == 0 && al(p.A) && al(p.B);
+}
+
+template <int TMAX, int ROWS>
+int launch_skinny_f32(const SkinnyF32Params& sp, cudaStream_t stream) {
+  const int rows_per_cta = kSkinnyF32Warps * ROWS;
+  const int grid = (sp.R + rows_per_cta - 1) / rows_per_cta;
+  skinny_f32_kernel<TMAX, ROWS><<<grid, kSkinnyF32Warps * 32, 0, stream>>>(sp);
+  MP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
+int run_skinny_f32(const Problem& p, cudaStream_t stream) {
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+  SkinnyF32Params sp{};
+  const bool narrow_is_a = p.m <= p.n;
+  sp.W = reinterpret_cast<const float*>(narrow_is_a ? p.B : p.A);
+  sp.ldw = narrow_is_a ? p.ldb : p.lda;
+  sp.X = reinterpret_cast<const float*>(narrow_is_a ? p.A : p.B);
+  sp.ldx = narrow_is_a ? p.lda : p.ldb;
+  sp.R = narrow_is_a ? p.n : p.m;
+  sp.T = narrow_is_a ? p.m : p.n;
+  sp.K = p.k;
+  sp.out = reinterpret_cast<float*>(p.C);
+  sp.stride_r = narrow_is_a ? p.c_stride_n : p.c_stride_m;
+  sp.stride_t = narrow_is_a ? p.c_stride_m : p.c_stride_n;
+  sp.alpha = p.alpha; sp.beta = p.beta;
+  // two rows per warp halve the re-reads of X as long as there are rows enough to fill the GPU
+  const bool two = sp.R >= 4 * kSkinnyF32Warps * d->sms;
+  if (sp.T <= 8) return two ? launch_skinny_f32<8, 2>(sp, stream) : launch_skinny_f32<8, 1>(sp, stream);
+  if (sp.T <= 16) return two ? launch_skinny_f32<16, 2>(sp, stream) : launch_skinny_f32<16, 1>(sp, stream);
+  if (sp.T <= 40) return two ? launch_skinny_f32<40, 2>(sp, stream) : launch_skinny_f32<40, 1>(sp, stream);
+  return launch_skinny_f32<64, 1>(sp, stream);
+}
+
 int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {
   if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
     return fail(MP_ERR_INVALID_ARG, "Unsupported data type %d", dtype);
@@ -640,7 +681,13 @@ int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, c
   const int eff_pid = pid >= 0 ? pid : (p.dtype == MP_FP32 ? 23 : 6);
   const TileCfg c = tile_cfg(p.dtype, eff_pid);
   if (!c.valid) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, p.dtype);
-  if (p.dtype == MP_FP32) return run_simt(p, c.ti, c.tj, split_k, ws, ws_bytes, stream);
+  if (p.dtype == MP_FP32) {
+    if (c.orient == 3) {          // the FP32 streaming kernel; shapes it does not cover take a 64x64 tile
+      if (skinny_f32_compatible(p)) return run_skinny_f32(p, stream);
+      return run_simt(p, 64, 64, split_k, ws, ws_bytes, stream);
+    }
+    return run_simt(p, c.ti, c.tj, split_k, ws, ws_bytes, stream);
+  }
   if (!tma_compatible(p)) return run_simt(p, 64, 64, split_k, ws, ws_bytes, stream);
   if (c.orient == 2) {          // the skinny streaming kernel; shapes it does not cover take the 128x16 tile
     if (gemv_compatible(p)) return run_gemv(p, stream);

@@ -165,6 +165,7 @@ LiveFlags read_live_flags(int dtype) {
   } else if (dtype == MP_FP32) {
     f.fp32_p3 = env_flag("MOONPOLY_ENABLE_FP32_PATTERN3", true);
     f.fp32_force = env_int("MOONPOLY_FP32_PATTERN3_FORCE_SPLITK", 0);
+    f.gen = env_flag("MOONPOLY_ENABLE_GENERATED_SELECTOR", true);
   } else {
     f.int8_p3 = env_flag("MOONPOLY_ENABLE_INT8_PATTERN3", true);
     f.gen = env_flag("MOONPOLY_ENABLE_GENERATED_SELECTOR", true);
@@ -356,6 +357,10 @@ TileCfg tile_cfg(int dtype, int pid) {
     return c;
   }
   if (dtype == MP_FP32) {
+    if (pid == 1101) {            // library-native FP32 streaming kernel (min(m,n) <= 64)
+      c.valid = true; c.orient = 3; c.ti = 64; c.tj = 64; c.align = 4; c.split_capable = false;
+      return c;
+    }
     if (pid < 0 || pid > 39) return c;
     c.valid = true; c.ti = kFp32Primary[pid].ti; c.tj = kFp32Primary[pid].tj; c.align = 1;
     c.split_capable = true;
@@ -382,11 +387,12 @@ namespace {
 // pid metadata resolved once (the selector evaluates ~90 pids per unseen shape)
 struct PidMeta { TileCfg cfg; int meta[3]; };
 struct MetaTables {
-  PidMeta fp16[440], int8[46], fp32[40], native[64], native256[64], native_i8[64], native256_i8[64], skinny, streaming, streaming_i8;
+  PidMeta fp16[440], int8[46], fp32[40], native[64], native256[64], native_i8[64], native256_i8[64], skinny, streaming, streaming_i8, streaming_f32;
   MetaTables() {
     skinny.cfg = tile_cfg(MP_FP16, 1100); pid_tile_meta(MP_FP16, 1100, skinny.meta);
     streaming.cfg = tile_cfg(MP_FP16, 1101); pid_tile_meta(MP_FP16, 1101, streaming.meta);
     streaming_i8.cfg = tile_cfg(MP_INT8, 1101); pid_tile_meta(MP_INT8, 1101, streaming_i8.meta);
+    streaming_f32.cfg = tile_cfg(MP_FP32, 1101); pid_tile_meta(MP_FP32, 1101, streaming_f32.meta);
     for (int p = 0; p < 64; ++p) { native[p].cfg = tile_cfg(MP_FP16, 1000 + p); pid_tile_meta(MP_FP16, 1000 + p, native[p].meta); }
     for (int p = 0; p < 64; ++p) { native256[p].cfg = tile_cfg(MP_FP16, 1200 + p); pid_tile_meta(MP_FP16, 1200 + p, native256[p].meta); }
     for (int p = 0; p < 64; ++p) { native_i8[p].cfg = tile_cfg(MP_INT8, 1000 + p); pid_tile_meta(MP_INT8, 1000 + p, native_i8[p].meta); }
@@ -412,7 +418,7 @@ const PidMeta* pid_meta(int dtype, int pid) {
     if (pid >= 1200 && pid < 1264) return t.native256_i8[pid - 1200].cfg.valid ? &t.native256_i8[pid - 1200] : nullptr;
     return pid < 46 ? &t.int8[pid] : nullptr;
   }
-  if (dtype == MP_FP32) return pid < 40 ? &t.fp32[pid] : nullptr;
+  if (dtype == MP_FP32) return pid == 1101 ? &t.streaming_f32 : pid < 40 ? &t.fp32[pid] : nullptr;
   return nullptr;
 }
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
@@ -647,6 +653,11 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
   } else if (dtype == MP_FP32) {
     plan = select_simple(MP_FP32, 40, m, n, k, lf.fp32_p3, lf.fp32_force, 8, e.fp32_p3_min_k,
                          e.fp32_p3_min_part_k, e.fp32_p3_margin, 1);
+    // few rows on one side: the FP32 streaming kernel (library-native pid 1101) replaces tile + split-K pass
+    if (lf.gen && lf.fp32_force <= 1 && std::min(m, n) >= 1 && std::min(m, n) <= 64 && k >= 4 && k % 4 == 0) {
+      const double bytes = 4.0 * ((double)m * k + (double)n * k + (double)m * n);
+      plan = mp_plan{MP_PATTERN_SINGLE, 1101, 1, 0, (float)(bytes / 6.0e9 + 3.0e-3)};
+    }
   } else {
     plan = select_simple(MP_INT8, 46, m, n, k, lf.int8_p3, lf.int8_force, 64, e.int8_p3_min_k,
                          e.int8_p3_min_part_k, e.int8_p3_margin, 16);

@@ -168,3 +168,81 @@ simt_splitk_reduce_kernel(const SimtParams p) {
 }
 
 }  // namespace mp
+
+// ------------------------------------------------------------------------------------------------
+// FP32 streaming kernel for a narrow side of at most 64 rows: one warp per ROWS rows of the wide
+// operand W[R,K]; the lanes read the rows once with 16-byte loads and keep one accumulator per
+// (row, narrow row), the rows of X[T,K] come from L1/L2 (each X vector serves ROWS rows), and the
+// 32 partial sums of each output meet in a shuffle tree.  A small FP32 problem (37 x 1024 x 1024)
+// is one short wave of such warps instead of a few 64x64 tiles with a split-K pass behind them.
+//   out[r * stride_r + t * stride_t] = alpha * sum_k W[r,k] * X[t,k] + beta * out[...]
+// ------------------------------------------------------------------------------------------------
+namespace mp {
+
+struct SkinnyF32Params {
+  const float* W; long long ldw;
+  const float* X; long long ldx;
+  float* out; long long stride_r, stride_t;
+  int R, T, K;                          // K % 4 == 0, rows 16-byte aligned
+  float alpha, beta;
+};
+
+constexpr int kSkinnyF32Warps = 4;
+
+template <int TMAX, int ROWS>
+__global__ void __launch_bounds__(kSkinnyF32Warps * 32)
+skinny_f32_kernel(const SkinnyF32Params p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r0 = (blockIdx.x * kSkinnyF32Warps + warp) * ROWS;
+  if (r0 >= p.R) return;
+  const float4* w[ROWS];
+  bool ok[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    ok[i] = r0 + i < p.R;
+    w[i] = reinterpret_cast<const float4*>(p.W + (long long)(ok[i] ? r0 + i : r0) * p.ldw);
+  }
+  const int chunks = p.K >> 2;
+  float acc[ROWS][TMAX];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i)
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) acc[i][t] = 0.0f;
+  for (int c = lane; c < chunks; c += 32) {
+    float4 a[ROWS];
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) a[i] = __ldcs(w[i] + c);
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) {
+      if (t < p.T) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(p.X + (long long)t * p.ldx) + c);
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+          acc[i][t] = fmaf(a[i].x, x.x, acc[i][t]);
+          acc[i][t] = fmaf(a[i].y, x.y, acc[i][t]);
+          acc[i][t] = fmaf(a[i].z, x.z, acc[i][t]);
+          acc[i][t] = fmaf(a[i].w, x.w, acc[i][t]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) {
+      if (t < p.T) {
+        float v = acc[i][t];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (ok[i] && lane == (t & 31)) {
+          float* o = p.out + (long long)(r0 + i) * p.stride_r + (long long)t * p.stride_t;
+          float res = p.alpha * v;
+          if (p.beta != 0.0f) res += p.beta * (*o);
+          *o = res;
+        }
+      }
+    }
+  }
+}
+
+}  // namespace mp

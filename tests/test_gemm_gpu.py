@@ -536,3 +536,22 @@ def test_int8_gemm_follows_measured_plans_bit_exact(api, m):
     got = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
     assert np.array_equal(got.astype(np.int64), ref)
     assert np.array_equal(api.gemm_rcc_pid(dev(a), dev(b), plan.pid, plan.split_k).cpu().numpy(), got)
+
+
+@pytest.mark.parametrize("m,n,k", [(37, 1024, 1024), (1, 300, 512), (64, 129, 2052), (700, 5, 1024), (9, 40, 8)])
+def test_fp32_streaming_kernel(api, oracle, m, n, k):
+    """Library-native pid 1101 for FP32 (one warp per row of the wide operand): within 1e-4 of the oracle on
+    uniform inputs, exact on small integers, alpha/beta, both mappings; the selector names it for these shapes."""
+    a = rng.uniform(95, 0, (m, k), -1.0, 1.0)
+    b = rng.uniform(95, 1, (n, k), -1.0, 1.0)
+    ref = oracle.gemm_f32_rcc(a, b)
+    assert api.select_plan(api.MP_FP32, m, n, k).pid == 1101
+    for c in (api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), api.gemm_rcc_pid(dev(a), dev(b), 1101, 1).cpu().numpy()):
+        assert np.all(np.abs(c - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref)))
+    ai = rng.small_ints(96, 0, (m, k), dtype=np.float32)
+    bi = rng.small_ints(96, 1, (n, k), dtype=np.float32)
+    c0 = rng.small_ints(96, 2, (n, m), dtype=np.float32)
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T
+    assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1).cpu().numpy(), exact.astype(np.float32))
+    got = api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1, c_nm=dev(c0).clone(), alpha=2.0, beta=-1.0).cpu().numpy()
+    assert np.array_equal(got, (2 * exact - c0.astype(np.int64)).astype(np.float32))
