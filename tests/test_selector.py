@@ -164,3 +164,31 @@ def test_selection_overhead_budget(api):
     print(f"selection: cold {cold * 1e6:.2f} us, memoised {warm * 1e6:.2f} us (ctypes overhead {base * 1e6:.2f} us removed)")
     assert cold < 15e-6          # generous on a loaded CI box; the budget is 5 us
     assert warm < 5e-6
+
+
+def test_measured_tables_name_runnable_kernels(api):
+    """Every bucket of the measured tables resolves to a kernel the library has, for FP16 (both mappings of the tuned
+    layers, aligned and unaligned token counts) and for INT8 on the scaled-matmul layers."""
+    fp16_layers = [(4096, 4096), (6144, 4096), (28672, 4096), (4096, 14336), (10240, 8192), (8192, 8192), (57344, 8192),
+                   (8192, 28672), (1024, 8192), (1024, 28672), (5120, 8192), (1280, 8192), (7168, 8192), (2048, 28672)]
+    tokens = [1, 2, 3, 7, 16, 31, 33, 64, 65, 100, 128, 129, 200, 255, 256, 300, 511, 512, 700, 1000, 1024, 1500, 2047, 2048,
+              3000, 4095, 4096, 6000, 8192, 12000]
+    for (N, K) in fp16_layers:
+        for M in tokens:
+            for (m, n) in ((N, M), (M, N)):             # Linear mapping and direct mapping
+                plan = api.select_plan(api.MP_FP16, m, n, K)
+                tile, align = api.pid_info(api.MP_FP16, plan.pid if plan.pid >= 0 else 0)
+                assert K % align == 0 and plan.split_k >= 1 and plan.estimated_ms > 0, (m, n, K, plan)
+                if plan.pid in (1100, 1101):
+                    assert min(m, n) <= 64, (m, n, K, plan)
+                if 1200 <= plan.pid < 1264:
+                    assert plan.split_k == 1 and 256 in tile[:2], (m, n, K, plan)
+    for (N, K) in [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]:
+        for M in tokens:
+            plan = api.select_plan(api.MP_INT8, M, N, K)
+            assert plan.pid >= 1000, (M, N, K, plan)
+            api.pid_info(api.MP_INT8, plan.pid)
+            if plan.pid == 1101:
+                assert M <= 64
+            cfg = api.predict_int8_scaled_mm_kernel(M, N, K)
+            assert 0 <= cfg < 6
