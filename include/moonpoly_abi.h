@@ -119,6 +119,13 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
 int mp_debug_schedule(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k,
                       int* units, int capacity, int* count, int* info);
 
+/* Test aid (no counterpart in the reference; needs no GPU): the growth rule of the library's own
+ * per-stream split-K scratch.  The buffer holds a counter area (`have_counter_bytes`, fixed when the
+ * buffer was created) followed by the partial sums; returns 1 when a call that wants
+ * `want_counter_bytes` of counters and `partial_bytes` of partials does not fit `have_bytes`. */
+int mp_debug_scratch_must_grow(size_t have_bytes, size_t have_counter_bytes, size_t want_counter_bytes,
+                               size_t partial_bytes);
+
 /* get_gemm_workspace_size_fp16_row_col_col (core/fp16/fp16_rcc.cu:3306-3316), extended to every
  * pid and dtype: bytes of scratch mp_gemm_rcc_pid needs for this problem (0 when split_k == 1). */
 int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes);
@@ -136,6 +143,15 @@ int mp_pid_info(int dtype, int pid, int tile[3], int* alignment);
 /* gemm_cost_model / gemm_splitk_cost_model (core/fp16/fp16_rcc_cost.cu:161-237 and the fp32/int8
  * siblings): predicted milliseconds of pid with split_k slices on RCC (m,n,k). */
 int mp_cost_ms(int dtype, int pid, int split_k, int m, int n, int k, float* ms);
+
+/* gemm_reduction_cost_model (core/fp16/fp16_rcc_cost.cu:190-210): the split-K hand-off and
+ * reduction term of mp_cost_ms alone, for RCC (m, n) and `split_k` slices (0 when split_k <= 1). */
+int mp_cost_reduction_ms(int dtype, int pid, int split_k, int m, int n, float* ms);
+
+/* cutlass_gemm_predict (core/fp16/fp16_rcc_cost.cu:256-279, core/fp32/fp32_rcc_cost.cu,
+ * core/int8/i8_rcc_cost.cu:232-246): the cheapest primary pid for RCC (m, n, k) among the pids whose
+ * K-alignment contract the shape meets; `ms` (may be NULL) receives its predicted milliseconds. */
+int mp_cost_predict_pid(int dtype, int m, int n, int k, int* pid, float* ms);
 
 /* run_fp16_pattern2_twin_gemm_row_col_col (core/fp16/fp16_rcc.cu:3297-3304 -> 75-108): columns
  * [0,split_n) and [split_n,n) of C are produced by two tile shapes inside ONE launch.
@@ -175,6 +191,10 @@ int mp_scaled_mm_config(int config_id, int out[4]);
 /* is_paper_elite_fp16_pid / paper_elite_fp16_kernel_count / paper_elite_fp16_pids
  * (generated/fp16/rcc/candidates.cu:35-60). `pids` may be NULL; returns the count. */
 int mp_elite_fp16_pids(int* pids, int capacity);
+
+/* is_explicit_neighborhood_pid (generated/fp16/rcc/candidates.cu:62-65): 1 for the FP16 pid ranges
+ * 90..205, 216..321 and 400..439, else 0.  Every pid of these ranges has a kernel here. */
+int mp_is_explicit_neighborhood_pid(int pid);
 
 /* The reference reads its MOONPOLY_* environment flags on every call (core/fp16/fp16_rcc.cu:110-144).
  * This library caches numeric flags at first use; mp_reload_env() re-reads all of them and drops

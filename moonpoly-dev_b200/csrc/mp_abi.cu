@@ -116,6 +116,12 @@ std::vector<Scratch> g_scratch;
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// The partials start behind the counter area the buffer was created with (`have_counters`), which
+// may be larger than what this call asks for: capacity is tested against that real layout.
+bool scratch_must_grow(size_t have_bytes, size_t have_counters, size_t want_counters, size_t partial_bytes) {
+  return have_counters < want_counters || have_bytes < std::max(have_counters, want_counters) + partial_bytes;
+}
+
 int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes, uint8_t** counters,
                 uint8_t** partials) {
   int dev = 0;
@@ -125,7 +131,7 @@ int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes,
   for (auto& e : g_scratch)
     if (e.dev == dev && e.stream == stream) { s = &e; break; }
   const size_t want_counters = std::max<size_t>(round_up(counter_bytes, 256), 1 << 16);
-  if (s == nullptr || s->counter_bytes < want_counters || s->bytes < want_counters + partial_bytes) {
+  if (s == nullptr || scratch_must_grow(s->bytes, s->counter_bytes, want_counters, partial_bytes)) {
     // Grow: a fresh, larger buffer.  The old one is kept (work already queued may still use it).
     const size_t cb = std::max(want_counters, s ? s->counter_bytes : 0);
     const size_t total = cb + std::max<size_t>(round_up(partial_bytes, 1 << 20) * 2, 8 << 20);
@@ -151,7 +157,7 @@ int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes,
 // ------------------------------------------------------------------------------------------------
 constexpr size_t kStaticScratchBytes = 8u << 20;   // 8 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-void* g_static_scratch_ptr[kMaxDevices] = {};
+std::atomic<void*> g_static_scratch_ptr[kMaxDevices] = {};
 
 // ------------------------------------------------------------------------------------------------
 // problem description shared by all dtypes
@@ -522,6 +528,7 @@ int launch_gemv_t(const GemvParams& gp, cudaStream_t stream) {
 
 bool gemv_compatible(const Problem& p) {
   return p.dtype == MP_FP16 && p.epi == EPI_F16 && std::min(p.m, p.n) <= 8 && std::min(p.m, p.n) >= 1 && p.k >= 8 &&
+         (p.k * 2) % 16 == 0 &&  // the kernel walks K in whole 16-byte chunks (a padded leading dimension does not help)
          tma_compatible(p);      // same rule: 16-byte aligned rows
 }
 
@@ -584,6 +591,7 @@ int launch_stream_nt(const StreamParams& sp, int sms, cudaStream_t stream) {
 bool stream_compatible(const Problem& p) {
   if (!(p.dtype == MP_FP16 && p.epi == EPI_F16) && p.dtype != MP_INT8) return false;
   return std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 16 &&
+         ((long long)p.k * elem_bytes(p.dtype)) % 16 == 0 &&   // K is walked in whole 16-byte chunks
          tma_compatible(p);      // same rule: 16-byte aligned rows
 }
 
@@ -675,6 +683,23 @@ Problem rcc_problem(int dtype, int m, int n, int k, const void* A, const void* B
   return p;
 }
 
+// The tensor-core launch a pid stands for on problem `p`.  The streaming pids (orient 2 / 3) name
+// kernels of their own; for shapes those do not cover they fall back to a narrow tensor tile whose
+// orientation follows the problem.  run_pid and mp_workspace_size both derive the launch here, so
+// the reported workspace size always matches what the call will need.
+Launch umma_launch_for(const Problem& p, const TileCfg& c, int split_k) {
+  Launch l;
+  l.split_k = std::max(1, split_k);
+  if (c.orient == 2) {
+    l.orient = p.m <= p.n ? 1 : 0; l.bn = 16;
+  } else if (c.orient == 3) {
+    l.orient = p.m <= p.n ? 1 : 0; l.bn = std::min(64, std::max(16, (std::min(p.m, p.n) + 15) / 16 * 16));
+  } else {
+    l.orient = c.orient; l.bn = c.bn; l.xm = c.xm == 2 ? 2 : 1;
+  }
+  return l;
+}
+
 // Runs one pid (or the dedicated split-K tile when pid < 0) on an RCC problem.
 int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, cudaStream_t stream) {
   if (p.m == 0 || p.n == 0) return MP_OK;
@@ -689,23 +714,9 @@ int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, c
     return run_simt(p, c.ti, c.tj, split_k, ws, ws_bytes, stream);
   }
   if (!tma_compatible(p)) return run_simt(p, 64, 64, split_k, ws, ws_bytes, stream);
-  if (c.orient == 2) {          // the skinny streaming kernel; shapes it does not cover take the 128x16 tile
-    if (gemv_compatible(p)) return run_gemv(p, stream);
-    Launch lf;
-    lf.orient = p.m <= p.n ? 1 : 0; lf.bn = 16; lf.split_k = std::max(1, split_k);
-    lf.workspace = ws; lf.workspace_bytes = ws_bytes;
-    return run_umma(p, lf, stream);
-  }
-  if (c.orient == 3) {          // the streaming warp-MMA kernel, with the same fallback
-    if (stream_compatible(p)) return run_stream(p, stream);
-    Launch lf;
-    lf.orient = p.m <= p.n ? 1 : 0; lf.bn = std::min(64, std::max(16, (std::min(p.m, p.n) + 15) / 16 * 16));
-    lf.split_k = std::max(1, split_k);
-    lf.workspace = ws; lf.workspace_bytes = ws_bytes;
-    return run_umma(p, lf, stream);
-  }
-  Launch l;
-  l.orient = c.orient; l.bn = c.bn; l.split_k = std::max(1, split_k); l.xm = c.xm == 2 ? 2 : 1;
+  if (c.orient == 2 && gemv_compatible(p)) return run_gemv(p, stream);        // the skinny streaming kernel
+  if (c.orient == 3 && stream_compatible(p)) return run_stream(p, stream);    // the streaming warp-MMA kernel
+  Launch l = umma_launch_for(p, c, split_k);
   l.workspace = ws; l.workspace_bytes = ws_bytes;
   return run_umma(p, l, stream);
 }
@@ -778,7 +789,29 @@ int mp_cost_ms(int dtype, int pid, int split_k, int m, int n, int k, float* ms) 
   return MP_OK;
 }
 
+int mp_cost_reduction_ms(int dtype, int pid, int split_k, int m, int n, float* ms) {
+  if (ms == nullptr) return fail(MP_ERR_INVALID_ARG, "ms is null");
+  if (!pid_exists(dtype, pid)) return fail(MP_ERR_BAD_PID, "pid %d has no kernel for dtype %d", pid, dtype);
+  *ms = mp::reduction_cost_ms(dtype, pid, split_k, m, n);
+  return MP_OK;
+}
+
+int mp_cost_predict_pid(int dtype, int m, int n, int k, int* pid, float* ms) {
+  if (pid == nullptr) return fail(MP_ERR_INVALID_ARG, "pid is null");
+  if (dtype != MP_FP16 && dtype != MP_INT8 && dtype != MP_FP32)
+    return fail(MP_ERR_INVALID_ARG, "Unsupported data type %d", dtype);
+  if (m <= 0 || n <= 0 || k <= 0) return fail(MP_ERR_INVALID_ARG, "non-positive problem size");
+  *pid = mp::predict_primary_pid(dtype, m, n, k, ms);
+  return MP_OK;
+}
+
+int mp_debug_scratch_must_grow(size_t have_bytes, size_t have_counter_bytes, size_t want_counter_bytes,
+                               size_t partial_bytes) {
+  return scratch_must_grow(have_bytes, have_counter_bytes, want_counter_bytes, partial_bytes) ? 1 : 0;
+}
+
 int mp_elite_fp16_pids(int* pids, int capacity) { return mp::elite_fp16_pids(pids, capacity); }
+int mp_is_explicit_neighborhood_pid(int pid) { return mp::is_explicit_neighborhood_fp16_pid(pid) ? 1 : 0; }
 
 int mp_debug_schedule(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k, int* units,
                       int capacity, int* count, int* info) {
@@ -808,7 +841,7 @@ int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size
   if (dtype == MP_FP32) { *bytes = simt; return MP_OK; }
   Problem p{};
   p.dtype = dtype; p.m = m; p.n = n; p.k = k;
-  Launch l; l.orient = c.orient; l.bn = c.bn; l.split_k = split_k;
+  const Launch l = umma_launch_for(p, c, split_k);
   *bytes = std::max(simt, umma_workspace_bytes(p, l, nullptr));
   return MP_OK;
 }
@@ -992,27 +1025,18 @@ int mp_gemm_rcc_pid_static_scratch(int dtype, int pid, int split_k, int m, int n
   int dev = -1;
   MP_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(MP_ERR_CUDA, "device index %d out of range", dev);
-  if (g_static_scratch_ptr[dev] == nullptr) {
+  void* scratch = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // set-up, once per device, with that device current: host code only holds a stand-in for the
     // array's name, so ask the runtime for its address on this device
     std::lock_guard<std::mutex> g(g_mu);
-    void* ptr = nullptr;
-    MP_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
-    g_static_scratch_ptr[dev] = ptr;
+    MP_CUDA_TRY(cudaGetSymbolAddress(&scratch, g_static_scratch));
+    g_static_scratch_ptr[dev].store(scratch, std::memory_order_release);
   }
   const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
   // the scratch keeps whatever the previous call left; run_umma clears the counters it needs at
   // zero (a memset on `stream`, not an allocation) before the launch
-  return run_pid(p, pid, split_k, g_static_scratch_ptr[dev], kStaticScratchBytes, reinterpret_cast<cudaStream_t>(stream));
+  return run_pid(p, pid, split_k, scratch, kStaticScratchBytes, reinterpret_cast<cudaStream_t>(stream));
 }
-
-#ifdef MP_TRACE
-// debugging aid of trace builds: copies the per-CTA phase timestamps (160 x 16 uint64) to `out`
-int mp_debug_trace(unsigned long long* out) {
-  MP_CUDA_TRY(cudaDeviceSynchronize());
-  MP_CUDA_TRY(cudaMemcpyFromSymbol(out, mp::g_mp_trace, sizeof(unsigned long long) * 160 * 16));
-  return MP_OK;
-}
-#endif
 
 }  // extern "C"

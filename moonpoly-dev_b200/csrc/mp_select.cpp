@@ -9,6 +9,8 @@
 #include <cstring>
 #include <limits>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 namespace mp {
 namespace {
@@ -35,8 +37,13 @@ constexpr U kFp16Primary[41] = {
 constexpr int kFp16SplitPids[17] = {4, 6, 7, 12, 13, 15, 19, 20, 23, 24, 25, 29, 31, 32, 33, 37, 39};
 // elite set (generated/fp16/rcc/candidates.cu:35-60)
 constexpr int kEliteExtra[5] = {400, 407, 413, 425, 439};
-// decode-selector / generated-plan pids that keep a kernel here; all are 16-wide token tiles
-constexpr int kFp16Explicit[12] = {91, 92, 95, 97, 99, 100, 166, 185, 201, 239, 286, 304};
+// "explicit neighbourhood" pids 90..205 and 216..321 (generated/fp16/rcc/candidates.cu:62-65): in the
+// reference every one of them is a 16-token-wide tile (pm = 16) over 8..128 weight rows; here they share the
+// 128 x 16 tile.  These need K % 4 == 0 only, the others K % 8 == 0 (candidates.cu, explicit_neighborhood_alignment).
+constexpr int kFp16ExplicitAlign4[45] = {114, 115, 116, 117, 118, 119, 126, 127, 128, 129, 130, 131, 138, 139, 140,
+                                         141, 142, 143, 148, 152, 155, 158, 161, 163, 168, 173, 178, 183, 189, 194,
+                                         198, 203, 225, 232, 268, 269, 276, 277, 283, 290, 306, 310, 313, 319, 321};
+inline bool fp16_explicit_range(int pid) { return (pid >= 90 && pid <= 205) || (pid >= 216 && pid <= 321); }
 
 // INT8 primary pids 0..45 (moonpoly/core/int8/i8_rcc_cost.cu:16-38 tile classes).
 constexpr U kInt8Primary[46] = {
@@ -225,9 +232,14 @@ Fit fit_for(int dtype) {
           fitted_fp32::kFixedMsPerExtraSlice, fitted_fp32::kTileMsPerExtraSlice};
 }
 
+const Fit& fit_of(int dtype) {     // MP_FP16 = 0, MP_INT8 = 1, MP_FP32 = 2
+  static const Fit fits[3] = {fit_for(MP_FP16), fit_for(MP_INT8), fit_for(MP_FP32)};
+  return fits[dtype == MP_FP16 ? 0 : dtype == MP_INT8 ? 1 : 2];
+}
+
 // slot in the fitted tables: primary pids keep their number; 400.. keep theirs (table has 440 slots)
 float fitted_unit_ms(int dtype, int pid, int k_iter) {
-  const Fit f = fit_for(dtype);
+  const Fit& f = fit_of(dtype);
   if (pid < 0 || pid >= f.count || !f.valid[pid] || f.nseg[pid] <= 0) return kInf;
   int seg = f.nseg[pid] - 1;
   for (int i = 0; i < f.nseg[pid]; ++i)
@@ -264,9 +276,9 @@ constexpr float kLaunchMs = 0.0022f;
 
 float reduction_ms(int dtype, int pid, const TileCfg& c, int tiles, int split_k) {
   if (split_k <= 1) return 0.0f;
-  const Fit f = fit_for(dtype);
+  const Fit& f = fit_of(dtype);
   const int extra = split_k - 1;
-  if (!env().disable_fitted && pid >= 0 && pid < f.count && f.valid[pid] && f.red_fixed[pid] >= 0.0) {
+  if (!g_env.disable_fitted && pid >= 0 && pid < f.count && f.valid[pid] && f.red_fixed[pid] >= 0.0) {
     const double r = f.red_fixed[pid] * extra + f.red_tile[pid] * std::max(1, tiles) * extra;
     return (float)std::max(0.0, r);
   }
@@ -326,8 +338,9 @@ TileCfg tile_cfg(int dtype, int pid) {
       if (bn < 16 || bn > 256) return c;
       c.valid = true; c.orient = (pid - 1200) >> 5; c.bn = bn; c.align = 8; c.split_capable = false; c.xm = 2;
       return c;
-    } else if (in_list(kFp16Explicit, 12, pid)) {
-      c.valid = true; c.orient = 0; c.bn = 16; c.align = 8; c.split_capable = true;
+    } else if (fp16_explicit_range(pid)) {
+      c.valid = true; c.orient = 0; c.bn = 16; c.align = in_list(kFp16ExplicitAlign4, 45, pid) ? 4 : 8;
+      c.split_capable = true;
       return c;
     }
     if (base < 0) return c;
@@ -429,23 +442,36 @@ float cost_ms(int dtype, int pid, int split_k, int m, int n, int k) {
   if (pm == nullptr || m <= 0 || n <= 0 || k <= 0) return kInf;
   const TileCfg& c = pm->cfg;
   const int* meta = pm->meta;
-  const int S = std::max(1, split_k);
-  const int lm = std::max(1, cdiv(n, meta[0]));   // feature_m = n
-  const int ln = std::max(1, cdiv(m, meta[1]));   // feature_n = m
-  const int k_iter = std::max(1, cdiv(k, meta[2] * S));
-  const long long units = (long long)lm * ln * S;
-  const int sms = g_num_sms.load(std::memory_order_relaxed);
-  const int waves = std::max(1, ceil_div(units, sms));
+  const unsigned S = (unsigned)std::max(1, split_k);
+  // unsigned 32-bit divisions: an unseen shape costs ~90 of these evaluations
+  const unsigned lm = std::max(1u, ((unsigned)n + (unsigned)meta[0] - 1u) / (unsigned)meta[0]);   // feature_m = n
+  const unsigned ln = std::max(1u, ((unsigned)m + (unsigned)meta[1] - 1u) / (unsigned)meta[1]);   // feature_n = m
+  const unsigned kd = (unsigned)meta[2] * S;
+  const int k_iter = (int)std::max(1u, ((unsigned)k + kd - 1u) / kd);
+  const unsigned long long units = (unsigned long long)lm * ln * S;
+  const unsigned sms = (unsigned)g_num_sms.load(std::memory_order_relaxed);
+  const int waves = units <= sms ? 1 : units < (1ull << 32) ? (int)(((unsigned)units + sms - 1u) / sms)
+                                                            : (int)((units + sms - 1ull) / sms);
+  static const bool* disable_fitted = &env().disable_fitted;      // g_env lives for the whole process; reload_env rewrites it in place
   float unit = kInf;
-  if (!env().disable_fitted) unit = fitted_unit_ms(dtype, pid, k_iter);
+  if (!*disable_fitted) unit = fitted_unit_ms(dtype, pid, k_iter);
   float total;
   if (std::isfinite(unit) && unit > 0.0f) {
     total = waves * unit;
   } else {
-    unit = analytic_unit_ms(dtype, c, k_iter, (int)std::min<long long>(units, sms));
+    unit = analytic_unit_ms(dtype, c, k_iter, (int)std::min<unsigned long long>(units, sms));
     total = waves * unit + kLaunchMs;
   }
-  return total + reduction_ms(dtype, pid, c, lm * ln, S);
+  return total + reduction_ms(dtype, pid, c, (int)(lm * ln), (int)S);
+}
+
+// Split-K hand-off and reduction term alone (gemm_reduction_cost_model of the reference).
+float reduction_cost_ms(int dtype, int pid, int split_k, int m, int n) {
+  const PidMeta* pm = pid_meta(dtype, pid);
+  if (pm == nullptr || m <= 0 || n <= 0) return kInf;
+  const int lm = std::max(1, cdiv(n, pm->meta[0]));
+  const int ln = std::max(1, cdiv(m, pm->meta[1]));
+  return reduction_ms(dtype, pid, pm->cfg, lm * ln, std::max(1, split_k));
 }
 
 int choose_pattern2_split_n(int n) {
@@ -513,6 +539,17 @@ int best_primary(int dtype, int count, int m, int n, int k, float* ms_out) {
   return best;
 }
 
+}  // namespace
+
+// Cheapest primary pid under the K-alignment contract (cutlass_gemm_predict of the reference).
+int predict_primary_pid(int dtype, int m, int n, int k, float* ms) {
+  const int count = dtype == MP_FP16 ? 40 : dtype == MP_INT8 ? 46 : 40;
+  const int pid = best_primary(dtype, count, m, n, k, ms);
+  return pid < 0 ? 0 : pid;
+}
+
+namespace {
+
 mp_plan select_fp16(int m, int n, int k, const LiveFlags& lf) {
   const Env& e = env();
   mp_plan best{MP_PATTERN_SINGLE, 0, 1, 0, kInf};
@@ -532,9 +569,17 @@ mp_plan select_fp16(int m, int n, int k, const LiveFlags& lf) {
         matched = true;
       }
     }
-    for (int i = 0; i < kMeasuredPlanCount; ++i) {
-      const PlanRow& r = kMeasuredPlans[i];
-      if (r.k != k || m < r.m_lo || m > r.m_hi || n < r.n_lo || n > r.n_hi) continue;
+    // rows are looked up through an index sorted by k (built once): a shape scans only its own K's rows
+    static const std::vector<std::pair<int, int>> by_k = [] {
+      std::vector<std::pair<int, int>> v;
+      for (int i = 0; i < kMeasuredPlanCount; ++i) v.emplace_back(kMeasuredPlans[i].k, i);
+      std::stable_sort(v.begin(), v.end(), [](const std::pair<int, int>& a, const std::pair<int, int>& b) { return a.first < b.first; });
+      return v;
+    }();
+    auto it = std::lower_bound(by_k.begin(), by_k.end(), std::make_pair(k, -1));
+    for (; it != by_k.end() && it->first == k; ++it) {
+      const PlanRow& r = kMeasuredPlans[it->second];
+      if (m < r.m_lo || m > r.m_hi || n < r.n_lo || n > r.n_hi) continue;
       if ((r.align_class == 1 && m % 8 != 0) || (r.align_class == 2 && m % 8 == 0)) continue;
       const int S = std::max(1, r.split_k);
       const TileCfg c = tile_cfg(MP_FP16, r.pid);
@@ -619,10 +664,11 @@ mp_plan select_simple(int dtype, int count, int m, int n, int k, bool p3_enabled
   return best;
 }
 
-// plan cache: direct-mapped, guarded by a spin-free seqlock-less mutex (selection itself is ~1 us)
+// plan cache: 2048 sets of two ways (the most recent plan of a set sits in way 0), one mutex; a lookup is a hash,
+// a lock and two compares
 struct CacheLine { int dtype, m, n, k; unsigned flags, epoch; mp_plan plan; };
-constexpr int kCacheSize = 1024;
-CacheLine g_cache[kCacheSize];
+constexpr int kCacheSets = 2048;
+CacheLine g_cache[kCacheSets][2];
 std::mutex g_cache_mu;
 
 inline unsigned hash_shape(int dtype, int m, int n, int k, unsigned flags) {
@@ -630,7 +676,10 @@ inline unsigned hash_shape(int dtype, int m, int n, int k, unsigned flags) {
   h ^= ((uint64_t)(unsigned)n + 0x7F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
   h ^= ((uint64_t)(unsigned)k + 0x1CE4E5B9ull) * 0x94D049BB133111EBull;
   h ^= (uint64_t)flags * 0x2545F4914F6CDD1Dull + (uint64_t)dtype;
-  return (unsigned)(h >> 40) & (kCacheSize - 1);
+  return (unsigned)(h >> 40) & (kCacheSets - 1);
+}
+inline bool line_is(const CacheLine& c, int dtype, int m, int n, int k, unsigned flags, unsigned epoch) {
+  return c.epoch == epoch && c.dtype == dtype && c.m == m && c.n == n && c.k == k && c.flags == flags;
 }
 
 }  // namespace
@@ -642,9 +691,12 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
   const unsigned slot = hash_shape(dtype, m, n, k, fkey);
   {
     std::lock_guard<std::mutex> g(g_cache_mu);
-    const CacheLine& c = g_cache[slot];
-    if (c.epoch == epoch && c.dtype == dtype && c.m == m && c.n == n && c.k == k && c.flags == fkey)
-      return c.plan;
+    CacheLine* set = g_cache[slot];
+    if (line_is(set[0], dtype, m, n, k, fkey, epoch)) return set[0].plan;
+    if (line_is(set[1], dtype, m, n, k, fkey, epoch)) {
+      std::swap(set[0], set[1]);
+      return set[0].plan;
+    }
   }
   mp_plan plan;
   const Env& e = env();
@@ -691,7 +743,8 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
   }
   {
     std::lock_guard<std::mutex> g(g_cache_mu);
-    g_cache[slot] = CacheLine{dtype, m, n, k, fkey, epoch, plan};
+    g_cache[slot][1] = g_cache[slot][0];
+    g_cache[slot][0] = CacheLine{dtype, m, n, k, fkey, epoch, plan};
   }
   return plan;
 }
@@ -753,6 +806,8 @@ ScaledCfg scaled_mm_select(int M, int N, int K) {
   }
   return best;
 }
+
+bool is_explicit_neighborhood_fp16_pid(int pid) { return fp16_explicit_range(pid) || (pid >= 400 && pid <= 439); }
 
 int elite_fp16_pids(int* pids, int capacity) {
   int count = 0;

@@ -35,6 +35,10 @@ void pid_tile_meta(int dtype, int pid, int out[3]);
 // convention of the reference: feature_m = n, feature_n = m (core/fp16/fp16_rcc.cu:451-458).
 float cost_ms(int dtype, int pid, int split_k, int m, int n, int k);
 
+// The split-K hand-off / reduction term of cost_ms alone, and the cheapest primary pid for a shape.
+float reduction_cost_ms(int dtype, int pid, int split_k, int m, int n);
+int predict_primary_pid(int dtype, int m, int n, int k, float* ms);
+
 // Online selection (memoised per shape and flag state).
 mp_plan select_plan(int dtype, int m, int n, int k);
 
@@ -48,6 +52,8 @@ void scaled_mm_config_meta(int id, int out[4]);
 constexpr int kScaledConfigCount = 6;
 
 int elite_fp16_pids(int* pids, int capacity);
+// pid ranges 90..205, 216..321 and 400..439 (generated/fp16/rcc/candidates.cu:62-65)
+bool is_explicit_neighborhood_fp16_pid(int pid);
 
 void reload_env();
 int num_sms_for_model();

@@ -27,15 +27,6 @@ namespace mp {
 
 __device__ int g_mp_status = 0;   // 0 = ok; otherwise the first MP_DEV_* code any kernel recorded
 
-// Optional phase tracing (compile with -DMP_TRACE): per CTA, nanosecond timestamps of the phases
-// of its first work unit.  Off in the shipped library.
-#ifdef MP_TRACE
-__device__ unsigned long long g_mp_trace[160][16];
-#define MP_TRACE_MARK(slot) do { g_mp_trace[blockIdx.x][slot] = globaltimer_ns(); } while (0)
-#else
-#define MP_TRACE_MARK(slot) do { } while (0)
-#endif
-
 constexpr int kUmmaM = 128;            // rows of X per tile
 constexpr int kRowBytes = 128;         // one K block = 128 bytes of K per row (64 fp16 / 128 int8)
 constexpr int kXTileBytes = kUmmaM * kRowBytes;
@@ -384,7 +375,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   int* status = &g_mp_status;
 
   if (threadIdx.x == 0) {
-    MP_TRACE_MARK(0);
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -412,7 +402,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   // the next kernel start its own prologue now.  Each role then waits (griddep_wait) before its
   // first access to global memory that the previous kernel may still produce or use: the
   // operands, C, the split-K scratch.  The MMA issuer touches only shared memory and TMEM.
-  if (threadIdx.x == 0) MP_TRACE_MARK(1);
   griddep_launch_dependents();
 
   constexpr int kElemsPerKb = (KIND == KIND_I8) ? 128 : 64;
@@ -444,7 +433,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
       }
       griddep_wait();
-      MP_TRACE_MARK(2);
       uint32_t it = 0;
       int s = 0;
       uint32_t ph = 0;
@@ -517,8 +505,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         uint32_t first = 0u;                                            // 0 until the accumulators hold a product
         for (int kb = u.kb0; kb < u.kb1; kb += p.kc) {
           if (!mbar_wait(full_bar(s), ph, status, MP_DEV_TIMEOUT_MMA_FULL)) { ok = false; break; }
-          if (ui == 0 && kb == u.kb0) MP_TRACE_MARK(3);
-          if (ui == 0 && kb + p.kc >= u.kb1) MP_TRACE_MARK(4);
           tc_fence_after();
           uint64_t ad = desc0 + (uint64_t)((uint32_t)s * stage16);
           uint64_t bd = ad + (uint64_t)((uint32_t)p.kc * x16);
@@ -589,7 +575,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         st.sq = sq_s; st.bq = bq_s; st.q_base = qb; st.sp = sp_h[0]; st.bp = bp_h[0];
       }
       if (!mbar_wait(tfull_bar((int)buf), use & 1u, status, MP_DEV_TIMEOUT_EPILOGUE)) { ok = false; break; }
-      if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(5);
       tc_fence_after();
       uint32_t t_addr = tmem_base + buf * (uint32_t)kMaxBN + ((uint32_t)(quad * 32) << 16);
       const int row_in_tile = quad * 32 + lane;
@@ -643,7 +628,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));   // TMEM buffer is free again
-        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(6);
         __threadfence();
         __syncwarp();
         // Reduction of this quadrant of the tile.  Share i is the run of 16-column chunks
@@ -662,7 +646,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         unsigned ticket = 0;
         if (lane == 0) ticket = atomicAdd(ctr, 1u);
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
-        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(7);
         const int chunks = r.bn >> 4;
         const bool last = ticket == (unsigned)(S - 1);
         const unsigned all_shares = (1u << S) - 1u;      // S <= 31
@@ -733,7 +716,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           }
         }
         __syncwarp();
-        if (ui == 0 && warp == 2 && lane == 0) MP_TRACE_MARK(8);
         if (lane == 0) {
           // the last warp to leave restores the counters (nobody polls or claims any more)
           if (atomicAdd(ctr + 2, 1u) == (unsigned)(S - 1)) { ctr[0] = 0u; ctr[1] = 0u; ctr[2] = 0u; }
@@ -745,7 +727,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) MP_TRACE_MARK(9);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();

@@ -6,8 +6,15 @@
 #include <iostream>
 #include <stdexcept>
 
+#include <cstdlib>
+#include <limits>
+#include <mutex>
+#include <vector>
+
 #include "../../include/moonpoly_abi.h"
+#include "candidates.cuh"
 #include "moonpoly.cuh"
+#include "moonpoly_cost.cuh"
 
 namespace moonpoly {
 namespace {
@@ -161,5 +168,135 @@ void run_moonpoly_selected_gemm_fp32_row_col_col(int pid, int m, int n, int k, c
                                                  float* C, float a, float b, cudaStream_t stream) {
   check(mp_gemm_rcc_pid(MP_FP32, pid, 1, m, n, k, A, B, C, a, b, nullptr, 0, stream));
 }
+
+// ---- metadata and routing API of generated/fp16/rcc/candidates.cuh:9-18 ----
+namespace fp16 {
+namespace row_col_col {
+
+bool is_explicit_neighborhood_pid(int pid) { return mp_is_explicit_neighborhood_pid(pid) != 0; }
+
+namespace {
+const std::vector<int>& elite() {
+  static const std::vector<int> pids = [] {
+    std::vector<int> v((size_t)mp_elite_fp16_pids(nullptr, 0));
+    mp_elite_fp16_pids(v.data(), (int)v.size());
+    return v;
+  }();
+  return pids;
+}
+}  // namespace
+
+bool is_paper_elite_fp16_pid(int pid) {
+  for (int p : elite())
+    if (p == pid) return true;
+  return false;
+}
+int paper_elite_fp16_kernel_count() { return (int)elite().size(); }
+const int* paper_elite_fp16_pids() { return elite().data(); }
+
+// the reference answers 1 / SharedMem() for a pid outside the explicit ranges (candidates.cu:66-112, 114-486)
+int explicit_neighborhood_alignment(int pid) {
+  int alignment = 1;
+  if (!is_explicit_neighborhood_pid(pid) || mp_pid_info(MP_FP16, pid, nullptr, &alignment) != MP_OK) return 1;
+  return alignment;
+}
+SharedMem explicit_neighborhood_shared_mem(int pid) {
+  int t[3] = {0, 0, 0};
+  if (!is_explicit_neighborhood_pid(pid) || mp_pid_info(MP_FP16, pid, t, nullptr) != MP_OK) return SharedMem();
+  return SharedMem(t[0], t[2], t[1]);      // SharedMem(pm, pk, pn)
+}
+void run_explicit_neighborhood_gemm(int pid, int m, int n, int k, cutlass::half_t* A, cutlass::half_t* B,
+                                    cutlass::half_t* C, float alpha, float beta, int split_k_slices,
+                                    cudaStream_t stream) {
+  if (!is_explicit_neighborhood_pid(pid)) return;     // the reference's switch falls through to `default: return;`
+  // pids 400..439 honour the run-time split; the others are single-slice kernels in the reference
+  const int split = (pid >= 400 && pid <= 439) ? split_k_slices : 1;
+  check(mp_gemm_rcc_pid(MP_FP16, pid, split, m, n, k, A, B, C, alpha, beta, nullptr, 0, stream));
+}
+
+// ---- FP16 cost API (core/fp16/fp16_rcc_cost.cu:143-279); ims is tiled by pm (RCC n), ins by pn (RCC m) ----
+const int num_gemm_primary = 41;
+
+namespace {
+float cost(int dtype, int pid, int split, int ims, int ins, int iks) {
+  float ms = std::numeric_limits<float>::infinity();
+  if (mp_cost_ms(dtype, pid, split, /*m=*/ins, /*n=*/ims, iks, &ms) != MP_OK)
+    return std::numeric_limits<float>::infinity();
+  return ms;
+}
+int predict(int dtype, int fm, int fn, int k) {
+  int pid = 0;
+  if (mp_cost_predict_pid(dtype, /*m=*/fn, /*n=*/fm, k, &pid, nullptr) != MP_OK) return 0;
+  return pid;
+}
+// MOONPOLY_DISABLE_FITTED_COST is read when the library parses its flags; toggle it around one evaluation
+std::mutex g_env_mu;
+float cost_with_fitted(bool fitted, int dtype, int pid, int ims, int ins, int iks) {
+  std::lock_guard<std::mutex> g(g_env_mu);
+  const char* old = std::getenv("MOONPOLY_DISABLE_FITTED_COST");
+  const std::string saved = old ? old : "";
+  setenv("MOONPOLY_DISABLE_FITTED_COST", fitted ? "0" : "1", 1);
+  mp_reload_env();
+  const float v = cost(dtype, pid, 1, ims, ins, iks);
+  if (old) setenv("MOONPOLY_DISABLE_FITTED_COST", saved.c_str(), 1);
+  else unsetenv("MOONPOLY_DISABLE_FITTED_COST");
+  mp_reload_env();
+  return v;
+}
+}  // namespace
+
+float analytic_gemm_cost_model(int ims, int ins, int iks, int pid) { return cost_with_fitted(false, MP_FP16, pid, ims, ins, iks); }
+float fitted_gemm_cost_model(int ims, int ins, int iks, int pid) { return cost_with_fitted(true, MP_FP16, pid, ims, ins, iks); }
+float gemm_cost_model(int ims, int ins, int iks, int pid) { return cost(MP_FP16, pid, 1, ims, ins, iks); }
+float gemm_splitk_cost_model(int ims, int ins, int iks, int pid, int split_k_slices) {
+  return cost(MP_FP16, pid, split_k_slices, ims, ins, iks);
+}
+float gemm_reduction_cost_model(int ims, int ins, int, int pid, int split_k_slices) {
+  if (split_k_slices <= 1) return 0.0f;
+  float ms = 0.0f;
+  if (mp_cost_reduction_ms(MP_FP16, pid, split_k_slices, /*m=*/ins, /*n=*/ims, &ms) != MP_OK) return 0.0f;
+  return ms;
+}
+int cutlass_gemm_predict(int m, int n, int k) {
+  const int pid = predict(MP_FP16, m, n, k);
+  if (std::getenv("MOONPOLY_DEBUG_PREDICT"))
+    std::cout << "[moonpoly][fp16] predict m=" << m << " n=" << n << " k=" << k << " -> pid=" << pid << std::endl;
+  return pid;
+}
+void dump_cost_model(int ims, int ins, int iks, int pid) {
+  int t[3] = {1, 1, 1};
+  if (mp_pid_info(MP_FP16, pid, t, nullptr) != MP_OK) return;
+  const int lm = (ims + t[0] - 1) / t[0], ln = (ins + t[1] - 1) / t[1];
+  const int sms = mp_num_sms() > 0 ? mp_num_sms() : num_SM;
+  const int waves = (lm * ln + sms - 1) / sms;
+  std::cout << "f_wave:" << waves << "; f_pipe:" << cost(MP_FP16, pid, 1, ims, ins, iks) / (waves > 0 ? waves : 1) << std::endl;
+}
+
+}  // namespace row_col_col
+}  // namespace fp16
+
+// ---- FP32 / INT8 cost API (core/fp32/fp32_rcc_cost.cu:128-233, core/int8/i8_rcc_cost.cu:141-246): the split-K
+// model of these two dtypes prices the dedicated split-K tile, which the C ABI addresses as pid -1 ----
+namespace fp32 {
+namespace simt {
+namespace row_col_col {
+float gemm_cost_model(int ims, int ins, int iks, int pid) { return fp16::row_col_col::cost(MP_FP32, pid, 1, ims, ins, iks); }
+float gemm_splitk_cost_model(int ims, int ins, int iks, int split_k_slices) {
+  return fp16::row_col_col::cost(MP_FP32, 23, split_k_slices, ims, ins, iks);
+}
+int cutlass_gemm_predict(int m, int n, int k) { return fp16::row_col_col::predict(MP_FP32, m, n, k); }
+}  // namespace row_col_col
+}  // namespace simt
+}  // namespace fp32
+
+namespace int8 {
+namespace row_col_col {
+float gemm_cost_model(int ims, int ins, int iks, int pid) { return fp16::row_col_col::cost(MP_INT8, pid, 1, ims, ins, iks); }
+float gemm_splitk_cost_model(int ims, int ins, int iks, int split_k_slices) {
+  return fp16::row_col_col::cost(MP_INT8, 6, split_k_slices, ims, ins, iks);
+}
+int cutlass_gemm_predict(int m, int n, int k) { return fp16::row_col_col::predict(MP_INT8, m, n, k); }
+}  // namespace row_col_col
+}  // namespace int8
 
 }  // namespace moonpoly

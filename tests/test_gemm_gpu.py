@@ -555,3 +555,55 @@ def test_fp32_streaming_kernel(api, oracle, m, n, k):
     assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1).cpu().numpy(), exact.astype(np.float32))
     got = api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1, c_nm=dev(c0).clone(), alpha=2.0, beta=-1.0).cpu().numpy()
     assert np.array_equal(got, (2 * exact - c0.astype(np.int64)).astype(np.float32))
+
+
+def test_scaled_mm_padded_leading_dimensions_and_ragged_k(api, oracle):
+    """Rows that are padded to a 16-byte multiple while K itself is not (K = 100, lda = ldb = 112): the streaming
+    kernels walk K in whole 16-byte chunks and must not be chosen; the tensor tiles zero-fill the K tail."""
+    L = api.lib()
+    K, ld = 100, 112
+    for (M, N) in ((5, 48), (40, 200), (300, 24)):
+        a = rng.int8_uniform(110, 0, (M, K))
+        b = rng.int8_uniform(110, 1, (N, K))
+        sa = rng.uniform(110, 2, (M,), 0.001, 0.02)
+        sb = rng.uniform(110, 3, (N,), 0.001, 0.02)
+        ap = np.full((M, ld), 77, np.int8); ap[:, :K] = a          # the padding holds garbage on purpose
+        bp = np.full((N, ld), -55, np.int8); bp[:, :K] = b
+        A, B, SA, SB = dev(ap), dev(bp), dev(sa), dev(sb)
+        out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+        rc = L.mp_scaled_mm_i8(M, N, K, A.data_ptr(), ld, B.data_ptr(), ld, SA.data_ptr(), 0, SB.data_ptr(), 0, None,
+                               out.data_ptr(), N, 0, None)
+        assert rc == 0, L.mp_last_error_string()
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), oracle.scaled_mm_i8(a, b, sa, sb)), (M, N)
+
+
+def test_library_scratch_regrows_behind_a_large_counter_area(api):
+    """A forced split-K call with 2592 tiles gives the library's own scratch a 162 KB counter area (the default is
+    64 KB) in front of 82 MB of partial sums.  The next call has few tiles but needs 82 MB + 32 KB of partial sums:
+    that fits behind a 64 KB counter area, not behind the one the buffer really has, so the buffer must grow.
+    Integer-valued inputs: results are exact whatever the summation order."""
+    k = 1024
+    a1 = rng.small_ints(120, 0, (2304, k), lo=-1, hi=1)            # 18 x 144 tiles of 128 x 16
+    b1 = rng.small_ints(120, 1, (2304, k))
+    got = api.gemm_rcc_tile(dev(a1), dev(b1), 0, 16, split_k=2).cpu().numpy()
+    assert np.array_equal(got, _exact_ref(a1, b1).astype(np.float16))
+    a2 = rng.small_ints(121, 0, (640, k), lo=-1, hi=1)             # 5 x 25 tiles of 128 x 224, 6 slices
+    b2 = rng.small_ints(121, 1, (5600, k))
+    got = api.gemm_rcc_tile(dev(a2), dev(b2), 0, 224, split_k=6).cpu().numpy()
+    assert np.array_equal(got, _exact_ref(a2, b2).astype(np.float16))
+    again = api.gemm_rcc_tile(dev(a1), dev(b1), 0, 16, split_k=2).cpu().numpy()
+    assert np.array_equal(again, _exact_ref(a1, b1).astype(np.float16))
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("pid,m,n", [(1101, 130, 65), (1101, 65, 130), (1100, 130, 65), (1101, 200, 300)])
+def test_reported_workspace_is_enough_for_the_streaming_pids_fallback(api, oracle, pid, m, n):
+    k, split = 2048, 2
+    a = rng.normal(122, 0, (m, k), 0.05)
+    b = rng.normal(122, 1, (n, k), 0.05)
+    need = api.workspace_size(api.MP_FP16, pid, m, n, k, split)
+    assert need > 0
+    ws = torch.full((need,), 0xCD, dtype=torch.uint8, device=DEV)
+    c = api.gemm_rcc_pid(dev(a), dev(b), pid, split, workspace=ws).cpu().numpy()
+    close_f16(c, oracle.gemm_f16_rcc(a, b))
