@@ -15,9 +15,16 @@ ranks and `value` counts the FLOPs of all ranks.
 `e2e` is the same metric with the activations A copied from pinned host memory and C copied back
 to pinned host memory inside the timed region of every GEMM (the weight stays resident, as a
 model parameter does).  `roofline` describes the dominant kernel (the tcgen05 GEMM at M = 4096)
-and `per_shape` the fraction of max(FLOPs/peak, bytes/HBM) each shape reaches.  `cpu_baseline` is
-the CPU oracle (the reference's host check loop restated, all host threads) on a bounded sample.
-`--impl reference` times that same CPU implementation alone.
+and carries the whole-sweep figures too: `sweep_geomean_frac`, `per_shape_frac` (fraction of
+max(FLOPs/peak, bytes/HBM) per M), and the side tables `int8_scaled_mm`, `fp16_splitk_decode`,
+`fp32_m37` and `stack` (the Llama-3-70B-shaped sharded linear stack at this GPU count).
+`cpu_baseline` is the CPU oracle (the reference's host check loop restated, all host threads) on a
+bounded sample; `--impl reference` times that same CPU implementation alone on the same 14 shapes
+(large M on a row sample, scaled).
+
+    python bench.py --case fp16:4096x4096x4096 [--case-pid P --case-split S] [--case-scaled]
+                    [--case-launches 3] [--case-copies 2]
+runs ONE small case a few times and exits: the command the profiler captures in profiles/ use.
 """
 import argparse
 import json
@@ -70,57 +77,74 @@ def load_peaks():
 # ------------------------------------------------------------------------------------------------
 # CPU legs (the only place outside tests/ and smoke() that touches oracle/)
 # ------------------------------------------------------------------------------------------------
-def cpu_inputs(m_list, seed=1):
-    from moonpoly_b200 import rng
-    b = rng.normal(seed, rng.STREAM_B, (N_DIM, K_DIM), 0.05)
-    a = {m: rng.normal(seed, rng.STREAM_A, (m, K_DIM), 0.05) for m in m_list}
-    return a, b
+CPU_FULL_ROWS = 128        # shapes up to this M run in full on the CPU; larger M run CPU_SAMPLE_ROWS rows and are scaled
+CPU_SAMPLE_ROWS = 64
 
 
 def cpu_time_shapes(m_list, budget_s, a=None, b=None):
-    """Times the oracle on the sweep's shapes in ascending M until `budget_s` is spent."""
+    """Times the oracle on the sweep's shapes in ascending M until `budget_s` is spent.  Every output row is an
+    independent set of dot products in the naive loop, so a shape above CPU_FULL_ROWS rows is timed on its first
+    CPU_SAMPLE_ROWS rows and scaled by M / CPU_SAMPLE_ROWS.  Returns [(M, seconds for the whole shape)]."""
     from oracle import oracle
     oracle.build()
     cores = oracle.host_threads()
     if a is None:
-        a, b = cpu_inputs(m_list)
+        a, b = cpu_inputs_sampled(m_list)
     out, spent = [], 0.0
     for m in m_list:
+        rows = m if m <= CPU_FULL_ROWS else CPU_SAMPLE_ROWS
         t0 = time.perf_counter()
-        oracle.gemm_f16_rcc(a[m], b, threads=cores)
+        oracle.gemm_f16_rcc(a[m][:rows], b, threads=cores)
         dt = time.perf_counter() - t0
-        out.append((m, dt))
+        out.append((m, dt * m / rows))
         spent += dt
         if spent > budget_s:
             break
     return out, cores
 
 
+def cpu_inputs_sampled(m_list, seed=1):
+    from moonpoly_b200 import rng
+    b = rng.normal(seed, rng.STREAM_B, (N_DIM, K_DIM), 0.05)
+    a = {m: rng.normal(seed, rng.STREAM_A, (min(m, CPU_FULL_ROWS if m <= CPU_FULL_ROWS else CPU_SAMPLE_ROWS), K_DIM), 0.05)
+         for m in m_list}
+    return a, b
+
+
+def sweep_config(world):
+    return {"workload": WORKLOAD, "sweep_m": SWEEP_M, "n": N_DIM, "k": K_DIM,
+            "reps_per_shape": {str(m): reps_for(m) for m in SWEEP_M},
+            "l2": f"inputs larger than L2: {WEIGHT_COPIES} rotating copies of the 32 MiB weight (256 MiB)",
+            "entry": "mp_gemm (online selector)", "parallelism": f"column-parallel x{world}, no collective"}
+
+
 def run_reference(args, rank, world):
     """The reference's CPU implementation of the path (its host check loop, restated in
-    oracle/mp_oracle.c) on all host threads; rank 0 only."""
+    oracle/mp_oracle.c) on all host threads, over the same 14 shapes as the GPU arm; rank 0 only."""
     if rank != 0:
         return
-    sample = [m for m in SWEEP_M if m <= 16]
-    a, b = cpu_inputs(sample)
+    a, b = cpu_inputs_sampled(SWEEP_M)
     for _ in range(args.warmup):
-        cpu_time_shapes(sample[:2], 1e9, a, b)
-    per_shape = {m: 0.0 for m in sample}
+        cpu_time_shapes(SWEEP_M[:3], 1e9, a, b)
+    per_shape = {m: 0.0 for m in SWEEP_M}
     t0 = time.perf_counter()
     cores = 1
     for _ in range(args.steps):
-        res, cores = cpu_time_shapes(sample, 1e9, a, b)
+        res, cores = cpu_time_shapes(SWEEP_M, 1e9, a, b)
         for m, dt in res:
             per_shape[m] += dt
     total = time.perf_counter() - t0
-    value = geomean([flops(m) / (per_shape[m] / args.steps) / 1e12 for m in sample])
+    per_tfl = {m: flops(m) / (per_shape[m] / args.steps) / 1e12 for m in SWEEP_M}
+    value = geomean([per_tfl[m] for m in SWEEP_M])
+    sample = (f"all 14 sweep shapes every step; M <= {CPU_FULL_ROWS} in full, larger M on {CPU_SAMPLE_ROWS} rows "
+              f"scaled by M/{CPU_SAMPLE_ROWS}")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": "M in {1,2,4,8,16} of the sweep per step"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": "sweep shapes M in {1,2,4,8,16}, N=K=4096, every step"},
+        "config": sweep_config(world),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+                         "per_shape_tflops": {str(m): round(per_tfl[m], 5) for m in SWEEP_M}},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -194,17 +218,24 @@ def extra_sections(api, L, st, dev, peaks):
 
     vp = ctypes.c_void_p
     out = {}
-    # ---- INT8 scaled_mm: (N,K) of qkv / o_proj / gate_up / down, M = clamp(round(8192**u), 1, 8192), seed 3
+    # ---- INT8 scaled_mm: (N,K) of qkv / o_proj / gate_up / down, M = clamp(round(8192**u), 1, 8192), seed 3;
+    # A, B int8 U{-127..127} and the fp32 scales U[0.001, 0.02] from the seeded stateless generator
     ms_list = rng.log_uniform_ints(3, rng.STREAM_SHAPES, 32, 1, 8192)
-    int8_peak = 2.0 * peaks["tflops"]          # no measured INT8 peak on this pool: twice the bf16 figure
-    fr, tops, rows = [], [], []
+    # no INT8 peak is measured on this pool: the denominator is twice the measured bf16 burst figure (tcgen05 kind::i8
+    # issues twice the MACs per instruction), and torch._int_mm on the same box is timed below as a same-box ceiling
+    int8_peak = 2.0 * peaks["tflops"]
+    fr, tops, rows, by_layer = [], [], [], {}
     for (N, K) in [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]:
         copies = 3 if N * K < 64 << 20 else 2
-        ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(copies)]
-        sb = torch.rand((N,), device=dev) * 0.019 + 0.001
+        w0 = torch.from_numpy(rng.int8_uniform(3, rng.STREAM_B, (N, K))).to(dev)
+        ws = [w0] + [torch.roll(w0, shifts=5 * i, dims=0).contiguous() for i in range(1, copies)]
+        sb = torch.from_numpy(rng.uniform(3, rng.STREAM_B_SCALE, (N,), 0.001, 0.02)).to(dev)
+        a_all = torch.from_numpy(rng.int8_uniform(3, rng.STREAM_A, (8192, K))).to(dev)
+        sa_all = torch.from_numpy(rng.uniform(3, rng.STREAM_A_SCALE, (8192,), 0.001, 0.02)).to(dev)
+        layer_fr = []
         for M in ms_list:
-            a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
-            sa = torch.rand((M,), device=dev) * 0.019 + 0.001
+            a = a_all[:M]
+            sa = sa_all[:M]
             o = torch.empty((M, N), dtype=torch.float16, device=dev)
 
             def call(i):
@@ -216,20 +247,33 @@ def extra_sections(api, L, st, dev, peaks):
             byts = M * K + N * K + 2.0 * M * N + 4.0 * (M + N)
             roof = max(ops / (int8_peak * 1e12), byts / (peaks["hbm_gbs"] * 1e9))
             fr.append(roof / t)
+            layer_fr.append(roof / t)
             tops.append(ops / t / 1e12)
-            rows.append({"N": N, "K": K, "M": M, "us": round(t * 1e6, 2), "tops": round(ops / t / 1e12, 2),
-                         "frac": round(roof / t, 4)})
-        del ws
-    out["int8_scaled_mm"] = {"geomean_tops": geomean(tops), "roofline_geomean_frac": geomean(fr),
-                             "int8_peak_tops_assumed": int8_peak, "shapes": len(rows),
-                             "worst": sorted(rows, key=lambda r: r["frac"])[:3], "best": sorted(rows, key=lambda r: -r["frac"])[:3]}
+            rows.append([N, K, M, round(t * 1e6, 2), round(roof / t, 3)])
+        by_layer[f"{N}x{K}"] = round(geomean(layer_fr), 4)
+        del ws, w0
+    ceiling = {}
+    try:
+        for (M, N, K) in [(4096, 4096, 4096), (8192, 28672, 4096)]:
+            a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+            b = torch.randint(-127, 128, (K, N), dtype=torch.int8, device=dev)
+            t = ev_time(lambda i: torch._int_mm(a, b), 5)
+            ceiling[f"{M}x{N}x{K}"] = round(2.0 * M * N * K / t / 1e12, 1)
+    except Exception as e:      # harness-only figure: its absence changes nothing else
+        ceiling = {"unavailable": str(e)[:80]}
+    out["int8_scaled_mm"] = {"geomean_tops": round(geomean(tops), 2), "roofline_geomean_frac": round(geomean(fr), 4),
+                             "int8_peak_tops": int8_peak, "int8_peak_source": "2 x measured bf16 burst (no measured INT8 peak on this pool)",
+                             "torch_int_mm_tops_same_box": ceiling, "shapes": len(rows), "geomean_frac_by_layer": by_layer,
+                             "rows_n_k_m_us_frac": rows}
     # ---- FP16 decode-shaped split-K through pids 400+ (Linear mapping), seed 2
     rows, fr, fr_sel = [], [], []
     for (N, K) in [(1024, 8192), (4096, 14336), (1024, 28672)]:
         copies = max(2, min(8, (300 << 20) // (N * K * 2)))
-        ws = [(torch.randn((N, K), device=dev) * 0.05).half() for _ in range(copies)]
+        w0 = torch.from_numpy(rng.normal(2, rng.STREAM_B, (N, K), 0.05)).to(dev)
+        ws = [w0] + [torch.roll(w0, shifts=3 * i, dims=0).contiguous() for i in range(1, copies)]
+        x_all = torch.from_numpy(rng.normal(2, rng.STREAM_A, (32, K), 0.05)).to(dev)
         for M in (1, 8, 16, 32):
-            x = (torch.randn((M, K), device=dev) * 0.05).half()
+            x = x_all[:M]
             y = torch.empty((M, N), dtype=torch.float16, device=dev)
             best = None
             for pid in (400, 407, 413, 425, 439):
@@ -251,9 +295,9 @@ def extra_sections(api, L, st, dev, peaks):
             t_sel = ev_time(call_sel, 12)
             fr_sel.append(roof / t_sel)
             rows.append({"M": M, "N": N, "K": K, "best_us": round(best[0] * 1e6, 2), "pid": best[1], "split_k": best[2],
-                         "gbs": round(byts / best[0] / 1e9, 1), "frac": round(roof / best[0], 4),
+                         "frac": round(roof / best[0], 4),
                          "selector_us": round(t_sel * 1e6, 2), "selector_frac": round(roof / t_sel, 4)})
-        del ws
+        del ws, w0
     # ---- FP32 config shape (M=37, N=K=1024, seed 0) through mp_gemm: CUDA-core FFMA tiles, launch-latency bound
     a32 = torch.from_numpy(rng.uniform(0, rng.STREAM_A, (37, 1024), -1.0, 1.0)).to(dev)
     b32 = [torch.from_numpy(rng.uniform(0, rng.STREAM_B, (1024, 1024), -1.0, 1.0)).to(dev) for _ in range(2)]
@@ -264,8 +308,11 @@ def extra_sections(api, L, st, dev, peaks):
                        1.0, 0.0, st)
         assert rc == 0, L.mp_last_error_string()
     t32 = ev_time(call32, 50)
-    out["fp32_m37_n1024_k1024"] = {"us": round(t32 * 1e6, 2), "gflops": round(2.0 * 37 * 1024 * 1024 / t32 / 1e9, 1),
-                                   "plan": repr(api.select_plan(api.MP_FP32, 37, 1024, 1024))}
+    b32_bytes = 4.0 * (37 * 1024 + 1024 * 1024 + 37 * 1024)
+    out["fp32_m37"] = {"us": round(t32 * 1e6, 2), "gflops": round(2.0 * 37 * 1024 * 1024 / t32 / 1e9, 1),
+                       "hbm_roofline_frac": round(b32_bytes / (peaks["hbm_gbs"] * 1e9) / t32, 4),
+                       "note": "4.5 MB problem: the HBM roofline is 0.7 us, below the launch-to-launch floor of any kernel",
+                       "plan": repr(api.select_plan(api.MP_FP32, 37, 1024, 1024))}
     # ---- host cost of a selection (mp_select_plan through ctypes; the empty-call cost of ctypes is measured with
     # mp_num_sms and subtracted): warm = the same shape again (plan cache hit), cold = shapes never seen before
     plan = api.Plan()
@@ -273,7 +320,7 @@ def extra_sections(api, L, st, dev, peaks):
     n_calls = 20000
     t0 = time.perf_counter()
     for i in range(n_calls):
-        L.mp_num_sms()
+        L.mp_select_plan(9, 1, 1, 1, pref)        # same argument list, returns at its first check: the cost of the ctypes call
     t_empty = (time.perf_counter() - t0) / n_calls
     t0 = time.perf_counter()
     for i in range(n_calls):
@@ -285,8 +332,8 @@ def extra_sections(api, L, st, dev, peaks):
     t_cold = (time.perf_counter() - t0) / n_calls
     out["selector_host_us"] = {"warm": round(max(0.0, t_warm - t_empty) * 1e6, 3), "cold": round(max(0.0, t_cold - t_empty) * 1e6, 3),
                                "ctypes_empty_call": round(t_empty * 1e6, 3), "calls": n_calls}
-    out["fp16_splitk_decode"] = {"roofline_geomean_frac": geomean(fr), "selector_roofline_geomean_frac": geomean(fr_sel),
-                                 "rows": rows}
+    out["fp16_splitk_decode"] = {"roofline_geomean_frac": round(geomean(fr), 4),
+                                 "selector_roofline_geomean_frac": round(geomean(fr_sel), 4), "rows": rows}
     return out
 
 
@@ -301,7 +348,6 @@ def run_ours(args, rank, world, local_rank):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        os.environ["NCCL_DEBUG"] = os.environ.get("MP_BENCH_NCCL_DEBUG", "WARN")   # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     L = api.lib()
@@ -432,6 +478,15 @@ def run_ours(args, rank, world, local_rank):
     code = api.device_status()
     assert code == 0
 
+    # the Llama-3-70B-shaped linear stack, N-sharded over the ranks (all-gather after o_proj and down when world > 1):
+    # a few steps at this GPU count, reported inside `roofline.stack`
+    stack_line = stack_nccl = None
+    if not args.no_stack:
+        from moonpoly_b200 import stack as stack_mod
+        stack_line = stack_mod.run_stack(rank, world, dev, dist, steps=args.stack_steps, warmup=2, gather="fused", root=ROOT)
+        if world > 1:      # the same steps with ncclAllGather instead of the fused peer stores, for comparison
+            stack_nccl = stack_mod.run_stack(rank, world, dev, dist, steps=args.stack_steps, warmup=2, gather="nccl", root=ROOT)
+
     def reduce_max(d):
         t = torch.tensor([d[m] for m in SWEEP_M], dtype=torch.float64, device=dev)
         if dist is not None:
@@ -469,8 +524,8 @@ def run_ours(args, rank, world, local_rank):
         if os.path.exists(traffic_path):
             with open(traffic_path) as fh:
                 traffic = json.load(fh).get("umma_gemm_f16_m4096_dram_bytes_per_launch")
-        # CPU baseline: the oracle on this box's host cores, bounded sample
-        cpu_res, cores = cpu_time_shapes([m for m in SWEEP_M if m <= 128], args.cpu_budget)
+        # CPU baseline: the oracle on this box's host cores, bounded sample (all 14 shapes; rows sampled above 128)
+        cpu_res, cores = cpu_time_shapes(SWEEP_M, args.cpu_budget)
         cpu_val = geomean([flops(m) / dt / 1e12 for m, dt in cpu_res])
         h2d = sum(max(2, reps_for(m) // 4) * m * K_DIM * 2 for m in SWEEP_M)
         d2h = sum(max(2, reps_for(m) // 4) * m * N_DIM * 2 for m in SWEEP_M)
@@ -511,24 +566,35 @@ def run_ours(args, rank, world, local_rank):
             extras["cuda_graph_replay"] = {"value": geomean(graph_tfl), "unit": "TFLOP/s",
                                            "per_shape_us": {str(m): round(flops(m) / (t * 1e12) * 1e6, 2)
                                                             for m, t in zip(SWEEP_M, graph_tfl)}}
+        sweep_frac = geomean([p["frac"] for p in per_shape])
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / peaks["tflops"], "traffic": traffic,
+                    "kernel": "umma_gemm_kernel<f16> at M=4096", "peak_source": peaks["source"] + " burst",
+                    "sweep_geomean_frac": round(sweep_frac, 4),
+                    "sweep_geomean_frac_nominal": round(geomean([p["frac_nominal"] for p in per_shape]), 4),
+                    "per_shape_frac": {str(p["M"]): p["frac"] for p in per_shape},
+                    "per_shape_us": {str(p["M"]): p["us"] for p in per_shape}}
+        for key in ("int8_scaled_mm", "fp16_splitk_decode", "fp32_m37", "selector_host_us", "cuda_graph_replay"):
+            if key in extras:
+                roofline[key] = extras.pop(key)
+        if stack_line is not None:
+            roofline["stack"] = {k: stack_line[k] for k in ("value", "unit", "n_gpus", "steps", "ms_per_step", "scaling",
+                                                            "roofline_frac", "decode", "prefill")}
+            roofline["stack"]["config"] = {k: stack_line["config"][k] for k in ("layers", "resident_layers", "gather", "parallelism")}
+        if stack_nccl is not None:
+            roofline["stack_nccl_allgather"] = {k: stack_nccl[k] for k in ("value", "ms_per_step", "roofline_frac", "decode", "prefill")}
+        cfg = sweep_config(world)
         line = {
             "metric": METRIC, "value": geomean([tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sweep_m": SWEEP_M, "n": N_DIM, "k": K_DIM,
-                       "reps_per_shape": {str(m): reps_for(m) for m in SWEEP_M},
-                       "l2": f"inputs larger than L2: {WEIGHT_COPIES} rotating copies of the 32 MiB weight (256 MiB)",
-                       "entry": "mp_gemm (online selector)", "parallelism": f"column-parallel x{world}, no collective",
-                       "peaks": peaks},
-            "roofline_geomean_frac": geomean([p["frac"] for p in per_shape]),
-            "roofline_geomean_frac_nominal": geomean([p["frac_nominal"] for p in per_shape]),
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["tflops"], "traffic": traffic,
-                         "kernel": "umma_gemm_kernel<f16> at M=4096", "peak_source": peaks["source"] + " burst"},
+            "config": cfg,
+            "roofline": roofline,
             "per_shape": per_shape,
+            "peaks": peaks,
             "cpu_baseline": {"value": cpu_val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                             "sample": "sweep shapes M in {%s}, N=K=4096, one run each" %
-                                       ",".join(str(m) for m, _ in cpu_res)},
+                             "sample": (f"sweep shapes M in {{{','.join(str(m) for m, _ in cpu_res)}}}, N=K=4096, one run each; "
+                                        f"M <= {CPU_FULL_ROWS} in full, larger M on {CPU_SAMPLE_ROWS} rows scaled by M/{CPU_SAMPLE_ROWS}")},
             "e2e": {"value": geomean([e2e_tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "A copied from pinned host and C copied back to pinned host per GEMM, weight resident; M >= 256: two staging slots, uploads and downloads on their own streams overlap the GEMMs"},
@@ -542,6 +608,46 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """One GEMM shape, a few launches through the library, nothing else: the small case that profiler captures use.
+    dtype:MxNxK in RCC terms (A [M,K], B stored [N,K]); with --case-scaled the INT8 scaled matmul (M tokens, N channels)."""
+    import torch
+    from moonpoly_b200 import api
+
+    dtype, dims = args.case.split(":")
+    m, n, k = (int(v) for v in dims.lower().split("x"))
+    tdt = {"fp16": torch.float16, "int8": torch.int8, "fp32": torch.float32}[dtype]
+    dev = "cuda"
+
+    def operand(rows):
+        if tdt == torch.int8:
+            return torch.randint(-127, 128, (rows, k), dtype=torch.int8, device=dev)
+        return (torch.randn((rows, k), device=dev) * 0.05).to(tdt)
+
+    As = [operand(m) for _ in range(args.case_copies)]
+    Bs = [operand(n) for _ in range(args.case_copies)]
+    if args.case_scaled:
+        sa = torch.rand((m,), device=dev) * 0.019 + 0.001
+        sb = torch.rand((n,), device=dev) * 0.019 + 0.001
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.case_launches):
+        a, b = As[i % args.case_copies], Bs[i % args.case_copies]
+        if args.case_scaled:
+            api.scaled_int8_mm(a, b.t(), sa, sb)
+        elif args.case_pid is None:
+            api.gemm_rcc(a, b)
+        else:
+            api.gemm_rcc_pid(a, b, args.case_pid, args.case_split)
+    e1.record()
+    torch.cuda.synchronize()
+    assert api.device_status() == 0
+    plan = "" if args.case_pid is not None or args.case_scaled else " " + repr(api.select_plan(api._dtype_code(As[0]), m, n, k))
+    print(f"{dtype} m={m} n={n} k={k} pid={args.case_pid} split_k={args.case_split}{plan}: "
+          f"{e0.elapsed_time(e1) / args.case_launches * 1e3:.2f} us per launch over {args.case_launches} launches")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -551,10 +657,21 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0, dest="cpu_budget")
     ap.add_argument("--no-extras", action="store_true", dest="no_extras",
                     help="skip the INT8 scaled_mm and FP16 split-K side tables")
+    ap.add_argument("--no-stack", action="store_true", dest="no_stack", help="skip the Llama-3-70B-shaped linear stack")
+    ap.add_argument("--stack-steps", type=int, default=12, dest="stack_steps")
+    ap.add_argument("--case", default=None, help="run one small case and exit, e.g. fp16:4096x4096x4096 (dtype:MxNxK, RCC)")
+    ap.add_argument("--case-pid", type=int, default=None, dest="case_pid")
+    ap.add_argument("--case-split", type=int, default=1, dest="case_split")
+    ap.add_argument("--case-scaled", action="store_true", dest="case_scaled")
+    ap.add_argument("--case-launches", type=int, default=3, dest="case_launches")
+    ap.add_argument("--case-copies", type=int, default=2, dest="case_copies")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.case is not None:
+        run_case(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return

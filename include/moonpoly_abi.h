@@ -34,8 +34,9 @@ typedef enum mp_status {
   MP_ERR_UNSUPPORTED = 8    /* device is not sm_100 / dtype not served                            */
 } mp_status;
 
-/* Values of moonpoly::MoonpolyDataType (moonpoly/include/moonpoly.cuh:20-24). */
-enum { MP_FP16 = 0, MP_INT8 = 1, MP_FP32 = 2 };
+/* Values of moonpoly::MoonpolyDataType (moonpoly/include/moonpoly.cuh:20-24).  MP_BF16 has no counterpart there
+ * (the reference removed its BF16 core GEMM, moonpoly/core/moonpoly_gemm.cu:74-77); mp_linear_bias accepts it. */
+enum { MP_FP16 = 0, MP_INT8 = 1, MP_FP32 = 2, MP_BF16 = 3 };
 
 /* Values of moonpoly::Fp16PolyPattern (moonpoly/include/moonpoly.cuh:33-37). */
 enum { MP_PATTERN_SINGLE = 1, MP_PATTERN_COMBINE = 2, MP_PATTERN_SPLITK = 3 };
@@ -58,6 +59,13 @@ int mp_gemm(int dtype, int m, int n, int k, const void* A, int a_col_major, cons
 /* moonpoly::moonpolyLinear (moonpoly/core/moonpoly_gemm.cu:41-44): Y[M,N] = X[M,K] * W[N,K]^T,
  * all row-major; remapped to RCC (m = N, n = M, A = W, B = X), alpha = 1, beta = 0. */
 int mp_linear(int dtype, int M, int N, int K, const void* X, const void* W, void* Y, void* stream);
+
+/* Linear with the bias add fused into the GEMM's epilogue, FP16 or BF16 (no counterpart in the reference, whose
+ * callers add the bias with a second kernel: integrations/vllm/v0.10.0/moonpoly_linear.patch:700-712, and whose
+ * core GEMM refuses BF16).  Y[M,N] = X[M,K] * W[N,K]^T (+ bias[N]), all row-major, operands and output of `dtype`
+ * (MP_FP16 or MP_BF16), fp32 accumulation.  The result is rounded to the output type first and the bias is then
+ * added in the output type -- bit-identical to the two-step `linear` followed by `+ bias`.  bias may be NULL. */
+int mp_linear_bias(int dtype, int M, int N, int K, const void* X, const void* W, const void* bias, void* Y, void* stream);
 
 /* run_moonpoly_gemm_{fp16,fp32,int8}_row_col_col (core/fp16/fp16_rcc.cu:3263-3269,
  * core/fp32/fp32_rcc.cu:2272-2282, core/int8/i8_rcc.cu:3143-3157): online selector, then the
@@ -159,6 +167,32 @@ int mp_cost_predict_pid(int dtype, int m, int n, int k, int* pid, float* ms);
  * k % 8 == 0, else MP_ERR_INVALID_ARG (the reference throws std::invalid_argument). */
 int mp_twin_gemm_fp16(int m, int n, int k, int split_n, const void* A, const void* B, void* C,
                       float alpha, float beta, void* stream);
+
+/* Column-parallel Linear fused with the all-gather of its output (no counterpart in the reference, which runs on
+ * one GPU; the vLLM integration it patches gathers with a separate NCCL call).  Rank r of g owns W_shard
+ * [N_local, K], the rows [col_offset, col_offset + N_local) of the full weight, and computes its slab
+ * Y[:, col_offset : col_offset + N_local] of the full row-major output Y[M, ld_dst].  The epilogue stores every
+ * finished tile into ALL n_dst copies of Y: dst[0..n_dst) are the bases of the full output buffer on this GPU and,
+ * peer-mapped, on the other GPUs of the box (plain stores over NVLink; no TMA, no multicast, no library call).
+ * FP16 only, alpha = 1, beta = 0, K % 8 == 0.  A consumer must not read a peer's slab before mp_peer_barrier. */
+int mp_linear_gather(int dtype, int M, int N_local, int K, const void* X, const void* W_shard, void* const* dst,
+                     int n_dst, long long ld_dst, long long col_offset, void* stream);
+
+/* Cross-GPU flag barrier for mp_linear_gather, one tiny kernel on `stream`.  flags_dev is a DEVICE array of
+ * `world` pointers, [r] = rank r's flag array of `world` unsigned words (peer-mapped for r != rank, zero at start).
+ * Publishes `value` into slot `rank` of every rank's array (after a system-scope fence, so the slab stores of the
+ * kernels before it in the stream are visible first) and waits until every rank's `value` has arrived here.
+ * Values must grow from call to call.  The wait is bounded by timeout_us (0 = one second); when it runs out the
+ * kernel records a code in the device status word (mp_device_status returns MP_ERR_DEVICE) and returns. */
+int mp_peer_barrier(unsigned* const* flags_dev, int world, int rank, unsigned value, unsigned timeout_us,
+                    void* stream);
+
+/* Helpers for the two calls above (plain CUDA IPC): a zero-filled device buffer plus the 64-byte handle another
+ * process of the same box opens to get a peer-mapped pointer (peer access is enabled on first use). */
+int mp_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+int mp_peer_open(const unsigned char handle[64], void** ptr);
+int mp_peer_close(void* ptr);
+int mp_peer_free(void* ptr);
 
 /* scaled_mm_mikpoly -> cutlass_scaled_mm_mikpoly_unified
  * (core/int8/scaled_mm/scaled_mm_bindings.cpp:20-92, scaled_mm_mikpoly_unified.cu:362-403):

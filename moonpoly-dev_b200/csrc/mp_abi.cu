@@ -36,6 +36,15 @@ bool streamk_from_env() {
   return !(v && v[0] && v[0] != '0');
 }
 std::atomic<bool> g_use_streamk{streamk_from_env()};
+// Split-K inside a thread-block cluster (partials exchanged through distributed shared memory instead of
+// the global scratch; see run_umma).  Bit-identical to the scratch path, but measured slower on B200
+// (M = 128, N = K = 4096: 15.3 us against 14.1 us; the cluster launch costs more than the exchange saves), so
+// it is off unless MOONPOLY_ENABLE_CLUSTER_SPLITK=1 (read at load and again by mp_reload_env).
+bool cluster_splitk_from_env() {
+  const char* v = std::getenv("MOONPOLY_ENABLE_CLUSTER_SPLITK");
+  return v && v[0] && v[0] != '0';
+}
+std::atomic<bool> g_use_cluster_splitk{cluster_splitk_from_env()};
 std::atomic<unsigned long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -66,7 +75,9 @@ struct DeviceState {
   bool ready = false;
   int sms = 0;
   int cc = 0;
-  bool attrs[6] = {false, false, false, false, false, false};
+  bool attrs[9] = {false, false, false, false, false, false, false, false, false};
+  bool stream_attrs[16] = {false, false, false, false, false, false, false, false, false, false, false, false,
+                           false, false, false, false};
 };
 constexpr int kMaxDevices = 32;
 DeviceState g_dev[kMaxDevices];
@@ -175,11 +186,16 @@ struct Problem {
   int a_scalar = 0, b_scalar = 0;
   const void* bias = nullptr;
   int out_bf16 = 0;
+  int bf16 = 0;              // dtype MP_FP16 with bf16 operands and output (mp_linear_bias with MP_BF16)
+  int bias_on_m = 0;         // 16-bit float GEMM with `bias`: 1 = indexed by the rows of A (the Linear mapping's channels)
+  // fused all-gather: further bases that receive the same output (the other GPUs' copies of the buffer)
+  void* peers[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int num_peers = 0;
 };
 
 struct Launch {
   int orient = 0, bn = 128, split_k = 1;
-  int xm = 1;            // 2: 256 x bn tiles (two 128-row halves of X share every Y tile); single slice, one region only
+  int xm = 1;            // 2: 256 x bn tiles (two 128-row halves of X share every Y tile); one region only
   int kc = 0;                 // K blocks per stage; 0 = choose
   int split_n = 0, bn1 = 0;   // twin: second region [split_n, n) with its own UMMA-N
   void* workspace = nullptr; size_t workspace_bytes = 0;
@@ -243,7 +259,8 @@ bool tma_compatible(const Problem& p) {
 size_t umma_workspace_bytes(const Problem& p, const Launch& l, size_t* counter_bytes) {
   const int P = l.orient == 0 ? p.m : p.n;
   const int Q = l.orient == 0 ? p.n : p.m;
-  const int tiles_p = (P + kUmmaM - 1) / kUmmaM;
+  const int xm = (l.xm == 2 && l.split_n <= 0) ? 2 : 1;
+  const int tiles_p = (P + kUmmaM * xm - 1) / (kUmmaM * xm);
   long long tiles;
   int bn_max = l.bn;
   if (l.split_n > 0) {
@@ -255,13 +272,13 @@ size_t umma_workspace_bytes(const Problem& p, const Launch& l, size_t* counter_b
   const size_t cb = round_up((size_t)tiles * 16 * sizeof(unsigned), 256);   // [tile][quadrant][arrived, claimed, left, -]
   if (counter_bytes) *counter_bytes = cb;
   if (l.split_k <= 1) return 0;
-  return cb + (size_t)tiles * l.split_k * bn_max * kUmmaM * 4;
+  return cb + (size_t)tiles * l.split_k * xm * bn_max * kUmmaM * 4;
 }
 
-template <int KIND, int EPI, bool SPLIT>
+template <int KIND, int EPI, bool SPLIT, bool CLUSTER = false>
 int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CUtensorMap& ty0,
                   const CUtensorMap& ty1, const UmmaParams& up, int grid, size_t smem, cudaStream_t stream) {
-  auto kern = umma_gemm_kernel<KIND, EPI, SPLIT>;
+  auto kern = umma_gemm_kernel<KIND, EPI, SPLIT, CLUSTER>;
   if (!d.attrs[attr_slot]) {
     MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     d.attrs[attr_slot] = true;
@@ -271,11 +288,22 @@ int launch_umma_t(DeviceState& d, int attr_slot, const CUtensorMap& tx, const CU
   cfg.blockDim = dim3(SPLIT ? kUmmaThreads : kUmmaThreadsWide);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (CLUSTER) {       // the K slices of a tile form one cluster: consecutive CTAs, grid is a multiple of it
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)up.cluster_k;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  cfg.numAttrs = na;
   MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tx, ty0, ty1, up));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
@@ -324,12 +352,12 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   const int kb_bytes = xm * kXTileBytes + bn_max * kRowBytes;
   // the scaled epilogue stages the tile's scales and bias in shared memory (up to 8 warps x 1.5 KB)
   const int epi_reserve = p.epi == EPI_SCALED ? 12288 : 0;
-  const int smem_for_stages = kSmemBudget - 1024 - 256 - epi_reserve;
+  const int smem_for_stages = kSmemBudget - 1024 - 256 - kClusterBarBytes - epi_reserve;
   int kc = l.kc;
   if (kc <= 0) kc = (smem_for_stages / (4 * kb_bytes) >= 3) ? 4 : (smem_for_stages / (2 * kb_bytes) >= 3) ? 2 : 1;
   while (kc > 1 && smem_for_stages / (kc * kb_bytes) < 2) kc >>= 1;
   // at most 31 slices: the reduction tracks claimed shares in one 32-bit mask (one bit seals it)
-  int S = std::max(1, std::min(std::min(xm == 2 ? 1 : l.split_k, 31), up.kb_total));
+  int S = std::max(1, std::min(std::min(l.split_k, 31), up.kb_total));
   up.kb_per_slice = ((up.kb_total + S - 1) / S + kc - 1) / kc * kc;     // slices start on a stage boundary
   S = (up.kb_total + up.kb_per_slice - 1) / up.kb_per_slice;              // every slice non-empty
   up.split_k = S;
@@ -342,7 +370,8 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.stage_bytes = kc * kb_bytes;
   up.stages = std::min(kMaxStages, smem_for_stages / up.stage_bytes);
   up.alpha = p.alpha; up.beta = p.beta; up.ialpha = p.ialpha; up.ibeta = p.ibeta;
-  up.ws_tile_words = bn_max * kUmmaM;
+  up.ws_tile_words = xm * bn_max * kUmmaM;
+  up.ws_half_words = bn_max * kUmmaM;
   up.scale_p = swap ? p.b_scales : p.a_scales;
   up.scale_q = swap ? p.a_scales : p.b_scales;
   up.scale_p_scalar = swap ? p.b_scalar : p.a_scalar;
@@ -350,6 +379,10 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   up.n_on_p = swap ? 1 : 0;
   up.bias = p.bias;
   up.out_bf16 = p.out_bf16;
+  up.ab_bf16 = p.bf16;
+  up.bias_on_p = p.epi == EPI_F16 ? (swap ? !p.bias_on_m : p.bias_on_m) : 0;
+  up.num_peers = p.num_peers;
+  for (int i = 0; i < p.num_peers; ++i) up.peer_out[i] = p.peers[i];
 
   up.ws_slices = S;
   const long long units = (long long)up.total_tiles * up.split_k;
@@ -362,7 +395,7 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
   // completed through the split-K scratch, and the other T - r tiles follow as whole waves.  Runs
   // are never shorter than a quarter of K, so a tile has at most ~5 contributors.
   size_t sk_cb = 0, sk_pb = 0;
-  if (g_use_streamk.load(std::memory_order_relaxed) && xm == 1 && S == 1 && up.num_regions == 1 && up.total_tiles > grid && grid == d->sms) {
+  if (g_use_streamk.load(std::memory_order_relaxed) && S == 1 && up.num_regions == 1 && up.total_tiles > grid && grid == d->sms) {
     const int r = up.total_tiles % grid;
     // measured on B200: pays while the remainder is at most half a wave (r/G = 0.30: -17 %, 0.46: -5 %,
     // 0.59 and above: the completion traffic costs more than the idle SMs did)
@@ -372,7 +405,7 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
       ipc = (ipc + kc - 1) / kc * kc;
       const int max_slices = (int)((up.kb_total + ipc - 2) / ipc + 1);
       sk_cb = round_up((size_t)r * 16 * sizeof(unsigned), 256);
-      sk_pb = (size_t)r * max_slices * bn_max * kUmmaM * 4;
+      sk_pb = (size_t)r * max_slices * xm * bn_max * kUmmaM * 4;
       if (l.workspace == nullptr || l.workspace_bytes >= sk_cb + sk_pb) {
         up.sk_tiles = r;
         up.sk_ipc = (int)ipc;
@@ -401,7 +434,15 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
     return MP_OK;
   }
 
-  if (S > 1 || up.sk_tiles > 0) {
+  // Split-K inside a cluster: when every work unit has a CTA of its own and there are 2, 4 or 8 slices, the
+  // slices of a tile are launched as one cluster and exchange partials through distributed shared memory;
+  // no scratch, no counters.  The parked tile (bn x 128 words) reuses the pipeline stages.
+  const bool cluster = g_use_cluster_splitk.load(std::memory_order_relaxed) && (S == 2 || S == 4 || S == 8) &&
+                       up.sk_tiles == 0 && units == grid && xm == 1 &&
+                       (size_t)bn_max * kUmmaM * 4 <= (size_t)up.stages * up.stage_bytes;
+  up.cluster_k = cluster ? S : 0;
+
+  if (!cluster && (S > 1 || up.sk_tiles > 0)) {
     size_t cb = sk_cb;
     const size_t need = up.sk_tiles > 0 ? sk_cb + sk_pb : umma_workspace_bytes(p, l, &cb);
     uint8_t *counters = nullptr, *partials = nullptr;
@@ -430,7 +471,12 @@ int run_umma(const Problem& p, Launch l, cudaStream_t stream) {
     ty1 = ty0;
   }
 
-  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + 1024 + epi_reserve;
+  const size_t smem = (size_t)up.stages * up.stage_bytes + 8 * (2 * up.stages + 4) + 16 + kClusterBarBytes + 1024 + epi_reserve;
+  if (cluster) {
+    if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16, true, true>(*d, 6, tx, ty0, ty1, up, grid, smem, stream);
+    if (p.epi == EPI_I32) return launch_umma_t<KIND_I8, EPI_I32, true, true>(*d, 7, tx, ty0, ty1, up, grid, smem, stream);
+    return launch_umma_t<KIND_I8, EPI_SCALED, true, true>(*d, 8, tx, ty0, ty1, up, grid, smem, stream);
+  }
   // kernels whose every unit is a whole tile run the variant without the reduction (8 epilogue warps)
   if (up.split_k > 1 || up.sk_tiles > 0) {
     if (p.dtype == MP_FP16) return launch_umma_t<KIND_F16, EPI_F16, true>(*d, 0, tx, ty0, ty1, up, grid, smem, stream);
@@ -474,7 +520,7 @@ int run_simt(const Problem& p, int ti, int tj, int split_k, void* workspace, siz
   sp.c_stride_i = p.c_stride_m; sp.c_stride_j = p.c_stride_n;
   sp.alpha = p.alpha; sp.beta = p.beta; sp.ialpha = p.ialpha; sp.ibeta = p.ibeta;
   sp.a_scales = p.a_scales; sp.b_scales = p.b_scales; sp.a_scalar = p.a_scalar; sp.b_scalar = p.b_scalar;
-  sp.bias = p.bias; sp.out_bf16 = p.out_bf16;
+  sp.bias = p.bias; sp.out_bf16 = p.out_bf16; sp.bias_on_i = p.bias_on_m;
   int S = std::max(1, split_k);
   if (p.k > 0) S = std::min(S, (p.k + 15) / 16); else S = 1;
   sp.k_per_slice = p.k > 0 ? ((p.k + S - 1) / S + 15) / 16 * 16 : 0;
@@ -503,6 +549,7 @@ int run_simt(const Problem& p, int ti, int tj, int split_k, void* workspace, siz
     if (ti == 128 && tj == 128) return launch_simt_f32<128, 128>(sp, stream);
     return launch_simt_f32<64, 64>(sp, stream);
   }
+  if (p.dtype == MP_FP16 && p.bf16) return launch_simt_t<__nv_bfloat16, SEPI_F16, 64, 64>(sp, stream);
   if (p.dtype == MP_FP16) return launch_simt_t<__half, SEPI_F16, 64, 64>(sp, stream);
   if (p.epi == EPI_I32) return launch_simt_t<int8_t, SEPI_I32, 64, 64>(sp, stream);
   return launch_simt_t<int8_t, SEPI_SCALED, 64, 64>(sp, stream);
@@ -588,6 +635,85 @@ int launch_stream_nt(const StreamParams& sp, int sms, cudaStream_t stream) {
   return launch_stream_t<KIND, EPI, 8, 4, 2>(sp, sms, stream);
 }
 
+// Cluster-K variant of the streaming kernel: a cluster of `ck` CTAs shares a block of W rows and cuts K.
+// Measured on B200 it loses to the one-CTA-per-row-block kernel on every benchmark shape but one (its tiles run
+// one after the other, so every tile pays a full memory latency: M = 32, N = K = 4096: 24.6 us against 11.2 us;
+// only (1, 1024, 28672) gains, 17.3 us against 24.1 us), so the library never picks it by itself unless
+// MOONPOLY_ENABLE_STREAM_CLUSTER=1; the tuning entry reaches it with an explicit number of K ranges.
+bool stream_cluster_from_env() {
+  const char* v = std::getenv("MOONPOLY_ENABLE_STREAM_CLUSTER");
+  return v && v[0] && v[0] != '0';
+}
+std::atomic<bool> g_use_stream_cluster{stream_cluster_from_env()};
+
+struct StreamCkChoice { int ck, row_blocks; };
+
+// ck: every warp should own at least one full batch of loads (8 K blocks of 64 bytes) of its CTA's K range, and
+// a CTA should hold about 4 T rows so that its share of X is small against its share of W; row blocks: one CTA
+// per SM where the rows allow it, never more than kCkMaxTiles tiles per CTA.
+StreamCkChoice choose_stream_ck(int R, int T, int K, int elt, int sms, int forced_ck) {
+  const int max_ck_by_k = std::max(1, (int)(((long long)K * elt) / 4096));
+  int ck = 1;
+  if (forced_ck > 0) {
+    ck = forced_ck;
+  } else {
+    const int want_rows = std::min(kCkMaxTiles * kStreamRows, std::max(kStreamRows, 4 * T));
+    while (ck < 8 && ck * 2 <= max_ck_by_k && (long long)R * ck / sms < want_rows) ck *= 2;
+  }
+  int row_blocks = std::max(1, sms / ck);
+  row_blocks = std::max(row_blocks, (R + kCkMaxTiles * kStreamRows - 1) / (kCkMaxTiles * kStreamRows));
+  row_blocks = std::min(row_blocks, std::max(1, R));
+  return {ck, row_blocks};
+}
+
+template <int KIND, int EPI, int NT, int UNROLL>
+int launch_stream_ck_t(DeviceState& d, int attr_slot, StreamCkParams cp, cudaStream_t stream) {
+  auto kern = stream_mma_ck_kernel<KIND, EPI, NT, UNROLL>;
+  constexpr int TP = NT * 8 + 1;
+  const size_t fixed = (size_t)(kCkMaxTiles + kStreamWarps) * kStreamRows * TP * 4 + 16;
+  const int elt = KIND == STREAM_I8 ? 1 : 2;
+  const long long chunks = (long long)cp.s.K * elt / 16, blocks = (chunks + 3) / 4;
+  const long long max_cta_chunks = 4 * ((blocks + cp.ck - 1) / cp.ck);
+  cp.x_row_bytes = (int)((max_cta_chunks + 1) * 16);
+  const size_t x_bytes = (size_t)cp.s.T * cp.x_row_bytes;
+  cp.stage_x = fixed + x_bytes <= (size_t)kSmemBudget ? 1 : 0;
+  const size_t smem = fixed + (cp.stage_x ? x_bytes : 0);
+  if (!d.stream_attrs[attr_slot]) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    d.stream_attrs[attr_slot] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(cp.row_blocks * cp.ck));
+  cfg.blockDim = dim3(kStreamWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = (unsigned)cp.ck;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  ++na;
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, cp));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
+template <int KIND, int EPI>
+int launch_stream_ck_nt(DeviceState& d, int base_slot, const StreamCkParams& cp, cudaStream_t stream) {
+  if (cp.s.T <= 8) return launch_stream_ck_t<KIND, EPI, 1, 8>(d, base_slot + 0, cp, stream);
+  if (cp.s.T <= 16) return launch_stream_ck_t<KIND, EPI, 2, 8>(d, base_slot + 1, cp, stream);
+  if (cp.s.T <= 32) return launch_stream_ck_t<KIND, EPI, 4, 8>(d, base_slot + 2, cp, stream);
+  return launch_stream_ck_t<KIND, EPI, 8, 4>(d, base_slot + 3, cp, stream);
+}
+
 bool stream_compatible(const Problem& p) {
   if (!(p.dtype == MP_FP16 && p.epi == EPI_F16) && p.dtype != MP_INT8) return false;
   return std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 16 &&
@@ -595,7 +721,9 @@ bool stream_compatible(const Problem& p) {
          tma_compatible(p);      // same rule: 16-byte aligned rows
 }
 
-int run_stream(const Problem& p, cudaStream_t stream) {
+// forced_ck: 0 = the library decides between the two streaming kernels; > 0 = the cluster-K kernel with that
+// many K ranges (1, 2, 4 or 8); < 0 = the one-CTA-per-row-block kernel.
+int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0) {
   DeviceState* d = nullptr;
   if (int rc = device_state(&d)) return rc;
   StreamParams sp{};
@@ -614,8 +742,28 @@ int run_stream(const Problem& p, cudaStream_t stream) {
   // scaled epilogue: tokens are the rows of A, channels the rows of B
   sp.chan_scale = p.b_scales; sp.chan_scalar = p.b_scalar;
   sp.tok_scale = p.a_scales; sp.tok_scalar = p.a_scalar;
-  sp.chan_on_r = narrow_is_a ? 1 : 0;
+  sp.chan_on_r = (p.epi == EPI_F16 && p.bias_on_m) ? (narrow_is_a ? 0 : 1) : (narrow_is_a ? 1 : 0);
   sp.bias = p.bias; sp.out_bf16 = p.out_bf16;
+  sp.num_peers = p.num_peers;
+  for (int i = 0; i < p.num_peers; ++i) sp.peer_out[i] = p.peers[i];
+  // The cluster-K kernel pays when the narrow side is wide enough for X to weigh against W (T > 8), or when the
+  // rows are too few to give every SM two CTAs of the plain kernel; it needs a K range per warp worth streaming.
+  if (forced_ck >= 0 && (forced_ck > 0 || g_use_stream_cluster.load(std::memory_order_relaxed))) {
+    const int elt = elem_bytes(p.dtype);
+    const StreamCkChoice ch = choose_stream_ck(sp.R, sp.T, sp.K, elt, d->sms, forced_ck);
+    const bool few_rows = sp.R < 8 * 2 * d->sms;
+    const bool enough_k = (long long)sp.K * elt >= 4096ll * ch.ck;
+    const bool rows_fit = (sp.R + ch.row_blocks - 1) / ch.row_blocks <= kCkMaxTiles * kStreamRows;
+    if (rows_fit && (forced_ck > 0 || (enough_k && (sp.T > 8 || (few_rows && ch.ck > 1))))) {
+      StreamCkParams cp{};
+      cp.s = sp; cp.ck = ch.ck; cp.row_blocks = ch.row_blocks;
+      if (p.dtype == MP_FP16 && p.bf16) return launch_stream_ck_nt<STREAM_BF16, STREAM_EPI_F16>(*d, 12, cp, stream);
+      if (p.dtype == MP_FP16) return launch_stream_ck_nt<STREAM_F16, STREAM_EPI_F16>(*d, 0, cp, stream);
+      if (p.epi == EPI_I32) return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_I32>(*d, 4, cp, stream);
+      return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_SCALED>(*d, 8, cp, stream);
+    }
+  }
+  if (p.dtype == MP_FP16 && p.bf16) return launch_stream_nt<STREAM_BF16, STREAM_EPI_F16>(sp, d->sms, stream);
   if (p.dtype == MP_FP16) return launch_stream_nt<STREAM_F16, STREAM_EPI_F16>(sp, d->sms, stream);
   if (p.epi == EPI_I32) return launch_stream_nt<STREAM_I8, STREAM_EPI_I32>(sp, d->sms, stream);
   return launch_stream_nt<STREAM_I8, STREAM_EPI_SCALED>(sp, d->sms, stream);
@@ -714,8 +862,11 @@ int run_pid(const Problem& p, int pid, int split_k, void* ws, size_t ws_bytes, c
     return run_simt(p, c.ti, c.tj, split_k, ws, ws_bytes, stream);
   }
   if (!tma_compatible(p)) return run_simt(p, 64, 64, split_k, ws, ws_bytes, stream);
-  if (c.orient == 2 && gemv_compatible(p)) return run_gemv(p, stream);        // the skinny streaming kernel
-  if (c.orient == 3 && stream_compatible(p)) return run_stream(p, stream);    // the streaming warp-MMA kernel
+  // the skinny CUDA-core kernel serves plain FP16 only: bf16 operands, a fused bias or extra destinations take the
+  // warp-MMA streaming kernel instead
+  const bool plain = !p.bf16 && p.bias == nullptr && p.num_peers == 0;
+  if (c.orient == 2 && plain && gemv_compatible(p)) return run_gemv(p, stream);        // the skinny streaming kernel
+  if ((c.orient == 3 || (c.orient == 2 && !plain)) && stream_compatible(p)) return run_stream(p, stream);    // the streaming warp-MMA kernel
   Launch l = umma_launch_for(p, c, split_k);
   l.workspace = ws; l.workspace_bytes = ws_bytes;
   return run_umma(p, l, stream);
@@ -762,6 +913,8 @@ int mp_num_sms(void) {
 int mp_reload_env(void) {
   mp::reload_env();
   g_use_streamk.store(streamk_from_env(), std::memory_order_relaxed);
+  g_use_cluster_splitk.store(cluster_splitk_from_env(), std::memory_order_relaxed);
+  g_use_stream_cluster.store(stream_cluster_from_env(), std::memory_order_relaxed);
   return MP_OK;
 }
 
@@ -867,10 +1020,12 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
     if (!gemv_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the skinny kernel needs FP16, min(m,n) <= 8 and 16-byte aligned rows");
     return run_gemv(pg, reinterpret_cast<cudaStream_t>(stream));
   }
-  if (orient == 3) {            // the streaming warp-MMA kernel (bn, kc, split_k unused)
+  if (orient == 3) {            // the streaming warp-MMA kernels (bn unused; split_k = K ranges of the cluster-K variant)
     const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
     if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16 or INT8, min(m,n) <= 64 and 16-byte aligned rows");
-    return run_stream(pg, reinterpret_cast<cudaStream_t>(stream));
+    if (kc != 0 && kc != 1 && kc != 2 && kc != 4 && kc != 8 && kc != -1)
+      return fail(MP_ERR_INVALID_ARG, "streaming kernel: kc selects the K ranges of the cluster variant (1, 2, 4, 8), -1 the plain kernel, 0 lets the library choose");
+    return run_stream(pg, reinterpret_cast<cudaStream_t>(stream), kc);
   }
   const int xm = (orient == 4 || orient == 5) ? 2 : 1;       // orient 4 / 5: orient 0 / 1 with 256-row tiles
   if (xm == 2) orient -= 4;
@@ -919,6 +1074,128 @@ int mp_gemm(int dtype, int m, int n, int k, const void* A, int a_col_major, cons
 
 int mp_linear(int dtype, int M, int N, int K, const void* X, const void* W, void* Y, void* stream) {
   return mp_gemm(dtype, N, M, K, W, 0, X, 1, Y, 1, 1.0f, 0.0f, stream);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Column-parallel Linear fused with the all-gather of its output, and the cross-GPU flag barrier that follows
+// ------------------------------------------------------------------------------------------------
+int mp_linear_gather(int dtype, int M, int N_local, int K, const void* X, const void* W_shard, void* const* dst,
+                     int n_dst, long long ld_dst, long long col_offset, void* stream) {
+  if (dtype != MP_FP16) return fail(MP_ERR_UNSUPPORTED, "the fused all-gather Linear is served for FP16");
+  if (dst == nullptr || n_dst < 1 || n_dst > 8) return fail(MP_ERR_INVALID_ARG, "1 to 8 destination buffers are supported, got %d", n_dst);
+  if (M < 0 || N_local < 0 || K < 0 || col_offset < 0 || ld_dst < col_offset + N_local)
+    return fail(MP_ERR_INVALID_ARG, "bad sizes: M=%d N_local=%d K=%d ld=%lld offset=%lld", M, N_local, K, ld_dst, col_offset);
+  for (int i = 0; i < n_dst; ++i)
+    if (dst[i] == nullptr) return fail(MP_ERR_INVALID_ARG, "destination %d is null", i);
+  if (M == 0 || N_local == 0) return MP_OK;
+  if (K == 0 || X == nullptr || W_shard == nullptr) return fail(MP_ERR_INVALID_ARG, "null operand pointer or K == 0");
+  // Linear -> RCC: m = N_local (A = W), n = M (B = X); C element (channel j, token t) lives at base + t * ld + offset + j
+  Problem p = rcc_problem(dtype, N_local, M, K, W_shard, X, reinterpret_cast<__half*>(dst[0]) + col_offset, 1.0f, 0.0f);
+  p.c_stride_m = 1;
+  p.c_stride_n = ld_dst;
+  p.num_peers = n_dst - 1;
+  for (int i = 1; i < n_dst; ++i) p.peers[i - 1] = reinterpret_cast<__half*>(dst[i]) + col_offset;
+  if (!tma_compatible(p))
+    return fail(MP_ERR_UNALIGNED_K, "the fused all-gather Linear needs 16-byte aligned operand rows (K %% 8 == 0)");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  mp_plan plan = mp::select_plan(dtype, N_local, M, K);
+  if (plan.pattern == MP_PATTERN_COMBINE) {       // the twin launch writes through the same epilogue
+    return run_twin(p, plan.split_n, s);
+  }
+  return run_pid(p, plan.pid, plan.split_k, nullptr, 0, s);
+}
+
+int mp_linear_bias(int dtype, int M, int N, int K, const void* X, const void* W, const void* bias, void* Y, void* stream) {
+  if (dtype != MP_FP16 && dtype != MP_BF16)
+    return fail(MP_ERR_INVALID_ARG, "mp_linear_bias serves MP_FP16 and MP_BF16, got dtype %d", dtype);
+  if (int rc = check_rcc_args(MP_FP16, N, M, K, W, X, Y)) return rc;
+  if (M == 0 || N == 0) return MP_OK;
+  // Linear -> RCC: m = N (A = W), n = M (B = X); the bias runs along m
+  Problem p = rcc_problem(MP_FP16, N, M, K, W, X, Y, 1.0f, 0.0f);
+  p.bias = bias;
+  p.bias_on_m = 1;
+  if (dtype == MP_BF16) { p.bf16 = 1; p.out_bf16 = 1; }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (K == 0) return run_simt(p, 64, 64, 1, nullptr, 0, s);
+  const mp_plan plan = mp::select_plan(MP_FP16, N, M, K);
+  if (plan.pattern == MP_PATTERN_COMBINE) return run_twin(p, plan.split_n, s);
+  return run_pid(p, plan.pid, plan.split_k, nullptr, 0, s);
+}
+
+namespace {
+// One warp: lane r < world first publishes `value` in rank r's flag array at this rank's slot (release at system
+// scope, after a system fence: the slab stores of the kernels before it in the stream are visible first), then
+// waits until rank r's value has arrived here.  The wait is bounded; on expiry the status word gets a code.
+__global__ void peer_barrier_kernel(unsigned* const* flags, int world, int rank, unsigned value,
+                                    unsigned long long timeout_ns, int* status) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  unsigned* theirs = flags[r] + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(value) : "memory");
+  const unsigned* mine = flags[rank] + r;
+  const unsigned long long t0 = mp::globaltimer_ns();
+  for (;;) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int)(v - value) >= 0) break;                       // counters only grow (wrap-around safe)
+    if (mp::globaltimer_ns() - t0 > timeout_ns) {
+      atomicCAS(status, 0, mp::MP_DEV_TIMEOUT_PEER);
+      break;
+    }
+  }
+}
+}  // namespace
+
+int mp_peer_barrier(unsigned* const* flags_dev, int world, int rank, unsigned value, unsigned timeout_us, void* stream) {
+  if (flags_dev == nullptr || world < 1 || world > 8 || rank < 0 || rank >= world)
+    return fail(MP_ERR_INVALID_ARG, "bad peer barrier arguments (world %d, rank %d)", world, rank);
+  DeviceState* d = nullptr;
+  if (int rc = device_state(&d)) return rc;
+  int* status = nullptr;
+  MP_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), mp::g_mp_status));
+  peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      flags_dev, world, rank, value, (unsigned long long)(timeout_us ? timeout_us : 1000000u) * 1000ull, status);
+  MP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
+int mp_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+  if (ptr == nullptr || handle == nullptr || bytes == 0) return fail(MP_ERR_INVALID_ARG, "bad arguments");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  MP_CUDA_TRY(cudaMalloc(&p, bytes));
+  MP_CUDA_TRY(cudaMemset(p, 0, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(MP_ERR_CUDA, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+  }
+  std::memcpy(handle, &h, 64);
+  *ptr = p;
+  return MP_OK;
+}
+
+int mp_peer_open(const unsigned char handle[64], void** ptr) {
+  if (ptr == nullptr || handle == nullptr) return fail(MP_ERR_INVALID_ARG, "bad arguments");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  MP_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return MP_OK;
+}
+
+int mp_peer_close(void* ptr) {
+  if (ptr == nullptr) return MP_OK;
+  MP_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return MP_OK;
+}
+
+int mp_peer_free(void* ptr) {
+  if (ptr == nullptr) return MP_OK;
+  MP_CUDA_TRY(cudaFree(ptr));
+  return MP_OK;
 }
 
 int mp_scaled_mm_predict(int M, int N, int K) { return mp::scaled_mm_select(M, N, K).id; }

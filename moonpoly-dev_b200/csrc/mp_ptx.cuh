@@ -18,6 +18,8 @@ enum : int {
   MP_DEV_TIMEOUT_EPILOGUE = 104,   // epilogue waited too long for a finished accumulator
   MP_DEV_TIMEOUT_DRAIN = 105,      // teardown waited too long for copies in flight
   MP_DEV_BAD_CONFIG = 106,
+  MP_DEV_TIMEOUT_CLUSTER = 107,    // a CTA waited too long for the other K slices of its thread-block cluster
+  MP_DEV_TIMEOUT_PEER = 108,       // the cross-GPU flag barrier waited too long for another rank
 };
 
 static constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
@@ -105,6 +107,70 @@ __device__ __forceinline__ bool counter_wait_ge_for(const unsigned* ctr, unsigne
     if (ld_acquire_u32(ctr) >= target) return true;
     if (globaltimer_ns() - t0 > limit_ns) return false;
   }
+}
+
+// ----------------------------------------------------------------------------- thread-block cluster
+// Distributed shared memory between the CTAs of a cluster: plain loads from a peer's shared memory and
+// mbarrier arrivals on a peer's barrier.  No load here is a TMA / bulk copy and none uses multicast.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of this CTA's shared-memory location `addr` in the CTA of rank `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+// Arrive on a barrier in any CTA of the cluster; release at cluster scope publishes this thread's earlier
+// shared-memory writes (and, after a __syncwarp, its warp's) to whoever acquires the barrier.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+// Bounded wait with acquire at cluster scope (same contract as mbar_wait).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  unsigned long long t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((it & 0xffu) == 0) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (now - t0 > kWaitLimitNs) {
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ uint4 ld_dsmem_v4(uint32_t cluster_addr) {
+  uint4 v;
+  asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_smem_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// All threads of all CTAs of the cluster (must be reached by every thread, warps converged).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ----------------------------------------------------------------------------- TMA

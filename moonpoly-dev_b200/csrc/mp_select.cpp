@@ -333,10 +333,10 @@ TileCfg tile_cfg(int dtype, int pid) {
       c.valid = true; c.orient = (pid - 1000) >> 5; c.bn = bn; c.align = 8; c.split_capable = true;
       return c;
     } else if (pid >= 1200 && pid < 1264) {
-      // library-native 256-row tiles: pid = 1200 + 32*orient + bn/16 (single slice only)
+      // library-native 256-row tiles: pid = 1200 + 32*orient + bn/16
       const int bn = ((pid - 1200) & 31) * 16;
       if (bn < 16 || bn > 256) return c;
-      c.valid = true; c.orient = (pid - 1200) >> 5; c.bn = bn; c.align = 8; c.split_capable = false; c.xm = 2;
+      c.valid = true; c.orient = (pid - 1200) >> 5; c.bn = bn; c.align = 8; c.split_capable = true; c.xm = 2;
       return c;
     } else if (fp16_explicit_range(pid)) {
       c.valid = true; c.orient = 0; c.bn = 16; c.align = in_list(kFp16ExplicitAlign4, 45, pid) ? 4 : 8;
@@ -360,7 +360,7 @@ TileCfg tile_cfg(int dtype, int pid) {
       const int base = pid >= 1200 ? 1200 : 1000;
       const int bn = ((pid - base) & 31) * 16;
       if (bn < 16 || bn > 256) return c;
-      c.valid = true; c.orient = (pid - base) >> 5; c.bn = bn; c.align = 16; c.split_capable = base == 1000;
+      c.valid = true; c.orient = (pid - base) >> 5; c.bn = bn; c.align = 16; c.split_capable = true;
       c.xm = base == 1200 ? 2 : 1;
       return c;
     }

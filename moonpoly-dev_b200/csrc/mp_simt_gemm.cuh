@@ -33,6 +33,7 @@ struct SimtParams {
   int a_scalar, b_scalar;
   const void* bias;
   int out_bf16;
+  int bias_on_i;                       // 16-bit float GEMM with a bias: 1 = the bias index is i, 0 = j
 };
 
 template <typename T> struct SimtAcc { using type = float; };
@@ -41,6 +42,7 @@ template <> struct SimtAcc<int8_t> { using type = int; };
 template <typename TIn> __device__ __forceinline__ typename SimtAcc<TIn>::type simt_cvt(TIn v);
 template <> __device__ __forceinline__ float simt_cvt<float>(float v) { return v; }
 template <> __device__ __forceinline__ float simt_cvt<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float simt_cvt<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ int simt_cvt<int8_t>(int8_t v) { return (int)v; }
 
 template <int EPI, typename TAcc>
@@ -53,9 +55,16 @@ __device__ __forceinline__ void simt_finish(const SimtParams& p, TAcc acc, int i
     *o = v;
   } else if constexpr (EPI == SEPI_F16) {
     float v = p.alpha * acc;
-    __half* o = reinterpret_cast<__half*>(p.C) + off;
-    if (p.beta != 0.0f) v += p.beta * __half2float(*o);
-    *o = __float2half_rn(v);
+    uint16_t* o = reinterpret_cast<uint16_t*>(p.C) + off;
+    if (p.beta != 0.0f)
+      v += p.beta * (p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(*o)) : __half2float(__ushort_as_half(*o)));
+    uint16_t h = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+    if (p.bias != nullptr) {
+      const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[p.bias_on_i ? i : j];
+      if (p.out_bf16) h = __bfloat16_as_ushort(__float2bfloat16_rn(__bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(b))));
+      else h = __half_as_ushort(__float2half_rn(__half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(b))));
+    }
+    *o = h;
   } else if constexpr (EPI == SEPI_I32) {
     int v = p.ialpha * acc;
     int* o = reinterpret_cast<int*>(p.C) + off;

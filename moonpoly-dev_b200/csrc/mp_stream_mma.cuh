@@ -24,7 +24,7 @@
 
 namespace mp {
 
-enum { STREAM_F16 = 0, STREAM_I8 = 1 };
+enum { STREAM_F16 = 0, STREAM_I8 = 1, STREAM_BF16 = 2 };
 enum { STREAM_EPI_F16 = 0, STREAM_EPI_I32 = 1, STREAM_EPI_SCALED = 2 };
 
 struct StreamParams {
@@ -38,6 +38,10 @@ struct StreamParams {
   const float* chan_scale; const float* tok_scale;
   int chan_scalar, tok_scalar, chan_on_r, out_bf16;
   const void* bias;                    // in the output type, indexed by channel; may be null
+  // fused all-gather of a column-parallel Linear: the same output buffer in the memory of the other GPUs
+  // (peer-mapped pointers, same strides); every result is stored there too with plain stores
+  void* peer_out[7];
+  int num_peers;
 };
 
 constexpr int kStreamWarps = 8;        // K is split eight ways inside a CTA
@@ -50,6 +54,13 @@ __device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], uint32_t a0, uin
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_m16n8k16_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                  uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ void mma_m16n8k32_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                 uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -59,15 +70,23 @@ __device__ __forceinline__ void mma_m16n8k32_s8(int (&d)[4], uint32_t a0, uint32
 }
 
 template <int EPI>
-__device__ __forceinline__ void stream_finish(const StreamParams& p, uint32_t accw, int r, int t) {
+__device__ __forceinline__ void stream_finish_to(const StreamParams& p, void* out_base, uint32_t accw, int r, int t) {
   const long long off = (long long)r * p.stride_r + (long long)t * p.stride_t;
   if constexpr (EPI == STREAM_EPI_F16) {
-    __half* o = reinterpret_cast<__half*>(p.out) + off;
+    // 16-bit float output (fp16, or bf16 when out_bf16): RN16(alpha * acc + beta * old), then + bias in that type
+    uint16_t* o = reinterpret_cast<uint16_t*>(out_base) + off;
     float v = p.alpha * __uint_as_float(accw);
-    if (p.beta != 0.0f) v += p.beta * __half2float(*o);
-    *o = __float2half_rn(v);
+    if (p.beta != 0.0f)
+      v += p.beta * (p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(*o)) : __half2float(__ushort_as_half(*o)));
+    uint16_t h = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+    if (p.bias != nullptr) {
+      const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[p.chan_on_r ? r : t];
+      if (p.out_bf16) h = __bfloat16_as_ushort(__float2bfloat16_rn(__bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(b))));
+      else h = __half_as_ushort(__float2half_rn(__half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(b))));
+    }
+    *o = h;
   } else if constexpr (EPI == STREAM_EPI_I32) {
-    int* o = reinterpret_cast<int*>(p.out) + off;
+    int* o = reinterpret_cast<int*>(out_base) + off;
     int v = p.ialpha * (int)accw;
     if (p.ibeta != 0) v += p.ibeta * (*o);
     *o = v;
@@ -88,8 +107,14 @@ __device__ __forceinline__ void stream_finish(const StreamParams& p, uint32_t ac
         h = __half_as_ushort(__float2half_rn(s));
       }
     }
-    reinterpret_cast<uint16_t*>(p.out)[off] = h;
+    reinterpret_cast<uint16_t*>(out_base)[off] = h;
   }
+}
+
+template <int EPI>
+__device__ __forceinline__ void stream_finish(const StreamParams& p, uint32_t accw, int r, int t) {
+  stream_finish_to<EPI>(p, p.out, accw, r, t);
+  for (int d = 0; d < p.num_peers; ++d) stream_finish_to<EPI>(p, p.peer_out[d], accw, r, t);
 }
 
 // NT = number of 8-row groups of X covered (T <= 8 * NT); UNROLL = K blocks (64 bytes of each row)
@@ -170,6 +195,9 @@ stream_mma_kernel(const StreamParams p) {
           if constexpr (KIND == STREAM_I8) {
             mma_m16n8k32_s8(acci[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
             mma_m16n8k32_s8(acci[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          } else if constexpr (KIND == STREAM_BF16) {
+            mma_m16n8k16_bf16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+            mma_m16n8k16_bf16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
           } else {
             mma_m16n8k16_f16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
             mma_m16n8k16_f16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
@@ -213,6 +241,218 @@ stream_mma_kernel(const StreamParams p) {
       stream_finish<EPI>(p, accw, row0 + r, t);
     }
   }
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Cluster-K variant.  The kernel above gives every CTA whole rows of W, so every CTA walks all of K
+// and pulls all of X[T,K] through L1/L2 once per 16-row tile: with T >= 16 that traffic (T*K*e bytes
+// per CTA) is as large as the W stream itself, and with few rows (R ~ 1024) there are not enough CTAs
+// to fill the GPU.  Here a thread-block cluster of CK CTAs shares one block of rows and cuts K into CK
+// contiguous ranges: each CTA stages only its K range of X in shared memory (padded rows, so the B
+// fragments load without bank conflicts), streams its K range of W against it for up to kCkMaxTiles
+// 16-row tiles, and keeps the 16 x T partial blocks in shared memory.  At the end the CTAs of the
+// cluster read each other's partial blocks through distributed shared memory (plain loads) and rank
+// r finishes the r-th share of the rows, adding the CK partials in rank order: results are
+// deterministic.  The only waits are hardware cluster barriers that every thread reaches.
+// ------------------------------------------------------------------------------------------------
+constexpr int kCkMaxTiles = 8;         // 16-row tiles per CTA (rows per CTA <= 128)
+
+struct StreamCkParams {
+  StreamParams s;
+  int ck;              // CTAs per cluster = K ranges
+  int row_blocks;      // gridDim.x / ck
+  int stage_x;         // 1: this CTA's K range of X is staged in shared memory
+  int x_row_bytes;     // padded bytes per staged X row (a multiple of 16, odd multiple keeps the banks apart)
+};
+
+__device__ __forceinline__ uint32_t stream_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void stream_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t stream_ld_dsmem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int KIND, int EPI, int NT, int UNROLL>
+__global__ void __launch_bounds__(kStreamWarps * 32, 1)
+stream_mma_ck_kernel(const StreamCkParams cp) {
+  const StreamParams& p = cp.s;
+  extern __shared__ __align__(16) uint8_t ck_smem[];
+  constexpr int kElt = KIND == STREAM_I8 ? 1 : 2;
+  constexpr int kChunkElems = 16 / kElt;
+  constexpr int TP = NT * 8 + 1;                         // padded width of a partial block row
+  // shared memory: part[kCkMaxTiles][16][TP] | red[8][16][TP] | staged X rows
+  uint32_t* part = reinterpret_cast<uint32_t*>(ck_smem);
+  uint32_t* red = part + kCkMaxTiles * kStreamRows * TP;
+  uint8_t* xs = reinterpret_cast<uint8_t*>(red + kStreamWarps * kStreamRows * TP);
+  xs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xs) + 15) & ~uintptr_t(15));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int rank = (int)stream_cluster_rank();
+  const int rb = (int)blockIdx.x / cp.ck;
+  const int r_begin = (int)((long long)rb * p.R / cp.row_blocks);
+  const int r_end = (int)((long long)(rb + 1) * p.R / cp.row_blocks);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const char* Wb = reinterpret_cast<const char*>(p.W);
+  const char* Xb = reinterpret_cast<const char*>(p.X);
+
+  // this CTA's K range, in K blocks of four 16-byte chunks
+  const int chunks = p.K / kChunkElems;
+  const int blocks = (chunks + 3) >> 2;
+  const int cta_blk0 = (int)((long long)rank * blocks / cp.ck);
+  const int cta_blk1 = (int)((long long)(rank + 1) * blocks / cp.ck);
+  const int per_warp = (cta_blk1 - cta_blk0 + kStreamWarps - 1) / kStreamWarps;
+  const int blk_begin = cta_blk0 + warp * per_warp;
+  const int blk_end = min(cta_blk1, blk_begin + per_warp);
+
+  // pull this CTA's part of W towards L2 while the previous kernel of the stream drains (a hint only)
+  {
+    const int b0 = cta_blk0 * 64, b1 = min(cta_blk1 * 64, p.K * kElt);          // byte range inside a row
+    const int lines_per_row = (b1 - b0 + 127) >> 7;
+    for (int i = threadIdx.x; i < (r_end - r_begin) * lines_per_row; i += kStreamWarps * 32) {
+      const int r = i / lines_per_row, l = i - r * lines_per_row;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(Wb + (long long)(r_begin + r) * p.ldw * kElt + b0 + (size_t)l * 128));
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // stage X[0..T) x [K range] (16-byte chunks; rows padded by 16 bytes)
+  const int cta_chunk0 = cta_blk0 * 4;
+  const int cta_chunks = min(cta_blk1 * 4, chunks) - cta_chunk0;
+  if (cp.stage_x) {
+    for (int i = threadIdx.x; i < p.T * cta_chunks; i += kStreamWarps * 32) {
+      const int t = i / cta_chunks, c = i - t * cta_chunks;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(Xb + (long long)t * p.ldx * kElt) + cta_chunk0 + c);
+      *reinterpret_cast<uint4*>(xs + (size_t)t * cp.x_row_bytes + (size_t)c * 16) = v;
+    }
+    __syncthreads();
+  }
+
+  const uint4* xr[NT];
+  const uint8_t* xsr[NT];
+  bool x_ok[NT];
+#pragma unroll
+  for (int nb = 0; nb < NT; ++nb) {
+    x_ok[nb] = nb * 8 + g < p.T;
+    xr[nb] = reinterpret_cast<const uint4*>(Xb + (long long)(nb * 8 + g) * p.ldx * kElt);
+    xsr[nb] = xs + (size_t)(nb * 8 + g) * cp.x_row_bytes;
+  }
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+  int tile = 0;
+  for (int row0 = r_begin; row0 < r_end; row0 += kStreamRows, ++tile) {
+    const bool row_lo_ok = row0 + g < r_end, row_hi_ok = row0 + g + 8 < r_end;
+    const uint4* w_lo = reinterpret_cast<const uint4*>(Wb + (long long)(row0 + g) * p.ldw * kElt);
+    const uint4* w_hi = reinterpret_cast<const uint4*>(Wb + (long long)(row0 + g + 8) * p.ldw * kElt);
+    float accf[NT][4];
+    int acci[NT][4];
+#pragma unroll
+    for (int nb = 0; nb < NT; ++nb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { accf[nb][i] = 0.0f; acci[nb][i] = 0; }
+
+    for (int b0 = blk_begin; b0 < blk_end; b0 += UNROLL) {
+      uint4 lo[UNROLL], hi[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = (b0 + u) * 4 + t4;
+        const bool ok = b0 + u < blk_end && c < chunks;
+        lo[u] = ok && row_lo_ok ? __ldcs(w_lo + c) : zero4;
+        hi[u] = ok && row_hi_ok ? __ldcs(w_hi + c) : zero4;
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int c = (b0 + u) * 4 + t4;
+        const bool ok = b0 + u < blk_end && c < chunks;
+#pragma unroll
+        for (int nb = 0; nb < NT; ++nb) {
+          uint4 xv = zero4;
+          if (ok && x_ok[nb]) {
+            if (cp.stage_x) xv = *reinterpret_cast<const uint4*>(xsr[nb] + (size_t)(c - cta_chunk0) * 16);
+            else xv = __ldg(xr[nb] + c);
+          }
+          if constexpr (KIND == STREAM_I8) {
+            mma_m16n8k32_s8(acci[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+            mma_m16n8k32_s8(acci[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          } else if constexpr (KIND == STREAM_BF16) {
+            mma_m16n8k16_bf16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+            mma_m16n8k16_bf16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          } else {
+            mma_m16n8k16_f16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+            mma_m16n8k16_f16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+          }
+        }
+      }
+    }
+
+    if (tile != 0) __syncthreads();                     // the previous tile's warp sums have been read
+#pragma unroll
+    for (int nb = 0; nb < NT; ++nb) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w[i] = KIND == STREAM_I8 ? (uint32_t)acci[nb][i] : __float_as_uint(accf[nb][i]);
+      uint32_t* rw = red + (size_t)warp * kStreamRows * TP;
+      rw[g * TP + nb * 8 + 2 * t4] = w[0];
+      rw[g * TP + nb * 8 + 2 * t4 + 1] = w[1];
+      rw[(g + 8) * TP + nb * 8 + 2 * t4] = w[2];
+      rw[(g + 8) * TP + nb * 8 + 2 * t4 + 1] = w[3];
+    }
+    __syncthreads();
+    // this CTA's partial block of the tile: the eight warp sums in warp order
+    for (int i = threadIdx.x; i < kStreamRows * NT * 8; i += kStreamWarps * 32) {
+      const int r = i / (NT * 8), t = i - r * (NT * 8);
+      uint32_t accw;
+      if constexpr (KIND == STREAM_I8) {
+        int v = 0;
+#pragma unroll
+        for (int w = 0; w < kStreamWarps; ++w) v += (int)red[((size_t)w * kStreamRows + r) * TP + t];
+        accw = (uint32_t)v;
+      } else {
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kStreamWarps; ++w) v += __uint_as_float(red[((size_t)w * kStreamRows + r) * TP + t]);
+        accw = __float_as_uint(v);
+      }
+      part[((size_t)tile * kStreamRows + r) * TP + t] = accw;
+    }
+  }
+
+  // exchange: every CTA of the cluster has parked its partial blocks; rank r finishes the r-th share of the rows
+  stream_cluster_sync();
+  {
+    const int rows = r_end - r_begin;
+    const int my0 = (int)((long long)rank * rows / cp.ck), my1 = (int)((long long)(rank + 1) * rows / cp.ck);
+    const bool rows_contig = p.stride_r == 1;
+    const uint32_t part_addr = static_cast<uint32_t>(__cvta_generic_to_shared(part));
+    for (int i = threadIdx.x; i < (my1 - my0) * p.T; i += kStreamWarps * 32) {
+      int r, t;
+      if (rows_contig) { r = my0 + i % (my1 - my0); t = i / (my1 - my0); }
+      else { t = i % p.T; r = my0 + i / p.T; }
+      const uint32_t off = part_addr + (uint32_t)((r * TP + t) * 4);       // r = tile * 16 + row in tile
+      uint32_t accw;
+      if constexpr (KIND == STREAM_I8) {
+        int v = 0;
+        for (int c = 0; c < cp.ck; ++c) v += (int)stream_ld_dsmem(off, (uint32_t)c);
+        accw = (uint32_t)v;
+      } else {
+        float v = 0.0f;
+        for (int c = 0; c < cp.ck; ++c) v += __uint_as_float(stream_ld_dsmem(off, (uint32_t)c));
+        accw = __float_as_uint(v);
+      }
+      stream_finish<EPI>(p, accw, r_begin + r, t);
+    }
+  }
+  stream_cluster_sync();          // nobody's shared memory goes away while a peer may still read it
 }
 
 }  // namespace mp

@@ -12,7 +12,9 @@
 // (the Pattern-2 twin GEMM of moonpoly/core/fp16/fp16_rcc.cu:75-108), and K may be cut into slices
 // (Pattern-3 / pids 400+); slices park fp32/int32 partials in a workspace and the last slice to
 // arrive sums them in slice order, so the result is bit-identical from run to run and no CTA ever
-// waits for another.
+// waits for another.  When every work unit has a CTA of its own and the slice count is 2, 4 or 8, the
+// slices of a tile are instead launched as one thread-block cluster and exchange their partials through
+// distributed shared memory (CLUSTER variant below): same sums in the same order, no trip through L2.
 //
 // Roles per CTA (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2..5 = epilogue (TMEM lane quadrant = warp % 4).  Accumulators are double-buffered in TMEM
@@ -36,6 +38,7 @@ constexpr int kMaxStages = 12;
 constexpr int kUmmaThreads = 192;       // kernels that may split K: producer, MMA issuer, 4 epilogue warps
 constexpr int kUmmaThreadsWide = 320;   // single-slice kernels: 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int kSmemBudget = 232448;    // 227 KB opt-in limit per CTA
+constexpr int kClusterBarBytes = 64;   // cluster variant: ready[4 quadrants] + done barriers behind the TMEM slot
 
 enum { KIND_F16 = 0, KIND_I8 = 1 };
 enum { EPI_F16 = 0, EPI_I32 = 1, EPI_SCALED = 2 };
@@ -66,13 +69,19 @@ struct UmmaParams {
   int prefetch_kb;    // K blocks of a CTA's first unit to prefetch into L2 before the dependency wait
   void* out;
   long long out_stride_p, out_stride_q;   // element strides of `out` along P and Q
+  // fused all-gather of a column-parallel Linear: every finished tile is also stored, with the same strides, at
+  // these bases -- the same output buffer in the memory of the other GPUs (peer-mapped pointers, plain stores)
+  void* peer_out[7];
+  int num_peers;
   float alpha, beta;
   int ialpha, ibeta;
   uint32_t* ws_partials;   // [total_tiles][split_k][bn_max / 4][128 rows] 16-byte words
   unsigned* ws_counters;   // [total_tiles][4 quadrants][arrived, claimed, left, -], zero on entry, left zero on exit
-  int ws_tile_words;       // bn_max * 128
+  int ws_tile_words;       // xm * bn_max * 128: one slice of one tile (its xm 128-row halves one after the other)
+  int ws_half_words;       // bn_max * 128: one 128-row half
   int ws_slices;           // slices per tile in the scratch numbering (split_k, or sk_max_slices for stream-K tiles)
   int helpers_ok;          // 1: all units run concurrently, early slices may help with the reduction
+  int cluster_k;           // > 1: the split_k slices of a tile are the CTAs of one cluster (CLUSTER kernels only)
   // stream-K head: the first sk_tiles tiles (single region, split_k == 1) are cut into contiguous runs of
   // sk_ipc K blocks, one run per CTA, so that the remainder of total_tiles / grid does not cost a whole wave
   int sk_tiles, sk_ipc;
@@ -82,6 +91,10 @@ struct UmmaParams {
   int n_on_p;              // 1: P is the weight/output-channel index (b_scales, bias live on P)
   const void* bias;        // in the output type, indexed by output channel; may be null
   int out_bf16;
+  // FP16-kind GEMM (EPI_F16): ab_bf16 = 1 reads both operands as bf16 (output then bf16 too, out_bf16 = 1);
+  // with `bias` set, bias_on_p says whether the bias index (the output channel) runs along P or along Q
+  int ab_bf16;
+  int bias_on_p;
 };
 
 struct UnitCoord {
@@ -163,17 +176,25 @@ __device__ __forceinline__ uint16_t f32_to_out16(float v, int bf16) {
 
 // Final value for one output element from its 32-bit accumulator word.
 template <int EPI>
-__device__ __forceinline__ void finish_store(const UmmaParams& p, uint32_t accw, int pi, int qi,
+__device__ __forceinline__ void finish_store(const UmmaParams& p, void* out_base, uint32_t accw, int pi, int qi,
                                              float sp, float sq_or_zero) {
   const long long off = (long long)pi * p.out_stride_p + (long long)qi * p.out_stride_q;
   if constexpr (EPI == EPI_F16) {
+    // out = RN16(alpha * acc + beta * old); with a bias: out = RN16(out + bias[channel]), added in the output type
     float v = p.alpha * __uint_as_float(accw);
-    __half* o = reinterpret_cast<__half*>(p.out) + off;
-    if (p.beta != 0.0f) v += p.beta * __half2float(*o);
-    *o = __float2half_rn(v);
+    uint16_t* o = reinterpret_cast<uint16_t*>(out_base) + off;
+    if (p.beta != 0.0f)
+      v += p.beta * (p.out_bf16 ? __bfloat162float(__ushort_as_bfloat16(*o)) : __half2float(__ushort_as_half(*o)));
+    uint16_t h = f32_to_out16(v, p.out_bf16);
+    if (p.bias != nullptr) {
+      const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[p.bias_on_p ? pi : qi];
+      if (p.out_bf16) h = __bfloat16_as_ushort(__float2bfloat16_rn(__bfloat162float(__ushort_as_bfloat16(h)) + __bfloat162float(__ushort_as_bfloat16(b))));
+      else h = __half_as_ushort(__float2half_rn(__half2float(__ushort_as_half(h)) + __half2float(__ushort_as_half(b))));
+    }
+    *o = h;
   } else if constexpr (EPI == EPI_I32) {
     int v = p.ialpha * (int)accw;
-    int* o = reinterpret_cast<int*>(p.out) + off;
+    int* o = reinterpret_cast<int*>(out_base) + off;
     if (p.ibeta != 0) v += p.ibeta * (*o);
     *o = v;
   } else {
@@ -194,22 +215,22 @@ __device__ __forceinline__ void finish_store(const UmmaParams& p, uint32_t accw,
         h = __half_as_ushort(__float2half_rn(s));
       }
     }
-    reinterpret_cast<uint16_t*>(p.out)[off] = h;
+    reinterpret_cast<uint16_t*>(out_base)[off] = h;
   }
 }
 
 // Store 16 consecutive Q columns [q0, q0+16) of row `pi` from accumulator words r[0..15].
 template <int EPI>
-__device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_t (&r)[16], int pi, int q0,
-                                              int q_end, const ScaledStage& st) {
+__device__ __forceinline__ void store_chunk16_to(const UmmaParams& p, void* out_base, const uint32_t (&r)[16], int pi, int q0,
+                                                 int q_end, const ScaledStage& st) {
   if (pi >= p.P) return;
   const int valid = min(16, q_end - q0);
   if (valid <= 0) return;
 
   if constexpr (EPI == EPI_F16) {
     // fast path: row of D is contiguous in memory and the 32-byte run is aligned
-    if (p.out_stride_q == 1 && valid == 16 && p.beta == 0.0f) {
-      __half* o = reinterpret_cast<__half*>(p.out) + (long long)pi * p.out_stride_p + q0;
+    if (p.out_stride_q == 1 && valid == 16 && p.beta == 0.0f && p.bias == nullptr && !p.out_bf16) {
+      __half* o = reinterpret_cast<__half*>(out_base) + (long long)pi * p.out_stride_p + q0;
       if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
         uint32_t w[8];
 #pragma unroll
@@ -227,8 +248,8 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
   if constexpr (EPI == EPI_F16) {
     // rows of D are the contiguous index of the output (the 32 lanes of a warp write 64 adjacent
     // bytes per column): one pointer walks the 16 columns, no per-element index arithmetic
-    if (p.out_stride_p == 1 && p.beta == 0.0f) {
-      __half* o = reinterpret_cast<__half*>(p.out) + pi + (long long)q0 * p.out_stride_q;
+    if (p.out_stride_p == 1 && p.beta == 0.0f && p.bias == nullptr && !p.out_bf16) {
+      __half* o = reinterpret_cast<__half*>(out_base) + pi + (long long)q0 * p.out_stride_q;
       const long long step = p.out_stride_q;
       if (valid == 16) {
 #pragma unroll
@@ -243,7 +264,7 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
   }
   if constexpr (EPI == EPI_I32) {
     if (p.out_stride_p == 1 && p.ibeta == 0) {
-      int* o = reinterpret_cast<int*>(p.out) + pi + (long long)q0 * p.out_stride_q;
+      int* o = reinterpret_cast<int*>(out_base) + pi + (long long)q0 * p.out_stride_q;
       const long long step = p.out_stride_q;
 #pragma unroll
       for (int j = 0; j < 16; ++j)
@@ -253,7 +274,7 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
   }
   if constexpr (EPI == EPI_I32) {
     if (p.out_stride_q == 1 && valid == 16 && p.ibeta == 0) {
-      int* o = reinterpret_cast<int*>(p.out) + (long long)pi * p.out_stride_p + q0;
+      int* o = reinterpret_cast<int*>(out_base) + (long long)pi * p.out_stride_p + q0;
       if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -271,7 +292,7 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
     const float* sqs = st.sq + (q0 - st.q_base);
     // fast path: this thread's 16 outputs are contiguous and 16-byte aligned; the result leaves as
     // two 16-byte stores
-    uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + (long long)pi * p.out_stride_p + q0;
+    uint16_t* o = reinterpret_cast<uint16_t*>(out_base) + (long long)pi * p.out_stride_p + q0;
     if (p.out_stride_q == 1 && valid == 16 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
       float sq[16];
 #pragma unroll
@@ -317,7 +338,7 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
     }
     // every other layout: one pointer walks the 16 columns (when the rows of D are the contiguous
     // index of the output, the 32 lanes of a warp write 64 adjacent bytes per column)
-    uint16_t* ow = reinterpret_cast<uint16_t*>(p.out) + (long long)pi * p.out_stride_p + (long long)q0 * p.out_stride_q;
+    uint16_t* ow = reinterpret_cast<uint16_t*>(out_base) + (long long)pi * p.out_stride_p + (long long)q0 * p.out_stride_q;
     const long long step = p.out_stride_q;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -343,8 +364,16 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    if (j < valid) finish_store<EPI>(p, r[j], pi, q0 + j, 0.0f, 0.0f);
+    if (j < valid) finish_store<EPI>(p, out_base, r[j], pi, q0 + j, 0.0f, 0.0f);
   }
+}
+
+// The caller's output, then the same tile at every peer base (fused all-gather; num_peers is 0 otherwise).
+template <int EPI>
+__device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_t (&r)[16], int pi, int q0,
+                                              int q_end, const ScaledStage& st) {
+  store_chunk16_to<EPI>(p, p.out, r, pi, q0, q_end, st);
+  for (int d = 0; d < p.num_peers; ++d) store_chunk16_to<EPI>(p, p.peer_out[d], r, pi, q0, q_end, st);
 }
 
 // ------------------------------------------------------------------------------------ the kernel
@@ -353,7 +382,12 @@ __device__ __forceinline__ void store_chunk16(const UmmaParams& p, const uint32_
 // SPLIT = false: every unit is a whole tile; the reduction is compiled out and 8 epilogue warps (two per TMEM
 // lane quadrant, taking alternate 32-column groups) halve the time a tile needs to leave TMEM -- that time is
 // exposed whenever a CTA has a single tile, and always with 256-row tiles.
-template <int KIND, int EPI, bool SPLIT>
+// CLUSTER = true (implies SPLIT): launched with cluster dimension split_k and exactly one work unit per CTA; the
+// CTAs of a cluster are the K slices of one tile.  Each parks its raw accumulators in its OWN shared memory
+// (the pipeline stages are idle by then), tells its peers, and sums its share of the tile's columns by reading
+// every slice's partials -- its own included -- through distributed shared memory, in slice order 0..S-1: the
+// same additions in the same order as the scratch path, so both give bit-identical results.
+template <int KIND, int EPI, bool SPLIT, bool CLUSTER = false>
 __global__ void __launch_bounds__(SPLIT ? kUmmaThreads : kUmmaThreadsWide, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY0,
                  const __grid_constant__ CUtensorMap tmY1, const UmmaParams p) {
@@ -369,6 +403,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   auto tempty_bar = [&](int b) { return bar_base + 8u * (uint32_t)(2 * stages + 2 + b); };
   volatile uint32_t* tmem_slot =
       reinterpret_cast<volatile uint32_t*>(smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4));
+  // cluster variant: ready[q] (count = slices) says "quadrant q of every slice is parked", done (count = 4 x
+  // slices) says "every warp of the cluster has finished reading": no CTA's shared memory may go away before
+  const uint32_t cbar_base = bar_base + 8u * (uint32_t)(2 * stages + 4) + 16u;
+  auto ready_bar = [&](int q) { return cbar_base + 8u * (uint32_t)q; };
+  const uint32_t done_bar = cbar_base + 32u;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -383,6 +422,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), SPLIT ? 4 : 8);
     }
+    if constexpr (CLUSTER) {
+      for (int q = 0; q < 4; ++q) mbar_init(ready_bar(q), (uint32_t)p.cluster_k);
+      mbar_init(done_bar, 4u * (uint32_t)p.cluster_k);
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tmX);
     tma_prefetch_desc(&tmY0);
@@ -396,6 +439,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // peers arrive on this CTA's cluster barriers: nobody may do so before they are initialised
+  if constexpr (CLUSTER) cluster_sync_all();
 
   // Programmatic dependent launch: everything above touched only this CTA's shared memory, TMEM
   // and kernel parameters, so it may overlap the tail of the previous kernel in the stream.  Let
@@ -500,7 +545,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * (uint32_t)kMaxBN;
         const uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kUmmaM, (uint32_t)r.bn)
-                                                 : umma_idesc(1u, 0u, kUmmaM, (uint32_t)r.bn);
+                                                 : umma_idesc(1u, p.ab_bf16 ? 1u : 0u, kUmmaM, (uint32_t)r.bn);
         const uint32_t y16 = (uint32_t)(r.bn * kRowBytes) >> 4;        // Y rows of one K block
         uint32_t first = 0u;                                            // 0 until the accumulators hold a product
         for (int kb = u.kb0; kb < u.kb1; kb += p.kc) {
@@ -553,7 +598,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       float sp_h[2] = {0.0f, 0.0f};
       uint16_t bp_h[2] = {0, 0};
       if constexpr (EPI == EPI_SCALED) {
-        uint8_t* mine = smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4) + 16 + (size_t)(warp - 2) * 1536;
+        uint8_t* mine = smem + (size_t)stages * p.stage_bytes + 8 * (2 * stages + 4) + 16 + kClusterBarBytes +
+                        (size_t)(warp - 2) * 1536;
         float* sq_s = reinterpret_cast<float*>(mine);
         uint16_t* bq_s = reinterpret_cast<uint16_t*>(mine + 1024);
         const int qb = r.q_begin + u.tq * r.bn;
@@ -604,15 +650,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar((int)buf));
-      } else if constexpr (SPLIT) {
-        // park this slice's raw accumulators as [tile][slice][column / 4][row] 16-byte words: the 32
-        // lanes of a warp (32 consecutive rows) then touch 512 contiguous bytes per access, both here
-        // and in the reduction below (row-major scratch would scatter each access over 32 lines)
-        uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.ws_slices + u.slice) * (size_t)p.ws_tile_words) +
-                      row_in_tile;
+      } else if constexpr (CLUSTER) {
+        // ---- split-K inside a cluster: park the raw accumulators in this CTA's own shared memory as
+        // [column / 4][row] 16-byte words (32 lanes = 512 contiguous bytes per access, conflict-free).  The
+        // pipeline stages are idle: this CTA's only unit has been consumed by the MMAs that tfull reported.
+        const uint32_t xbuf = smem_base + (uint32_t)row_in_tile * 16u;
         for (int c0 = 0; c0 < r.bn; c0 += 32) {
           uint32_t v[2][16];
-          const bool two = c0 + 16 < r.bn;                       // two TMEM loads in flight per wait
+          const bool two = c0 + 16 < r.bn;
           tmem_ld_x16(t_addr + (uint32_t)c0, v[0]);
           if (two) tmem_ld_x16(t_addr + (uint32_t)c0 + 16u, v[1]);
           tmem_ld_wait();
@@ -621,9 +666,83 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             if (h == 0 || two) {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                __stcg(part + (size_t)(((c0 + 16 * h) >> 2) + j) * kUmmaM,
-                       make_uint4(v[h][4 * j], v[h][4 * j + 1], v[h][4 * j + 2], v[h][4 * j + 3]));
+                st_smem_v4(xbuf + (uint32_t)(((c0 + 16 * h) >> 2) + j) * (uint32_t)(kUmmaM * 16),
+                           make_uint4(v[h][4 * j], v[h][4 * j + 1], v[h][4 * j + 2], v[h][4 * j + 3]));
             }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(tempty_bar((int)buf));
+          // tell every slice of the tile (this one included) that quadrant `quad` of slice u.slice is parked
+          for (int s = 0; s < S; ++s) mbar_arrive_cluster(mapa_shared(ready_bar(quad), (uint32_t)s));
+        }
+        const bool got = mbar_wait_cluster(ready_bar(quad), 0u, status, MP_DEV_TIMEOUT_CLUSTER);
+        if (got) {
+          // this CTA finishes share `slice` of the 16-column chunks; every column is summed in slice order 0..S-1
+          const int chunks = r.bn >> 4;
+          const int c_begin = ((int)u.slice * chunks / S) << 4;
+          const int c_end = (((int)u.slice + 1) * chunks / S) << 4;
+          for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+            uint32_t v[16];
+            const uint32_t off = xbuf + (uint32_t)(c0 >> 2) * (uint32_t)(kUmmaM * 16);
+            for (int s0 = 0; s0 < S; s0 += kSliceBatch) {
+              uint4 x[kSliceBatch][4];
+#pragma unroll
+              for (int ds = 0; ds < kSliceBatch; ++ds)
+                if (s0 + ds < S) {
+                  const uint32_t remote = mapa_shared(off, (uint32_t)(s0 + ds));
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) x[ds][j] = ld_dsmem_v4(remote + (uint32_t)j * (uint32_t)(kUmmaM * 16));
+                }
+#pragma unroll
+              for (int ds = 0; ds < kSliceBatch; ++ds)
+                if (s0 + ds < S) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const uint32_t w[4] = {x[ds][j].x, x[ds][j].y, x[ds][j].z, x[ds][j].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      uint32_t& acc = v[4 * j + e];
+                      if (s0 + ds == 0) acc = w[e];
+                      else if constexpr (KIND == KIND_I8) acc = (uint32_t)((int)acc + (int)w[e]);
+                      else acc = __float_as_uint(__fadd_rn(__uint_as_float(acc), __uint_as_float(w[e])));
+                    }
+                  }
+                }
+            }
+            store_chunk16<EPI>(p, v, pi, q_tile0 + c0, q_end, st);
+          }
+        }
+        __syncwarp();
+        // the peers' shared memory is no longer needed by this warp (also reported after a failed wait, so that a
+        // healthy peer can leave)
+        if (lane == 0)
+          for (int s = 0; s < S; ++s) mbar_arrive_cluster(mapa_shared(done_bar, (uint32_t)s));
+        if (!got) { ok = false; break; }
+      } else if constexpr (SPLIT) {
+        // park this slice's raw accumulators as [tile][slice][half][column / 4][row] 16-byte words: the 32
+        // lanes of a warp (32 consecutive rows) then touch 512 contiguous bytes per access, both here
+        // and in the reduction below (row-major scratch would scatter each access over 32 lines)
+        for (int h = 0; h < p.xm; ++h) {
+          uint4* part = reinterpret_cast<uint4*>(p.ws_partials + ((size_t)u.tile * p.ws_slices + u.slice) * (size_t)p.ws_tile_words +
+                                                 (size_t)h * p.ws_half_words) + row_in_tile;
+          const uint32_t t_half = t_addr + (uint32_t)h * (uint32_t)kMaxBN;
+          for (int c0 = 0; c0 < r.bn; c0 += 32) {
+            uint32_t v[2][16];
+            const bool two = c0 + 16 < r.bn;                       // two TMEM loads in flight per wait
+            tmem_ld_x16(t_half + (uint32_t)c0, v[0]);
+            if (two) tmem_ld_x16(t_half + (uint32_t)c0 + 16u, v[1]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh)
+              if (hh == 0 || two) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  __stcg(part + (size_t)(((c0 + 16 * hh) >> 2) + j) * kUmmaM,
+                         make_uint4(v[hh][4 * j], v[hh][4 * j + 1], v[hh][4 * j + 2], v[hh][4 * j + 3]));
+              }
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -647,12 +766,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (lane == 0) ticket = atomicAdd(ctr, 1u);
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         const int chunks = r.bn >> 4;
+        const int total_chunks = chunks * p.xm;           // the tile's 128-row halves one after the other
         const bool last = ticket == (unsigned)(S - 1);
         const unsigned all_shares = (1u << S) - 1u;      // S <= 31
         unsigned mine = 0;                      // shares this warp sums
         if (last) {
           mine = 1u << ticket;
-        } else if (p.helpers_ok && ((int)ticket + 1) * chunks / S > (int)ticket * chunks / S) {
+        } else if (p.helpers_ok && ((int)ticket + 1) * total_chunks / S > (int)ticket * total_chunks / S) {
           unsigned got = 0;
           if (lane == 0) {
             atomicOr(ctr + 1, 1u << ticket);
@@ -672,10 +792,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           while (mine != 0) {
             const int share = __ffs((int)mine) - 1;
             mine &= mine - 1;
-            const int c_begin = (share * chunks / S) << 4;
-            const int c_end = ((share + 1) * chunks / S) << 4;
-          const uint4* base = reinterpret_cast<const uint4*>(p.ws_partials + (size_t)u.tile * p.ws_slices * (size_t)p.ws_tile_words) +
-                              row_in_tile;
+            const int sb = share * total_chunks / S, se = (share + 1) * total_chunks / S;
+            for (int h = 0; h < p.xm; ++h) {
+            const int lo = max(sb, h * chunks) - h * chunks, hi = min(se, (h + 1) * chunks) - h * chunks;
+            if (lo >= hi) continue;
+            const int c_begin = lo << 4, c_end = hi << 4;
+            const int pi_h = pi + h * kUmmaM;
+            if constexpr (EPI == EPI_SCALED) { st.sp = sp_h[h]; st.bp = bp_h[h]; }
+          const uint4* base = reinterpret_cast<const uint4*>(p.ws_partials + (size_t)u.tile * p.ws_slices * (size_t)p.ws_tile_words +
+                                                             (size_t)h * p.ws_half_words) + row_in_tile;
           const size_t slice_words16 = (size_t)p.ws_tile_words >> 2;
           // 32 columns per pass (the last pass may be half wide); the loads of up to kSliceBatch slices
           // are all in flight before the first is consumed
@@ -709,10 +834,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     }
                 }
             }
-            store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[0]), pi, q_tile0 + c0, q_end, st);
+            store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[0]), pi_h, q_tile0 + c0, q_end, st);
             if (nq == 8)
-              store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[16]), pi, q_tile0 + c0 + 16, q_end, st);
+              store_chunk16<EPI>(p, *reinterpret_cast<const uint32_t(*)[16]>(&v[16]), pi_h, q_tile0 + c0 + 16, q_end, st);
           }
+            }
           }
         }
         __syncwarp();
@@ -725,6 +851,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   }
 
   // ------------------------------------------------------------------ teardown
+  if constexpr (CLUSTER) {
+    // this CTA's shared memory must outlive every peer's reads of it
+    if (threadIdx.x == 0 && p.cluster_k > 1) mbar_wait_cluster(done_bar, 0u, status, MP_DEV_TIMEOUT_CLUSTER);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-MP_FP16, MP_INT8, MP_FP32 = 0, 1, 2
+MP_FP16, MP_INT8, MP_FP32, MP_BF16 = 0, 1, 2, 3
 MP_OK = 0
 STATUS_NAMES = {0: "MP_OK", 1: "MP_ERR_INVALID_ARG", 2: "MP_ERR_LAYOUT", 3: "MP_ERR_UNALIGNED_K",
                 4: "MP_ERR_BAD_PID", 5: "MP_ERR_WORKSPACE", 6: "MP_ERR_CUDA", 7: "MP_ERR_DEVICE",
@@ -72,6 +72,13 @@ def lib() -> ctypes.CDLL:
         L.mp_scaled_mm_config.argtypes = [ci, ctypes.POINTER(ci * 4)]
         L.mp_elite_fp16_pids.argtypes = [ctypes.POINTER(ci), ci]
         L.mp_device_status.argtypes = [vp, ctypes.POINTER(ci)]
+        L.mp_linear_bias.argtypes = [ci, ci, ci, ci, vp, vp, vp, vp, vp]
+        L.mp_linear_gather.argtypes = [ci, ci, ci, ci, vp, vp, ctypes.POINTER(vp), ci, ctypes.c_longlong, ctypes.c_longlong, vp]
+        L.mp_peer_barrier.argtypes = [vp, ci, ci, ctypes.c_uint, ctypes.c_uint, vp]
+        L.mp_peer_alloc.argtypes = [sz, ctypes.POINTER(vp), ctypes.c_char_p]
+        L.mp_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.mp_peer_close.argtypes = [vp]
+        L.mp_peer_free.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -251,9 +258,33 @@ def _linear_checks(x: torch.Tensor, w: torch.Tensor) -> None:
         raise ValueError("A and B must have the same dtype")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """moonpoly.linear / moonpoly_ops.linear: Y[M,N] = X[M,K] @ W[N,K]^T on the current stream."""
+def linear_bias(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y[M,N] = X[M,K] @ W[N,K]^T (+ bias[N]) in one launch, fp16 or bf16 (the reference adds the bias with a second
+    kernel and serves fp16 only).  The bias is added in the output type after the GEMM's rounding, so the result is
+    bit-identical to `linear(x, w) + bias`."""
     _linear_checks(x, w)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("linear_bias serves fp16 and bf16")
+    x = x.contiguous()
+    w = w.contiguous()
+    M, K = x.shape
+    N = w.shape[0]
+    if bias is not None:
+        if bias.dtype != x.dtype or bias.numel() != N or not bias.is_cuda:
+            raise ValueError("bias must be a CUDA tensor of N elements in the input dtype")
+        bias = bias.contiguous()
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    _check(lib().mp_linear_bias(MP_FP16 if x.dtype == torch.float16 else MP_BF16, M, N, K, _ptr(x), _ptr(w), _ptr(bias),
+                                _ptr(y), _stream(x)))
+    return y
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """moonpoly.linear / moonpoly_ops.linear: Y[M,N] = X[M,K] @ W[N,K]^T on the current stream.  bf16 inputs, which
+    the reference refuses (moonpoly/core/moonpoly_gemm.cu:74-77), are served here by the same tensor-core kernels."""
+    _linear_checks(x, w)
+    if x.dtype == torch.bfloat16:
+        return linear_bias(x, w, None)
     x = x.contiguous()
     w = w.contiguous()
     dt = _dtype_code(x)
@@ -376,6 +407,47 @@ def scaled_int8_mm(a: torch.Tensor, b: torch.Tensor, a_scales: torch.Tensor, b_s
                                  _ptr(b_scales), int(b_scales.numel() == 1), _ptr(bias), _ptr(out), N,
                                  0 if out_dtype == torch.float16 else 1, _stream(a)))
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# fused all-gather Linear: peer-mapped output buffers and the flag barrier (see shard.PeerOutput)
+# ------------------------------------------------------------------------------------------------
+def peer_alloc(nbytes: int):
+    """(device pointer, 64-byte IPC handle) of a zero-filled buffer other processes of the box can map."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    _check(lib().mp_peer_alloc(nbytes, ctypes.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    ptr = ctypes.c_void_p()
+    _check(lib().mp_peer_open(handle, ctypes.byref(ptr)))
+    return ptr.value
+
+
+def peer_close(ptr: int) -> None:
+    _check(lib().mp_peer_close(ctypes.c_void_p(ptr)))
+
+
+def peer_free(ptr: int) -> None:
+    _check(lib().mp_peer_free(ctypes.c_void_p(ptr)))
+
+
+def linear_gather(x: torch.Tensor, w_shard: torch.Tensor, dst_ptrs, ld_dst: int, col_offset: int) -> None:
+    """mp_linear_gather: Y[:, col_offset : col_offset + N_local] = X @ W_shard^T stored into every buffer of
+    `dst_ptrs` (device pointers of the full row-major output [M, ld_dst], this GPU's first)."""
+    _linear_checks(x, w_shard)
+    M, K = x.shape
+    n_local = w_shard.shape[0]
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*[ctypes.c_void_p(int(p)) for p in dst_ptrs])
+    _check(lib().mp_linear_gather(_dtype_code(x), M, n_local, K, _ptr(x), _ptr(w_shard), arr, len(dst_ptrs), ld_dst,
+                                  col_offset, _stream(x)))
+
+
+def peer_barrier(flag_table: torch.Tensor, world: int, rank: int, value: int, timeout_us: int = 0) -> None:
+    """mp_peer_barrier on the current stream; flag_table is a device int64 tensor of `world` flag-array pointers."""
+    _check(lib().mp_peer_barrier(_ptr(flag_table), world, rank, value, timeout_us, _stream(flag_table)))
 
 
 # ------------------------------------------------------------------------------------------------

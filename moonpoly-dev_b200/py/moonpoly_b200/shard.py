@@ -3,8 +3,10 @@
 The GEMM path shards by output columns: rank r owns rows [r*N/g, (r+1)*N/g) of the Linear weight
 W[N,K] (RCC A rows), activations X[M,K] are replicated, and every rank produces Y_r[M, N/g] with no
 data-path collective.  Only a layer whose full output is consumed (o_proj, down_proj in a
-Llama-style block) reassembles Y with ONE all-gather: NCCL yields [g][M][N/g], which is permuted
-to row-major [M, N].
+Llama-style block) reassembles Y.  Two ways: ONE NCCL all-gather (yields [g][M][N/g], permuted to
+row-major [M, N]), or the fused path (PeerOutput): the GEMM's epilogue stores every finished tile
+straight into the full [M, N] buffer of every GPU through peer-mapped pointers, and one small
+flag-barrier kernel with a bounded wait tells every rank that all slabs have landed.
 """
 from __future__ import annotations
 
@@ -21,6 +23,73 @@ def shard_bounds(n: int, world: int, rank: int) -> Tuple[int, int]:
     base, extra = divmod(n, world)
     start = rank * base + min(rank, extra)
     return start, start + base + (1 if rank < extra else 0)
+
+
+class _DevicePointer:
+    """Lets torch view memory this module allocated through the library (cuda array interface)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class PeerOutput:
+    """The full output Y[max_rows, n_total] (fp16) of a gathered layer: one copy per GPU, every copy mapped into
+    every rank (CUDA IPC), plus a flag array per rank for the barrier.  `exchange(obj) -> list of every rank's obj`
+    defaults to torch.distributed.all_gather_object on `group`."""
+
+    def __init__(self, max_rows: int, n_total: int, rank: int, world: int, group: Optional[dist.ProcessGroup] = None,
+                 exchange: Optional[Callable] = None, device: Optional[torch.device] = None):
+        from . import api
+        self.api, self.rank, self.world, self.n_total, self.max_rows = api, rank, world, n_total, max_rows
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.local_ptr, h_buf = api.peer_alloc(max_rows * n_total * 2)
+        self.flag_ptr, h_flag = api.peer_alloc(256)
+        if exchange is None:
+            def exchange(obj):
+                out = [None] * world
+                dist.all_gather_object(out, obj, group=group)
+                return out
+        handles = exchange((h_buf, h_flag)) if world > 1 else [(h_buf, h_flag)]
+        self.buf_ptrs, self.flag_ptrs, self._opened = [], [], []
+        for r in range(world):
+            if r == rank:
+                self.buf_ptrs.append(self.local_ptr)
+                self.flag_ptrs.append(self.flag_ptr)
+            else:
+                b, f = api.peer_open(handles[r][0]), api.peer_open(handles[r][1])
+                self._opened += [b, f]
+                self.buf_ptrs.append(b)
+                self.flag_ptrs.append(f)
+        # destination order of the GEMM: this GPU's copy first, then the peers
+        self.dst = [self.local_ptr] + [self.buf_ptrs[r] for r in range(world) if r != rank]
+        self.flag_table = torch.tensor(self.flag_ptrs, dtype=torch.int64, device=self.device)
+        self.epoch = 0
+
+    def tensor(self, rows: int) -> torch.Tensor:
+        """This GPU's copy of the output, rows [0, rows), as a torch view (no copy)."""
+        t = torch.as_tensor(_DevicePointer(self.local_ptr, (self.max_rows, self.n_total), "<f2"), device=self.device)
+        return t[:rows]
+
+    def linear_gather(self, x: torch.Tensor, w_shard: torch.Tensor, col_offset: int) -> None:
+        if x.shape[0] > self.max_rows:
+            raise ValueError(f"{x.shape[0]} rows do not fit the buffer of {self.max_rows}")
+        self.api.linear_gather(x, w_shard, self.dst, self.n_total, col_offset)
+
+    def barrier(self, timeout_us: int = 0) -> None:
+        """Every rank's slab stores issued before this call are visible on this GPU once the kernel it enqueues has
+        run; the wait inside is bounded (api.device_status() reports an expiry)."""
+        self.epoch += 1
+        self.api.peer_barrier(self.flag_table, self.world, self.rank, self.epoch, timeout_us)
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        for p in self._opened:
+            self.api.peer_close(p)
+        self._opened = []
+        for p in (self.local_ptr, self.flag_ptr):
+            if p:
+                self.api.peer_free(p)
+        self.local_ptr = self.flag_ptr = 0
 
 
 class ColumnParallelLinear:
@@ -47,6 +116,14 @@ class ColumnParallelLinear:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Local slab Y_r[M, N_r]; no communication."""
         return self.compute(x, self.w)
+
+    def forward_gather_fused(self, x: torch.Tensor, out: PeerOutput, timeout_us: int = 0) -> torch.Tensor:
+        """Full Y[M, N] on every rank without a separate collective: the GEMM stores this rank's slab into every
+        GPU's copy of `out`, then the flag barrier.  Returns this GPU's copy (a view)."""
+        lo, _ = shard_bounds(self.n_total, self.world, self.rank)
+        out.linear_gather(x, self.w, lo)
+        out.barrier(timeout_us)
+        return out.tensor(x.shape[0])
 
     def gather(self, y_local: torch.Tensor) -> torch.Tensor:
         """Full Y[M, N] on every rank (one all-gather).  Equal shards (N % world == 0, true for every

@@ -44,71 +44,80 @@ def load_peaks(root: str) -> dict:
     return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--no-gather", action="store_true", help="skip the all-gathers (GEMM time only)")
-    args = ap.parse_args()
-
+def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3, layers: int = LAYERS,
+              gather: str = "nccl", resident_frac: float = 0.85, root: str = None):
+    """Runs the stack on an initialised process group (dist is None on one GPU) and returns the result line on
+    rank 0 (None elsewhere).  gather: "fused" = the GEMM epilogue stores each slab into every GPU's copy of the
+    full output through peer-mapped pointers, then one flag-barrier kernel; "nccl" = ncclAllGather after o_proj and
+    down; "none" = GEMMs only."""
     import torch
     from . import api
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
-        dist.init_process_group("nccl", device_id=dev)
 
     L = api.lib()
     vp = ctypes.c_void_p
     stream = torch.cuda.current_stream()
     st = vp(stream.cuda_stream)
+    do_gather = gather != "none" and dist is not None
 
-    # resident layers: as many distinct weight sets as fit in half of the free memory (cycled over the 80 layers)
-    shard = [(name, n // world, k, gather) for (name, n, k, gather) in PROJECTIONS]
+    # resident layers: as many distinct weight sets as fit in `resident_frac` of the free memory (cycled over the layers)
+    shard = [(name, n // world, k, g) for (name, n, k, g) in PROJECTIONS]
     per_layer = sum(n * k * 2 for (_, n, k, _) in shard)
+    max_m = 8192
+    act_bytes = sum(max_m * k * 2 for k in {k for (_, _, k, _) in shard}) + sum(max_m * n * 2 for (_, n, _, _) in shard) + \
+        sum(world * max_m * n * 2 for (_, n, _, g) in shard if g)
     free, _ = torch.cuda.mem_get_info(dev)
-    resident = max(1, min(args.layers, int(0.5 * free / per_layer)))
+    resident = max(1, min(layers, int((resident_frac * free - act_bytes) / per_layer)))
     gen = torch.Generator(device=dev)
     gen.manual_seed(4 + 1000 * rank)
     weights = [[torch.empty((n, k), dtype=torch.float16, device=dev).normal_(0.0, 0.02, generator=gen)
                 for (_, n, k, _) in shard] for _ in range(resident)]
-    max_m = 8192
     x_in = {k: torch.empty((max_m, k), dtype=torch.float16, device=dev).normal_(0.0, 1.0, generator=gen)
             for k in sorted({k for (_, _, k, _) in shard})}
     y_loc = [torch.empty((max_m * n,), dtype=torch.float16, device=dev) for (_, n, _, _) in shard]
     y_all = [torch.empty((world * max_m * n,), dtype=torch.float16, device=dev) if g else None for (_, n, _, g) in shard]
 
-    tokens = draw_tokens(4, args.warmup + args.steps)
+    tokens = draw_tokens(4, warmup + steps)
 
-    def step(m: int, gather_events=None) -> None:
-        for layer in range(args.layers):
+    fused = {}
+    if do_gather and gather == "fused":
+        from .shard import PeerOutput
+        for j, (_, n, _, g) in enumerate(shard):
+            if g:
+                po = PeerOutput(max_m, n * world, rank, world)
+                fused[j] = (po, (vp * world)(*[vp(int(q)) for q in po.dst]), vp(po.flag_table.data_ptr()))
+    epoch = [0]
+
+    def step(m: int) -> None:
+        for layer in range(layers):
             ws = weights[layer % resident]
-            for j, (_, n, k, gather) in enumerate(shard):
+            for j, (_, n, k, g) in enumerate(shard):
+                if g and j in fused:
+                    _, dst, flag_table = fused[j]
+                    rc = L.mp_linear_gather(api.MP_FP16, m, n, k, vp(x_in[k].data_ptr()), vp(ws[j].data_ptr()), dst, world,
+                                            n * world, rank * n, st)
+                    if rc == 0:
+                        epoch[0] += 1
+                        rc = L.mp_peer_barrier(flag_table, world, rank, epoch[0], 0, st)
+                    if rc:
+                        raise RuntimeError(L.mp_last_error_string().decode())
+                    continue
                 rc = L.mp_linear(api.MP_FP16, m, n, k, vp(x_in[k].data_ptr()), vp(ws[j].data_ptr()), vp(y_loc[j].data_ptr()), st)
                 if rc:
                     raise RuntimeError(L.mp_last_error_string().decode())
-                if gather and dist is not None and not args.no_gather:
+                if g and do_gather:
                     dist.all_gather_into_tensor(y_all[j][: world * m * n], y_loc[j][: m * n])
 
-    for i in range(args.warmup):
+    for i in range(warmup):
         step(tokens[i])
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(steps):
         evs[i][0].record(stream)
-        step(tokens[args.warmup + i])
+        step(tokens[warmup + i])
         evs[i][1].record(stream)
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
@@ -119,38 +128,67 @@ def main() -> None:
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms = ms.tolist()
+    for po, _, _ in fused.values():
+        po.close()
+    del weights, x_in, y_loc, y_all
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
 
+    root = root or os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", ".."))
+    peaks = load_peaks(root)
+    ms_steps = tokens[warmup:]
+    flops_full = [2.0 * m * sum(n * k for (_, n, k, _) in PROJECTIONS) * layers for m in ms_steps]
+    roof_ms = []
+    for m in ms_steps:
+        t = 0.0
+        for (_, n, k, _) in shard:
+            f = 2.0 * m * n * k
+            b = 2.0 * (m * k + n * k + m * n)
+            t += max(f / (peaks["tflops"] * 1e12), b / (peaks["hbm_gbs"] * 1e9))
+        roof_ms.append(t * layers * 1e3)
+    decode = [i for i, m in enumerate(ms_steps) if m <= 256]
+    prefill = [i for i, m in enumerate(ms_steps) if m > 256]
+
+    def agg(idx):
+        if not idx:
+            return None
+        return {"steps": len(idx), "ms_per_step": round(sum(ms[i] for i in idx) / len(idx), 3),
+                "tflops": round(sum(flops_full[i] for i in idx) / (sum(ms[i] for i in idx) * 1e-3) / 1e12, 1),
+                "roofline_frac": round(sum(roof_ms[i] for i in idx) / sum(ms[i] for i in idx), 4)}
+    return {"metric": "llama70b_fp16_linear_stack_tflops", "value": sum(flops_full) / (sum(ms) * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": sum(ms) / len(ms), "higher_is_better": True, "scaling": "strong", "dtype": "f16",
+            "data": "synthetic", "roofline_frac": sum(roof_ms) / sum(ms), "decode": agg(decode), "prefill": agg(prefill),
+            "host_wall_ms_per_step": wall / steps * 1e3,
+            "config": {"workload": "Llama-3-70B-shaped FP16 linear stack", "layers": layers, "resident_layers": resident,
+                       "gather": gather if world > 1 else "none",
+                       "parallelism": f"column-parallel x{world}, all-gather after o_proj and down" if do_gather
+                       else f"column-parallel x{world}, no collective", "peaks": peaks,
+                       "tokens_min_max": [min(ms_steps), max(ms_steps)]}}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"])
+    args = ap.parse_args()
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    line = run_stack(rank, world, dev, dist, args.steps, args.warmup, args.layers, args.gather)
     if rank == 0:
-        root = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", "..", ".."))
-        peaks = load_peaks(root)
-        ms_steps = tokens[args.warmup:]
-        flops_full = [2.0 * m * sum(n * k for (_, n, k, _) in PROJECTIONS) * args.layers for m in ms_steps]
-        roof_ms = []
-        for m in ms_steps:
-            t = 0.0
-            for (_, n, k, _) in shard:
-                f = 2.0 * m * n * k
-                b = 2.0 * (m * k + n * k + m * n)
-                t += max(f / (peaks["tflops"] * 1e12), b / (peaks["hbm_gbs"] * 1e9))
-            roof_ms.append(t * args.layers * 1e3)
-        decode = [i for i, m in enumerate(ms_steps) if m <= 256]
-        prefill = [i for i, m in enumerate(ms_steps) if m > 256]
-
-        def agg(idx):
-            if not idx:
-                return None
-            return {"steps": len(idx), "ms_per_step": sum(ms[i] for i in idx) / len(idx),
-                    "tflops": sum(flops_full[i] for i in idx) / (sum(ms[i] for i in idx) * 1e-3) / 1e12,
-                    "roofline_frac": sum(roof_ms[i] for i in idx) / sum(ms[i] for i in idx)}
-        line = {"metric": "llama70b_fp16_linear_stack_tflops", "value": sum(flops_full) / (sum(ms) * 1e-3) / 1e12,
-                "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": sum(ms) / len(ms), "higher_is_better": True, "scaling": "strong", "dtype": "f16",
-                "data": "synthetic", "roofline_frac": sum(roof_ms) / sum(ms), "decode": agg(decode), "prefill": agg(prefill),
-                "host_wall_ms_per_step": wall / args.steps * 1e3,
-                "config": {"workload": "Llama-3-70B-shaped FP16 linear stack", "layers": args.layers, "resident_layers": resident,
-                           "parallelism": f"column-parallel x{world}, all-gather after o_proj and down" if world > 1 and not args.no_gather
-                           else f"column-parallel x{world}, no collective", "peaks": peaks,
-                           "tokens_min_max": [min(ms_steps), max(ms_steps)]}}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

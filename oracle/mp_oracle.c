@@ -175,9 +175,45 @@ static void scaled_mm_rows(const job_t *j) {
   }
 }
 
+/* Linear with a fused bias, fp16 or bf16 operands: acc = sum_k W[ch,k] * X[t,k] in fp32 (ascending k, the loop of
+ * moonpoly/core/moonpoly_gemm.cu:1613-1617 under the Linear remap of :41-44), y = RN16(acc), then the bias is added
+ * IN THE OUTPUT TYPE as the reference's callers do with a second kernel (output = linear(x, w); output + bias:
+ * integrations/vllm/v0.10.0/moonpoly_linear.patch:700-712): y = RN16(float(y) + float(bias[ch])).
+ * Parity note: no reference kernel computes this in one pass, so this function is pinned through its two halves --
+ * the GEMM half against the reference's kernels, the bias half by its definition.  Rows of Y (tokens) are split
+ * over the threads: col0 / col1 are token indices here. */
+static void linear_bias_rows(const job_t *j) {
+  const uint16_t *X = (const uint16_t *)j->B, *W = (const uint16_t *)j->A, *bias = (const uint16_t *)j->bias;
+  uint16_t *Y = (uint16_t *)j->C;
+  const int N = j->m, K = j->k, bf = j->out_bf16;
+  for (int t = j->col0; t < j->col1; ++t) {
+    for (int ch = 0; ch < N; ++ch) {
+      float acc = 0.0f;
+      const uint16_t *x = X + (size_t)t * K, *w = W + (size_t)ch * K;
+      if (bf) {
+        for (int kk = 0; kk < K; ++kk) acc += bf16_to_f32(w[kk]) * bf16_to_f32(x[kk]);
+      } else {
+        const half_t *xh = (const half_t *)x, *wh = (const half_t *)w;
+        for (int kk = 0; kk < K; ++kk) acc += (float)wh[kk] * (float)xh[kk];
+      }
+      uint16_t y;
+      if (bf) {
+        y = f32_to_bf16_rn(acc);
+        if (bias) y = f32_to_bf16_rn(bf16_to_f32(y) + bf16_to_f32(bias[ch]));
+      } else {
+        half_t h = (half_t)acc;
+        if (bias) { half_t b; memcpy(&b, &bias[ch], 2); h = (half_t)((float)h + (float)b); }
+        memcpy(&y, &h, 2);
+      }
+      Y[(size_t)t * N + ch] = y;
+    }
+  }
+}
+
 static void *worker(void *p) {
   const job_t *j = (const job_t *)p;
   switch (j->kind) {
+    case 5: linear_bias_rows(j); break;
     case 0: gemm_f16_cols(j); break;
     case 1: gemm_f32_cols(j); break;
     case 2: gemm_i8_cols(j); break;
@@ -259,6 +295,14 @@ void orc_scaled_mm_i8(int m, int n, int k, const int8_t *A, const int8_t *B_nk,
  * moonpoly/core/moonpoly_gemm.cu:41-44: RCC m = N, n = M, A = W, B = X. */
 void orc_linear_f16(int M, int N, int K, const void *X, const void *W, void *Y, int threads) {
   orc_gemm_f16_rcc(N, M, K, W, X, Y, 1.0f, 0.0f, threads);
+}
+
+/* Linear with fused bias (bias may be NULL), operands / output fp16 (bf16 = 0) or bf16 (bf16 = 1, passed as their
+ * 16-bit patterns). */
+void orc_linear_bias(int M, int N, int K, const void *X, const void *W, const void *bias, void *Y, int bf16, int threads) {
+  job_t j = {0};
+  j.kind = 5; j.m = N; j.n = M; j.k = K; j.A = W; j.B = X; j.C = Y; j.bias = bias; j.out_bf16 = bf16;
+  run_split(j, M, threads);
 }
 
 /* Pattern-2 twin GEMM restated from moonpoly/core/fp16/fp16_rcc.cu:97-104:

@@ -131,6 +131,23 @@ def linear_f16(X, W, threads=None):
     return Y
 
 
+def linear_bias(X, W, bias=None, bf16=False, threads=None):
+    """Linear(X[M,K], W[N,K]) (+ bias[N]) -> Y[M,N], bias added in the output type after the rounding of the GEMM.
+    fp16 arrays, or (bf16=True) uint16 arrays holding bfloat16 bit patterns; returns the same kind."""
+    dt = np.uint16 if bf16 else np.float16
+    X = np.ascontiguousarray(X, dtype=dt)
+    W = np.ascontiguousarray(W, dtype=dt)
+    M, K = X.shape
+    N, _ = W.shape
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=dt).reshape(-1)
+        assert bias.size == N
+    Y = np.zeros((M, N), dt)
+    lib().orc_linear_bias(ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), _p(X), _p(W), _p(bias), _p(Y),
+                          ctypes.c_int(int(bf16)), ctypes.c_int(threads or host_threads()))
+    return Y
+
+
 def twin_gemm_f16(A, B_nk, split_n, alpha=1.0, beta=0.0, C_nm=None, threads=None):
     A = np.ascontiguousarray(A, dtype=np.float16)
     B_nk = np.ascontiguousarray(B_nk, dtype=np.float16)

@@ -176,7 +176,9 @@ def test_fp16_linear_matches_rcc_remap(api, oracle):
 def test_layout_and_dtype_errors(api):
     a = torch.zeros((4, 8), dtype=torch.float16, device=DEV)
     with pytest.raises(ValueError):
-        api.linear(a.to(torch.bfloat16), a.to(torch.bfloat16))
+        api.gemm_rcc(a.to(torch.bfloat16), a.to(torch.bfloat16))     # the RCC entry keeps the reference's dtype set
+    with pytest.raises(ValueError):
+        api.linear(a.to(torch.float64), a.to(torch.float64))
     L = api.lib()
     rc = L.mp_gemm(0, 4, 4, 8, a.data_ptr(), 1, a.data_ptr(), 1, a.data_ptr(), 1, 1.0, 0.0, None)
     assert rc == 2
@@ -607,3 +609,231 @@ def test_reported_workspace_is_enough_for_the_streaming_pids_fallback(api, oracl
     ws = torch.full((need,), 0xCD, dtype=torch.uint8, device=DEV)
     c = api.gemm_rcc_pid(dev(a), dev(b), pid, split, workspace=ws).cpu().numpy()
     close_f16(c, oracle.gemm_f16_rcc(a, b))
+
+
+# ------------------------------------------------------------------ split-K inside a thread-block cluster
+def _with_and_without_cluster(api, monkeypatch, fn):
+    """Runs fn() with the cluster split-K path (MOONPOLY_ENABLE_CLUSTER_SPLITK=1) and with the default path (partials
+    through the global scratch)."""
+    try:
+        monkeypatch.setenv("MOONPOLY_ENABLE_CLUSTER_SPLITK", "1")
+        api.reload_env()
+        with_cluster = fn()
+    finally:
+        monkeypatch.delenv("MOONPOLY_ENABLE_CLUSTER_SPLITK", raising=False)
+        api.reload_env()
+    without = fn()
+    return with_cluster, without
+
+
+@pytest.mark.parametrize("orient,bn,split,m,n,k", [
+    (1, 128, 4, 128, 4096, 4096),      # the sweep's M = 128 plan: 32 tiles x 4 slices, one CTA each
+    (1, 64, 4, 64, 4096, 4096), (0, 128, 2, 4096, 255, 4096), (1, 256, 2, 250, 2000, 2048),
+    (0, 16, 8, 1024, 8, 8192),         # decode shape through a 128 x 16 tile, 8 slices
+    (0, 32, 8, 1000, 30, 8200), (1, 48, 4, 40, 1100, 2072), (0, 96, 2, 300, 90, 520), (0, 208, 4, 130, 200, 2048)])
+def test_fp16_cluster_splitk_bit_identical_to_scratch_path(api, oracle, monkeypatch, orient, bn, split, m, n, k):
+    """The K slices of a tile run as one thread-block cluster and exchange partial sums through distributed shared
+    memory.  Every column is still summed in slice order, so the result must equal the scratch path's bit for bit
+    (N(0,1)*0.05 inputs: any change of summation order would show), and agree with the oracle."""
+    a = rng.normal(130, 0, (m, k), 0.05)
+    b = rng.normal(130, 1, (n, k), 0.05)
+    c0 = rng.normal(130, 2, (n, m), 1.0)
+    A, B = dev(a), dev(b)
+    got, plain = _with_and_without_cluster(api, monkeypatch, lambda: api.gemm_rcc_tile(A, B, orient, bn, split_k=split).cpu().numpy())
+    assert np.array_equal(got, plain)
+    rows = min(m, 256)                                   # every output is an independent dot product: check the first rows
+    close_f16(got[:, :rows], oracle.gemm_f16_rcc(a[:rows], b))
+    got_ab, plain_ab = _with_and_without_cluster(
+        api, monkeypatch,
+        lambda: api.gemm_rcc_tile(A, B, orient, bn, split_k=split, c_nm=dev(c0).clone(), alpha=0.5, beta=-1.5).cpu().numpy())
+    assert np.array_equal(got_ab, plain_ab)
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("split", [2, 4, 8])
+def test_int8_cluster_splitk_exact(api, oracle, monkeypatch, split):
+    m, n, k = 150, 700, 4096
+    a = rng.int8_uniform(131, 0, (m, k))
+    b = rng.int8_uniform(131, 1, (n, k))
+    A, B = dev(a), dev(b)
+    got, plain = _with_and_without_cluster(api, monkeypatch, lambda: api.gemm_rcc_tile(A, B, 1, 128, split_k=split).cpu().numpy())
+    assert np.array_equal(got, plain)
+    assert np.array_equal(got, oracle.gemm_i8_rcc(a, b))
+    # the scaled epilogue on the same launch shape
+    sa = rng.uniform(131, 2, (m,), 0.001, 0.02)
+    sb = rng.uniform(131, 3, (n,), 0.001, 0.02)
+    bias = rng.uniform(131, 4, (n,), -1.0, 1.0).astype(np.float16)
+    L = api.lib()
+    SA, SB, BI = dev(sa), dev(sb), dev(bias)
+
+    def scaled():
+        out = torch.empty((m, n), dtype=torch.float16, device=DEV)
+        rc = L.mp_scaled_mm_i8_tile(1, 128, split, m, n, k, A.data_ptr(), k, B.data_ptr(), k, SA.data_ptr(), 0, SB.data_ptr(), 0,
+                                    BI.data_ptr(), out.data_ptr(), n, 0, None)
+        assert rc == 0, L.mp_last_error_string()
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+    s_got, s_plain = _with_and_without_cluster(api, monkeypatch, scaled)
+    assert np.array_equal(s_got.view(np.uint16), s_plain.view(np.uint16))
+    assert np.array_equal(s_got.view(np.uint16), oracle.scaled_mm_i8(a, b, sa, sb, bias).view(np.uint16))
+    assert api.device_status() == 0
+
+
+# ------------------------------------------------------------------ cluster-K streaming kernel
+@pytest.mark.parametrize("m,n,k,ck", [
+    (16, 4096, 4096, 2), (32, 4096, 4096, 2), (32, 4096, 4096, 1), (9, 1024, 8192, 4), (1, 1024, 8192, 4), (8, 1024, 28672, 8),
+    (32, 1024, 8192, 4), (24, 1000, 8200, 4), (64, 2048, 4096, 2), (40, 513, 2056, 2), (4096, 20, 4096, 2), (700, 3, 16384, 8),
+    (5, 130, 72, 1), (17, 33, 4096, 4)])
+def test_fp16_cluster_k_streaming_kernel(api, oracle, m, n, k, ck):
+    """The streaming kernel whose clusters cut K: staged X ranges, partial blocks exchanged through distributed shared
+    memory and added in rank order.  Against the oracle, exact on integers, reproducible, with alpha / beta, both
+    mappings (narrow side on m or on n), ragged rows, ragged K ranges."""
+    a = rng.normal(140, 0, (m, k), 0.05)
+    b = rng.normal(140, 1, (n, k), 0.05)
+    c0 = rng.normal(140, 2, (n, m), 1.0)
+    ref = oracle.gemm_f16_rcc(a, b)
+    A, B = dev(a), dev(b)
+    got = api.gemm_rcc_tile(A, B, 3, 16, kc=ck).cpu().numpy()
+    close_f16(got, ref)
+    assert np.array_equal(got, api.gemm_rcc_tile(A, B, 3, 16, kc=ck).cpu().numpy())
+    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=-1).cpu().numpy(), ref)            # the plain streaming kernel
+    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=0).cpu().numpy(), ref)             # the library's own choice
+    ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
+    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=ck, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
+    ai = rng.small_ints(141, 0, (m, k), lo=-1, hi=1)
+    bi = rng.small_ints(141, 1, (n, k))
+    exact = _exact_ref(ai, bi)
+    if np.abs(exact).max() < 2048:
+        assert np.array_equal(api.gemm_rcc_tile(dev(ai), dev(bi), 3, 16, kc=ck).cpu().numpy(), exact.astype(np.float16))
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k,ck", [(32, 1024, 8192, 2), (16, 4096, 16384, 4), (9, 600, 4096, 1), (2000, 12, 8192, 2)])
+def test_int8_cluster_k_streaming_kernel_bit_exact(api, oracle, monkeypatch, m, n, k, ck):
+    a = rng.int8_uniform(142, 0, (m, k))
+    b = rng.int8_uniform(142, 1, (n, k))
+    c0 = rng.int8_uniform(142, 2, (n, m)).astype(np.int32) * 37
+    ref = oracle.gemm_i8_rcc(a, b)
+    got = api.gemm_rcc_tile(dev(a), dev(b), 3, 16, kc=ck).cpu().numpy()
+    assert np.array_equal(got, ref)
+    got_ab = api.gemm_rcc_tile(dev(a), dev(b), 3, 16, kc=ck, c_nm=dev(c0), alpha=2.0, beta=-3.0).cpu().numpy()
+    assert np.array_equal(got_ab, oracle.gemm_i8_rcc(a, b, 2, -3, c0))
+    # the scaled epilogue reaches the cluster-K kernel when the library is allowed to pick it by itself
+    monkeypatch.setenv("MOONPOLY_ENABLE_STREAM_CLUSTER", "1")
+    api.reload_env()
+    M, N = (m, n)
+    sa = rng.uniform(142, 3, (M,), 0.001, 0.02)
+    sb = rng.uniform(142, 4, (N,), 0.001, 0.02)
+    bias = rng.uniform(142, 5, (N,), -1.0, 1.0).astype(np.float16)
+    L = api.lib()
+    out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+    A, B, SA, SB, BI = dev(a), dev(b), dev(sa), dev(sb), dev(bias)
+    rc = L.mp_scaled_mm_i8_tile(3, 16, 1, M, N, k, A.data_ptr(), k, B.data_ptr(), k, SA.data_ptr(), 0, SB.data_ptr(), 0,
+                                BI.data_ptr(), out.data_ptr(), N, 0, None)
+    assert rc == 0, L.mp_last_error_string()
+    torch.cuda.synchronize()
+    monkeypatch.delenv("MOONPOLY_ENABLE_STREAM_CLUSTER")
+    api.reload_env()
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), oracle.scaled_mm_i8(a, b, sa, sb, bias).view(np.uint16))
+    assert api.device_status() == 0
+
+
+# ------------------------------------------------------------------ 256-row tiles with K slices
+@pytest.mark.parametrize("orient,bn,split,m,n,k", [(4, 256, 4, 512, 4096, 4096), (5, 256, 2, 1000, 1023, 4096),
+                                                    (4, 128, 8, 257, 300, 2120), (5, 192, 3, 600, 700, 1096),
+                                                    (4, 64, 2, 2500, 200, 2048), (4, 256, 8, 255, 4096, 4096)])
+def test_fp16_256_row_tiles_with_k_slices(api, oracle, orient, bn, split, m, n, k):
+    """256-row tiles whose K is cut into slices: both 128-row halves of every slice are parked in the scratch and
+    summed in slice order.  Exact on integer-valued inputs (ragged edges, alpha / beta), reproducible and within
+    tolerance of the oracle on N(0,1)*0.05 inputs; pids 1200+ honour the run-time split factor."""
+    a = rng.small_ints(150, 0, (m, k), lo=-1, hi=1)
+    b = rng.small_ints(150, 1, (n, k))
+    ref = _exact_ref(a, b)
+    assert np.abs(ref).max() < 2048
+    A, B = dev(a), dev(b)
+    got = api.gemm_rcc_tile(A, B, orient, bn, split_k=split).cpu().numpy()
+    assert np.array_equal(got, ref.astype(np.float16))
+    pid = 1200 + 32 * (orient - 4) + bn // 16
+    assert np.array_equal(api.gemm_rcc_pid(A, B, pid, split).cpu().numpy(), got)
+    need = api.workspace_size(api.MP_FP16, pid, m, n, k, split)
+    ws = torch.full((need,), 0x5A, dtype=torch.uint8, device=DEV)
+    assert np.array_equal(api.gemm_rcc_pid(A, B, pid, split, workspace=ws).cpu().numpy(), got)
+    c0 = rng.small_ints(150, 2, (n, m)).astype(np.float16)
+    got_ab = api.gemm_rcc_tile(A, B, orient, bn, split_k=split, c_nm=dev(c0).clone(), alpha=2.0, beta=-1.0).cpu().numpy()
+    assert np.array_equal(got_ab, (2.0 * ref - c0.astype(np.float64)).astype(np.float16))
+    an = rng.normal(151, 0, (m, k), 0.05)
+    bn_ = rng.normal(151, 1, (n, k), 0.05)
+    rows = sorted(set([0, m - 1] + list(range(0, m, max(1, m // 64)))))
+    gn = api.gemm_rcc_tile(dev(an), dev(bn_), orient, bn, split_k=split).cpu().numpy()
+    close_f16(gn[:, rows], oracle.gemm_f16_rcc(an[rows], bn_))
+    assert np.array_equal(gn, api.gemm_rcc_tile(dev(an), dev(bn_), orient, bn, split_k=split).cpu().numpy())
+    assert api.device_status() == 0
+
+
+def test_256_row_tiles_stream_k_head_and_int8_slices(api, monkeypatch):
+    # 10 x 20 tiles of 256 x 256 on 148 CTAs: the 52 left-over tiles go first, cut along K over all CTAs
+    m, n, k = 2560, 5120, 512
+    a = rng.small_ints(152, 0, (m, k), lo=-1, hi=1)
+    b = rng.small_ints(152, 1, (n, k))
+    ref = _exact_ref(a, b).astype(np.float16)
+    A, B = dev(a), dev(b)
+    try:
+        got = api.gemm_rcc_tile(A, B, 4, 256).cpu().numpy()
+        monkeypatch.setenv("MOONPOLY_DISABLE_STREAMK", "1")
+        api.reload_env()
+        plain = api.gemm_rcc_tile(A, B, 4, 256).cpu().numpy()
+    finally:
+        monkeypatch.delenv("MOONPOLY_DISABLE_STREAMK", raising=False)
+        api.reload_env()
+    assert np.array_equal(got, ref) and np.array_equal(plain, ref)
+    a8 = rng.int8_uniform(153, 0, (700, 2048))
+    b8 = rng.int8_uniform(153, 1, (900, 2048))
+    ref8 = (a8.astype(np.float64) @ b8.astype(np.float64).T).T.astype(np.int64)
+    for orient, split in ((4, 2), (5, 4)):
+        got8 = api.gemm_rcc_tile(dev(a8), dev(b8), orient, 256, split_k=split).cpu().numpy()
+        assert np.array_equal(got8.astype(np.int64), ref8)
+    assert api.device_status() == 0
+
+
+# ------------------------------------------------------------------ BF16 and fused bias (Linear)
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 2048), (7, 4096, 4096), (24, 512, 8192), (64, 1000, 1024), (130, 384, 520),
+                                   (300, 2304, 1024), (1000, 520, 2048), (5, 48, 40), (2100, 4096, 512)])
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_linear_bias_fp16_bf16_vs_oracle(api, oracle, M, N, K, bf16, with_bias):
+    """Linear with the bias fused into the epilogue, fp16 and bf16: streaming kernels, tensor tiles with and without
+    split-K, 256-row tiles, and the CUDA-core tiles for K that TMA cannot describe (K = 40).  Against the oracle within
+    the path's tolerance, and bit-identical to the two-step linear + bias the reference's callers do."""
+    x32 = rng.normal(170, 0, (M, K), 0.05, dtype=np.float32)
+    w32 = rng.normal(170, 1, (N, K), 0.05, dtype=np.float32)
+    b32 = rng.uniform(170, 5, (N,), -1.0, 1.0)
+    if bf16:
+        xb, wb, bb = (oracle.bf16_bits_from_f32(v) for v in (x32, w32, b32))
+        X, W, B = (dev(v.view(np.int16)).view(torch.bfloat16) for v in (xb, wb, bb))
+        ref = oracle.f32_from_bf16_bits(oracle.linear_bias(xb, wb, bb if with_bias else None, bf16=True))
+        rtol, atol = 2e-2, 8e-3            # bf16 keeps 8 bits of mantissa
+    else:
+        xh, wh, bh = x32.astype(np.float16), w32.astype(np.float16), b32.astype(np.float16)
+        X, W, B = dev(xh), dev(wh), dev(bh)
+        ref = oracle.linear_bias(xh, wh, bh if with_bias else None).astype(np.float32)
+        rtol, atol = 1e-2, 1e-3
+    y = api.linear_bias(X, W, B if with_bias else None)
+    got = y.float().cpu().numpy()
+    bad = np.abs(got - ref) > atol + rtol * np.abs(ref)
+    assert not bad.any(), f"{bad.sum()} of {bad.size} differ; max abs {np.abs(got - ref).max()}"
+    two_step = api.linear(X, W)
+    if with_bias:
+        two_step = two_step + B            # torch adds in fp32 and rounds once to the tensor dtype: the same operation
+    assert torch.equal(y, two_step)
+    assert api.device_status() == 0
+
+
+def test_bf16_linear_exact_on_integers(api):
+    M, N, K = 70, 300, 1024
+    x = rng.small_ints(171, 0, (M, K), lo=-1, hi=1, dtype=np.float32)
+    w = rng.small_ints(171, 1, (N, K), dtype=np.float32)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(ref).max() <= 256                # exactly representable in bf16
+    y = api.linear(dev(x).to(torch.bfloat16), dev(w).to(torch.bfloat16))
+    assert y.dtype == torch.bfloat16
+    assert np.array_equal(y.float().cpu().numpy(), ref.astype(np.float32))

@@ -120,11 +120,13 @@ def test_fp16_oracle_rounding_pinned_by_reference(oracle, tmp_path):
     batch.add("fp16_pid", a, b, pid=8)
     ref = batch.run()[0]
     orc = oracle.gemm_f16_rcc(a, b)
-    ulp = np.abs(ref.view(np.int16).astype(np.int32) - orc.view(np.int16).astype(np.int32))
-    same_sign = np.signbit(ref) == np.signbit(orc)
-    assert np.all(ulp[same_sign] <= 1), f"max distance {ulp[same_sign].max()} fp16 steps"
-    assert np.all(np.abs(ref[~same_sign].astype(np.float32)) < 1e-3)       # sign flips only around zero
-    assert (ulp[same_sign] == 0).mean() > 0.97
+    # fp32 accumulation noise of a 4096-term sum of this size is a few 1e-6: outputs may differ by that, or by one
+    # fp16 step where a sum lands near a rounding boundary -- never by more
+    r32, o32 = ref.astype(np.float32), orc.astype(np.float32)
+    step = np.spacing(np.maximum(np.abs(ref), np.abs(orc)).astype(np.float16)).astype(np.float32)
+    diff = np.abs(r32 - o32)
+    assert np.all(diff <= step + 5e-6), f"max excess {(diff - step).max():.3g}"
+    assert (diff == 0).mean() > 0.97, f"only {(diff == 0).mean():.4f} of the outputs are identical"
 
 
 def test_fp16_online_selector_three_way(api, oracle, tmp_path):
@@ -176,11 +178,13 @@ def test_fp16_twin_gemm_three_way(api, oracle, tmp_path):
 def test_int8_three_way_bit_exact(api, oracle, tmp_path):
     batch = RefBatch(tmp_path)
     cases = []
-    for (m, n, k) in ((64, 128, 128), (37, 200, 4096), (150, 70, 512)):
+    # m % 4 == 0 throughout: the reference's INT8 kernels store C with 16-byte vectors along m and fault with
+    # "misaligned address" on column-major C whose leading dimension m is not a multiple of 4
+    for (m, n, k) in ((64, 128, 128), (36, 200, 4096), (152, 72, 512)):
         a, b = rng.int8_uniform(3, rng.STREAM_A, (m, k)), rng.int8_uniform(3, rng.STREAM_B, (n, k))
         cases.append(("auto", 0, a, b))
         batch.add("int8_auto", a, b)
-    a, b = rng.int8_uniform(104, 0, (150, 512)), rng.int8_uniform(104, 1, (70, 512))
+    a, b = rng.int8_uniform(104, 0, (152, 512)), rng.int8_uniform(104, 1, (72, 512))
     for pid in (0, 6, 17, 30, 45):
         cases.append(("pid", pid, a, b))
         batch.add("int8_pid", a, b, pid=pid)

@@ -1,4 +1,4 @@
-"""Column-parallel Linear on two real GPUs (NCCL); skipped on a one-GPU box."""
+"""Column-parallel Linear on two real GPUs: NCCL all-gather and the fused peer-store gather; skipped on a one-GPU box."""
 import os
 import socket
 
@@ -37,6 +37,22 @@ def _worker(rank, world, port, tmp):
         y = layer.gather(layer.forward(x))
         full = api.linear(x, w)
         assert torch.equal(y, full)          # same kernels on the same columns: bit-identical
+        # the fused path: slabs stored straight into every GPU's copy of Y through peer-mapped pointers (plain
+        # stores, no multimem), then the flag barrier
+        from moonpoly_b200.shard import PeerOutput
+        out = PeerOutput(256, N, rank, world)
+        try:
+            for rows in (48, 5, 200):
+                xs = torch.from_numpy(rng.normal(42 + rows, 0, (rows, K), 0.05)).cuda()
+                got = layer.forward_gather_fused(xs, out)
+                torch.cuda.synchronize()
+                # the NCCL-gathered result of the same shards: same kernels on the same columns, bit-identical
+                assert torch.equal(got, layer.gather(layer.forward(xs))), rows
+                ref = api.linear(xs, w).float()
+                assert torch.all((got.float() - ref).abs() <= 1e-3 + 1e-2 * ref.abs()), rows
+                dist.barrier()               # nobody overwrites the buffer while a peer still compares
+        finally:
+            out.close()
         assert api.device_status() == 0
         open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
     finally:
