@@ -331,7 +331,9 @@ def extra_sections(api, L, st, dev, peaks):
         L.mp_select_plan(api.MP_FP16, 3 + i, 4104 + 8 * (i % 97), 4096, pref)
     t_cold = (time.perf_counter() - t0) / n_calls
     out["selector_host_us"] = {"warm": round(max(0.0, t_warm - t_empty) * 1e6, 3), "cold": round(max(0.0, t_cold - t_empty) * 1e6, 3),
-                               "ctypes_empty_call": round(t_empty * 1e6, 3), "calls": n_calls}
+                               "warm_call_total": round(t_warm * 1e6, 3), "cold_call_total": round(t_cold * 1e6, 3),
+                               "ctypes_call": round(t_empty * 1e6, 3), "calls": n_calls,
+                               "note": "warm / cold = call total minus the cost of a ctypes call that returns at its first check"}
     out["fp16_splitk_decode"] = {"roofline_geomean_frac": round(geomean(fr), 4),
                                  "selector_roofline_geomean_frac": round(geomean(fr_sel), 4), "rows": rows}
     return out

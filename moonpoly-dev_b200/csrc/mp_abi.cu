@@ -76,6 +76,7 @@ struct DeviceState {
   int sms = 0;
   int cc = 0;
   bool attrs[9] = {false, false, false, false, false, false, false, false, false};
+  bool skinny_attrs[2] = {false, false};
   bool stream_attrs[16] = {false, false, false, false, false, false, false, false, false, false, false, false,
                            false, false, false, false};
 };
@@ -786,6 +787,22 @@ int launch_skinny_f32(const SkinnyF32Params& sp, cudaStream_t stream) {
   return MP_OK;
 }
 
+template <int TMAX, int ROWS>
+int launch_skinny_f32_smem(DeviceState& d, int slot, const SkinnyF32Params& sp, cudaStream_t stream) {
+  auto kern = skinny_f32_smem_kernel<TMAX, ROWS>;
+  if (!d.skinny_attrs[slot]) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    d.skinny_attrs[slot] = true;
+  }
+  const size_t smem = (size_t)sp.T * sp.K * 4;
+  const int rows_per_pass = kSkinnySmemWarps * ROWS;
+  const int grid = std::max(1, std::min(d.sms, (sp.R + rows_per_pass - 1) / rows_per_pass));
+  kern<<<grid, kSkinnySmemWarps * 32, smem, stream>>>(sp);
+  MP_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return MP_OK;
+}
+
 int run_skinny_f32(const Problem& p, cudaStream_t stream) {
   DeviceState* d = nullptr;
   if (int rc = device_state(&d)) return rc;
@@ -802,6 +819,11 @@ int run_skinny_f32(const Problem& p, cudaStream_t stream) {
   sp.stride_r = narrow_is_a ? p.c_stride_n : p.c_stride_m;
   sp.stride_t = narrow_is_a ? p.c_stride_m : p.c_stride_n;
   sp.alpha = p.alpha; sp.beta = p.beta;
+  // X small enough for shared memory and wide enough that re-reading it through L1 hurts: the staged kernel
+  if (sp.T > 8 && sp.T <= 40 && (size_t)sp.T * sp.K * 4 <= 200u * 1024u && sp.R >= 64) {
+    if (sp.T <= 16) return launch_skinny_f32_smem<16, 2>(*d, 0, sp, stream);
+    return launch_skinny_f32_smem<40, 2>(*d, 1, sp, stream);
+  }
   // two rows per warp halve the re-reads of X as long as there are rows enough to fill the GPU
   const bool two = sp.R >= 4 * kSkinnyF32Warps * d->sms;
   if (sp.T <= 8) return two ? launch_skinny_f32<8, 2>(sp, stream) : launch_skinny_f32<8, 1>(sp, stream);

@@ -540,7 +540,8 @@ def test_int8_gemm_follows_measured_plans_bit_exact(api, m):
     assert np.array_equal(api.gemm_rcc_pid(dev(a), dev(b), plan.pid, plan.split_k).cpu().numpy(), got)
 
 
-@pytest.mark.parametrize("m,n,k", [(37, 1024, 1024), (1, 300, 512), (64, 129, 2052), (700, 5, 1024), (9, 40, 8)])
+@pytest.mark.parametrize("m,n,k", [(37, 1024, 1024), (1, 300, 512), (64, 129, 2052), (700, 5, 1024), (9, 40, 8),
+                                   (16, 500, 2000), (33, 2000, 1280), (40, 64, 1024), (12, 4096, 4096), (1000, 20, 2560)])
 def test_fp32_streaming_kernel(api, oracle, m, n, k):
     """Library-native pid 1101 for FP32 (one warp per row of the wide operand): within 1e-4 of the oracle on
     uniform inputs, exact on small integers, alpha/beta, both mappings; the selector names it for these shapes."""

@@ -85,3 +85,70 @@ def test_stack_token_draws_follow_the_decode_prefill_mix():
     assert min(a) >= 1 and max(a) <= 8192
     n_total = sum(n * k for (_, n, k, _) in stack.PROJECTIONS)
     assert n_total == (10240 + 8192 + 57344) * 8192 + 8192 * 28672
+
+
+class _FakeApi:
+    """Stands in for the CUDA library's peer-memory calls: pointers are numbers, handles name their owner."""
+
+    def __init__(self, rank):
+        self.rank, self.next, self.opened, self.closed, self.freed, self.calls = rank, 0, [], [], [], []
+
+    def peer_alloc(self, nbytes):
+        self.next += 1
+        ptr = 1000 * (self.rank + 1) + self.next
+        return ptr, f"h{self.rank}:{ptr}".encode()
+
+    def peer_open(self, handle):
+        owner, ptr = handle.decode()[1:].split(":")
+        self.opened.append(int(ptr))
+        return 500000 + int(ptr)                      # a different address than the owner's: a mapping
+
+    def peer_close(self, ptr):
+        self.closed.append(ptr)
+
+    def peer_free(self, ptr):
+        self.freed.append(ptr)
+
+    def linear_gather(self, x, w, dst, ld, off):
+        self.calls.append(("gather", tuple(dst), ld, off))
+
+    def peer_barrier(self, table, world, rank, value, timeout_us):
+        self.calls.append(("barrier", world, rank, value))
+
+
+def test_peer_output_maps_every_rank_and_orders_destinations(monkeypatch):
+    """Host logic of the fused all-gather buffers for a world of three: handle exchange, own copy first in the
+    destination list, flag table in rank order, growing barrier values, clean-up."""
+    from moonpoly_b200 import shard
+    world = 3
+    apis = [_FakeApi(r) for r in range(world)]
+    handles = []
+    for r in range(world):                            # what each rank would contribute to the exchange
+        a = _FakeApi(r)
+        handles.append((a.peer_alloc(1)[1], a.peer_alloc(1)[1]))
+    outs = []
+    real_tensor = torch.tensor
+    for r in range(world):
+        import moonpoly_b200.api as real_api
+        monkeypatch.setattr(real_api, "peer_alloc", apis[r].peer_alloc)
+        monkeypatch.setattr(real_api, "peer_open", apis[r].peer_open)
+        monkeypatch.setattr(real_api, "peer_close", apis[r].peer_close)
+        monkeypatch.setattr(real_api, "peer_free", apis[r].peer_free)
+        monkeypatch.setattr(real_api, "linear_gather", apis[r].linear_gather)
+        monkeypatch.setattr(real_api, "peer_barrier", apis[r].peer_barrier)
+        monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+        out = shard.PeerOutput(16, 24, r, world, exchange=lambda obj: handles, device=torch.device("cpu"))
+        outs.append(out)
+        own = 1000 * (r + 1) + 1
+        assert out.buf_ptrs[r] == own and out.dst[0] == own and len(out.dst) == world
+        assert sorted(out.dst[1:]) == sorted(500000 + 1000 * (q + 1) + 1 for q in range(world) if q != r)
+        assert out.flag_table.tolist() == [1000 * (q + 1) + 2 if q == r else 500000 + 1000 * (q + 1) + 2 for q in range(world)]
+        layer = shard.ColumnParallelLinear(torch.zeros((8, 4)), 24, r, world, compute=lambda x, w: None)
+        monkeypatch.setattr(out, "tensor", lambda rows: rows)
+        layer.forward_gather_fused(torch.zeros((5, 4)), out)
+        layer.forward_gather_fused(torch.zeros((5, 4)), out)
+        assert [c for c in apis[r].calls if c[0] == "gather"][0][2:] == (24, 8 * r)          # ld = N, offset = r * N / g
+        assert [c[3] for c in apis[r].calls if c[0] == "barrier"] == [1, 2]
+        out.close()
+        assert len(apis[r].closed) == 2 * (world - 1) and sorted(apis[r].freed) == [own, own + 1]
+    assert real_tensor is torch.tensor
