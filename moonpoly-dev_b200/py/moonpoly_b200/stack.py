@@ -80,11 +80,24 @@ def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3
 
     fused = {}
     if do_gather and gather == "fused":
+        # peer-mapped copies of the two gathered outputs; when any rank cannot map its peers (no peer access between
+        # the GPUs, IPC refused) every rank falls back to ncclAllGather together
         from .shard import PeerOutput
-        for j, (_, n, _, g) in enumerate(shard):
-            if g:
-                po = PeerOutput(max_m, n * world, rank, world)
-                fused[j] = (po, (vp * world)(*[vp(int(q)) for q in po.dst]), vp(po.flag_table.data_ptr()))
+        err = ""
+        try:
+            for j, (_, n, _, g) in enumerate(shard):
+                if g:
+                    po = PeerOutput(max_m, n * world, rank, world)
+                    fused[j] = (po, (vp * world)(*[vp(int(q)) for q in po.dst]), vp(po.flag_table.data_ptr()))
+        except Exception as e:       # noqa: BLE001
+            err = str(e)[:120]
+        ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            for po, _, _ in fused.values():
+                po.close()
+            fused = {}
+            gather = "nccl (peer mapping unavailable" + (": " + err if err else " on another rank") + ")"
     epoch = [0]
 
     def step(m: int) -> None:

@@ -10,7 +10,8 @@ order of attempts, the same operator calls.  A layer's forward goes through, in 
                            decode-selector table names for (M, N, K)  (VLLM_USE_MOONPOLY_PID_WHITELIST=1)
   3. the split-K / stream-K pid with a pooled workspace for decode shapes
                            (VLLM_USE_MOONPOLY_STREAMK, default on; pid VLLM_MOONPOLY_STREAMK_PID, default 40)
-  4. `moonpoly_ops.linear`
+  4. `moonpoly_ops.linear` (with a bias: `moonpoly_ops.linear_bias`, which adds it inside the GEMM's epilogue with
+     the same result; VLLM_MOONPOLY_FUSE_BIAS=0 keeps the separate add)
 
 and every attempt that raises or produces a non-finite value falls through to the next one; `None`
 tells the caller to use its own GEMM.  Inputs of any rank are flattened to 2-D and the output is
@@ -165,7 +166,13 @@ def apply_moonpoly_linear(weight: torch.Tensor, x: torch.Tensor, bias: Optional[
             STATS["streamk_skipped"] += 1
     if out is None:
         try:
-            out = ops.linear(x2, w)
+            if bias is not None and _flag("VLLM_MOONPOLY_FUSE_BIAS", "1") and hasattr(ops, "linear_bias") \
+                    and bias.dtype == x2.dtype and bias.numel() == n:
+                # not in the reference: the bias add rides in the GEMM's epilogue (bit-identical to the separate add)
+                out = ops.linear_bias(x2, w, bias)
+                bias = None
+            else:
+                out = ops.linear(x2, w)
             STATS["linear"] += 1
         except Exception:
             STATS["declined"] += 1

@@ -56,6 +56,27 @@ at::Tensor linear_cuda(const at::Tensor& x, const at::Tensor& w) {
   return y;
 }
 
+// Extension beyond the reference's op set: Linear with the bias add fused into the epilogue, fp16 or bf16.
+at::Tensor linear_bias_cuda(const at::Tensor& x, const at::Tensor& w, const std::optional<at::Tensor>& bias) {
+  require(x.is_cuda() && w.is_cuda(), "Tensors must be on CUDA device");
+  require(x.dim() == 2 && w.dim() == 2, "linear_bias: input and weight must be 2D");
+  require(x.size(1) == w.size(1), "linear_bias: weight shape mismatch");
+  require(x.scalar_type() == w.scalar_type(), "linear_bias: input and weight dtypes differ");
+  require(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "linear_bias: fp16 or bf16 only");
+  c10::cuda::CUDAGuard guard(x.device());
+  const at::Tensor xc = x.contiguous(), wc = w.contiguous();
+  at::Tensor bc;
+  if (bias.has_value() && bias->defined()) {
+    require(bias->is_cuda() && bias->scalar_type() == x.scalar_type() && bias->numel() == w.size(0),
+            "linear_bias: bias must be a CUDA tensor of N elements in the input dtype");
+    bc = bias->contiguous();
+  }
+  at::Tensor y = at::empty({x.size(0), w.size(0)}, x.options());
+  check(mp_linear_bias(x.scalar_type() == at::kHalf ? MP_FP16 : MP_BF16, (int)x.size(0), (int)w.size(0), (int)x.size(1),
+                       xc.data_ptr(), wc.data_ptr(), bc.defined() ? bc.data_ptr() : nullptr, y.data_ptr(), stream_of(x)));
+  return y;
+}
+
 // The measured decode plans live inside the online selector of the library, so the C++-selector
 // op is the plain op (non-fp16 / non-2-D / non-contiguous inputs take this route in the reference too).
 at::Tensor linear_cpp_selector_cuda(const at::Tensor& x, const at::Tensor& w) { return linear_cuda(x, w); }
@@ -195,6 +216,9 @@ std::tuple<int, int, int, int> scaled_mm_config(int id) {
 at::Tensor linear_meta(const at::Tensor& x, const at::Tensor& w) {
   return at::empty_symint({x.sym_size(0), w.sym_size(0)}, x.options());
 }
+at::Tensor linear_bias_meta(const at::Tensor& x, const at::Tensor& w, const std::optional<at::Tensor>&) {
+  return at::empty_symint({x.sym_size(0), w.sym_size(0)}, x.options());
+}
 int64_t ws_size_meta(const at::Tensor&, const at::Tensor&, int64_t, int64_t) { return 0; }
 at::Tensor linear_ws_meta(const at::Tensor& x, const at::Tensor& w, int64_t, const at::Tensor&, int64_t) {
   return at::empty_symint({x.sym_size(0), w.sym_size(0)}, x.options());
@@ -206,6 +230,7 @@ void out_meta(const at::Tensor&, const at::Tensor&, at::Tensor&, int64_t, const 
 TORCH_LIBRARY(moonpoly_ops, m) {
   m.def("linear(Tensor input, Tensor weight) -> Tensor");
   m.def("linear_cpp_selector(Tensor input, Tensor weight) -> Tensor");
+  m.def("linear_bias(Tensor input, Tensor weight, Tensor? bias=None) -> Tensor");      // not in the reference's op set
   m.def("fp16_workspace_size(Tensor input, Tensor weight, int pid, int split_k_slices=2) -> int");
   m.def("fp16_rcc_workspace_size(Tensor a, Tensor b_col, int pid, int split_k_slices=2) -> int");
   m.def("linear_fp16_pid_ws(Tensor input, Tensor weight, int pid, Tensor workspace, int split_k_slices=2) -> Tensor");
@@ -216,6 +241,7 @@ TORCH_LIBRARY(moonpoly_ops, m) {
 TORCH_LIBRARY_IMPL(moonpoly_ops, CUDA, m) {
   m.impl("linear", &linear_cuda);
   m.impl("linear_cpp_selector", &linear_cpp_selector_cuda);
+  m.impl("linear_bias", &linear_bias_cuda);
   m.impl("fp16_workspace_size", &fp16_workspace_size);
   m.impl("fp16_rcc_workspace_size", &fp16_rcc_workspace_size);
   m.impl("linear_fp16_pid_ws", &linear_fp16_pid_ws);
@@ -226,6 +252,7 @@ TORCH_LIBRARY_IMPL(moonpoly_ops, CUDA, m) {
 TORCH_LIBRARY_IMPL(moonpoly_ops, Meta, m) {
   m.impl("linear", &linear_meta);
   m.impl("linear_cpp_selector", &linear_meta);
+  m.impl("linear_bias", &linear_bias_meta);
   m.impl("fp16_workspace_size", &ws_size_meta);
   m.impl("fp16_rcc_workspace_size", &ws_size_meta);
   m.impl("linear_fp16_pid_ws", &linear_ws_meta);
@@ -237,6 +264,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "MoonPoly GEMM for B200 (sm_100a): torch binding above the C ABI of libmoonpoly_gemm.so";
   m.def("linear", &linear_cuda, py::arg("A"), py::arg("B"));
   m.def("linear_cpp_selector", &linear_cpp_selector_cuda, py::arg("A"), py::arg("B"));
+  m.def("linear_bias", &linear_bias_cuda, py::arg("A"), py::arg("B"), py::arg("bias") = py::none());
   m.def("linear_cpp_forced_pid", &linear_cpp_forced_pid, py::arg("A"), py::arg("B"), py::arg("pid"), py::arg("split_k"));
   m.def("fp16_workspace_size", &fp16_workspace_size, py::arg("A"), py::arg("B"), py::arg("pid"), py::arg("split_k_slices") = 2);
   m.def("linear_fp16_pid_ws", &linear_fp16_pid_ws, py::arg("A"), py::arg("B"), py::arg("pid"), py::arg("workspace"),

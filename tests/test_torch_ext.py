@@ -28,6 +28,7 @@ def test_schemas_and_meta_kernels(moonpoly):
     ws = torch.empty((0,), dtype=torch.uint8, device="meta")
     assert ops.linear(x, w).shape == (5, 24)
     assert ops.linear_cpp_selector(x, w).shape == (5, 24)
+    assert ops.linear_bias(x, w, None).shape == (5, 24)            # beyond the reference's op set
     assert ops.fp16_workspace_size(x, w, 40) == 0
     assert ops.linear_fp16_pid_ws(x, w, 40, ws).shape == (5, 24)
     out = torch.empty((5, 24), dtype=torch.float16, device="meta")
@@ -147,3 +148,19 @@ def test_scaled_int8_mm_vs_float_reference(moonpoly, M, N, K, out_dtype, mode, w
     # (the product is rounded before the bias is added, so a cancelling bias keeps the product's ulp)
     rtol, atol = (4e-3, 1e-2) if out_dtype == torch.float16 else (3e-2, 6e-2)
     torch.testing.assert_close(out.float(), ref, rtol=rtol, atol=atol)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_linear_bias_op_matches_two_step(moonpoly, dtype):
+    torch.manual_seed(3)
+    x = (torch.randn(33, 1024, device="cuda") * 0.05).to(dtype)
+    w = (torch.randn(520, 1024, device="cuda") * 0.05).to(dtype)
+    b = torch.randn(520, device="cuda").to(dtype)
+    fused = torch.ops.moonpoly_ops.linear_bias(x, w, b)
+    plain = torch.ops.moonpoly_ops.linear_bias(x, w, None)
+    assert torch.equal(fused, plain + b)
+    assert torch.equal(moonpoly.linear_bias(x, w, b), fused)
+    if dtype == torch.float16:
+        assert torch.equal(plain, torch.ops.moonpoly_ops.linear(x, w))
+    torch.testing.assert_close(fused.float(), x.float() @ w.float().t() + b.float(), rtol=2e-2, atol=2e-2)
