@@ -611,9 +611,10 @@ int run_gemv(const Problem& p, cudaStream_t stream) {
 // Streaming warp-MMA path: one side of the problem has at most 64 rows; the other operand is streamed once.
 template <int KIND, int EPI, int NT, int UNROLL, int MINB>
 int launch_stream_t(const StreamParams& sp, int sms, cudaStream_t stream) {
-  // a whole multiple of the SM count when the rows allow it, else one CTA per 8 rows
+  // a whole multiple of the SM count when the rows allow it, else one CTA per 8 rows; with a token split every
+  // block of rows is taken by t_split neighbouring CTAs
   const int per_sm = std::min(MINB, sp.R / (8 * sms));
-  const int grid = per_sm >= 1 ? per_sm * sms : std::max(1, (sp.R + 7) / 8);
+  const int grid = (per_sm >= 1 ? per_sm * sms : std::max(1, (sp.R + 7) / 8)) * std::max(1, sp.t_split);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(kStreamWarps * 32);
@@ -630,11 +631,20 @@ int launch_stream_t(const StreamParams& sp, int sms, cudaStream_t stream) {
 
 template <int KIND, int EPI>
 int launch_stream_nt(const StreamParams& sp, int sms, cudaStream_t stream) {
-  if (sp.T <= 8) return launch_stream_t<KIND, EPI, 1, 8, 2>(sp, sms, stream);
-  if (sp.T <= 16) return launch_stream_t<KIND, EPI, 2, 8, 2>(sp, sms, stream);
-  if (sp.T <= 32) return launch_stream_t<KIND, EPI, 4, 8, 2>(sp, sms, stream);
+  const int rows = sp.t_split > 1 ? sp.t_per : sp.T;       // rows of X one CTA works against
+  if (rows <= 8) return launch_stream_t<KIND, EPI, 1, 8, 2>(sp, sms, stream);
+  if (rows <= 16) return launch_stream_t<KIND, EPI, 2, 8, 2>(sp, sms, stream);
+  if (rows <= 32) return launch_stream_t<KIND, EPI, 4, 8, 2>(sp, sms, stream);
   return launch_stream_t<KIND, EPI, 8, 4, 2>(sp, sms, stream);
 }
+
+// Token split of the streaming kernel (see StreamParams::t_split).  0 = the library's rule below, 1 = off,
+// 2 / 4 / 8 = forced; MOONPOLY_STREAM_TSPLIT overrides the rule the same way.
+int stream_tsplit_from_env() {
+  const char* v = std::getenv("MOONPOLY_STREAM_TSPLIT");
+  return v && v[0] ? std::atoi(v) : 0;
+}
+std::atomic<int> g_stream_tsplit{stream_tsplit_from_env()};
 
 // Cluster-K variant of the streaming kernel: a cluster of `ck` CTAs shares a block of W rows and cuts K.
 // Measured on B200 it loses to the one-CTA-per-row-block kernel on every benchmark shape but one (its tiles run
@@ -715,6 +725,17 @@ int launch_stream_ck_nt(DeviceState& d, int base_slot, const StreamCkParams& cp,
   return launch_stream_ck_t<KIND, EPI, 8, 4>(d, base_slot + 3, cp, stream);
 }
 
+// When to split the tokens.  Measured on B200 (Linear mapping, FP16): with N = K = 4096 the repeated reads of W
+// cost more than the narrower X saves (M = 16: 12.2 us split in two against 8.3 us; M = 32: 15.2 against 11.1),
+// and the same holds for every layer with enough rows to give each SM a CTA.  The split pays only when the rows are
+// too few to fill the GPU (N = 1024, K = 8192: M = 16 10.0 -> 8.0 us, M = 32 14.7 -> 10.6 us), where it doubles the
+// number of CTAs: two parts when one CTA per 8 rows leaves SMs idle and there are more than 8 rows of X.
+int stream_tsplit_rule(int R, int T, int K, int elt) {
+  (void)K; (void)elt;
+  const int sms = mp::num_sms_for_model();
+  return (T > 8 && (R + 7) / 8 < sms) ? 2 : 1;
+}
+
 bool stream_compatible(const Problem& p) {
   if (!(p.dtype == MP_FP16 && p.epi == EPI_F16) && p.dtype != MP_INT8) return false;
   return std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 16 &&
@@ -724,7 +745,7 @@ bool stream_compatible(const Problem& p) {
 
 // forced_ck: 0 = the library decides between the two streaming kernels; > 0 = the cluster-K kernel with that
 // many K ranges (1, 2, 4 or 8); < 0 = the one-CTA-per-row-block kernel.
-int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0) {
+int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int forced_tsplit = 0) {
   DeviceState* d = nullptr;
   if (int rc = device_state(&d)) return rc;
   StreamParams sp{};
@@ -763,6 +784,17 @@ int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0) {
       if (p.epi == EPI_I32) return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_I32>(*d, 4, cp, stream);
       return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_SCALED>(*d, 8, cp, stream);
     }
+  }
+  // token split: parts of 8 or 16 rows of X per CTA, never an empty part
+  {
+    int ts = forced_tsplit > 0 ? forced_tsplit : g_stream_tsplit.load(std::memory_order_relaxed);
+    if (ts == 0) ts = stream_tsplit_rule(sp.R, sp.T, sp.K, elem_bytes(p.dtype));
+    ts = std::max(1, std::min(ts, (sp.T + 7) / 8));
+    if (ts > 1) {
+      sp.t_per = ((sp.T + ts - 1) / ts + 7) / 8 * 8;
+      ts = (sp.T + sp.t_per - 1) / sp.t_per;
+    }
+    sp.t_split = ts;
   }
   if (p.dtype == MP_FP16 && p.bf16) return launch_stream_nt<STREAM_BF16, STREAM_EPI_F16>(sp, d->sms, stream);
   if (p.dtype == MP_FP16) return launch_stream_nt<STREAM_F16, STREAM_EPI_F16>(sp, d->sms, stream);
@@ -937,6 +969,7 @@ int mp_reload_env(void) {
   g_use_streamk.store(streamk_from_env(), std::memory_order_relaxed);
   g_use_cluster_splitk.store(cluster_splitk_from_env(), std::memory_order_relaxed);
   g_use_stream_cluster.store(stream_cluster_from_env(), std::memory_order_relaxed);
+  g_stream_tsplit.store(stream_tsplit_from_env(), std::memory_order_relaxed);
   return MP_OK;
 }
 
@@ -1047,7 +1080,7 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
     if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16 or INT8, min(m,n) <= 64 and 16-byte aligned rows");
     if (kc != 0 && kc != 1 && kc != 2 && kc != 4 && kc != 8 && kc != -1)
       return fail(MP_ERR_INVALID_ARG, "streaming kernel: kc selects the K ranges of the cluster variant (1, 2, 4, 8), -1 the plain kernel, 0 lets the library choose");
-    return run_stream(pg, reinterpret_cast<cudaStream_t>(stream), kc);
+    return run_stream(pg, reinterpret_cast<cudaStream_t>(stream), kc, split_k > 1 ? split_k : 0);
   }
   const int xm = (orient == 4 || orient == 5) ? 2 : 1;       // orient 4 / 5: orient 0 / 1 with 256-row tiles
   if (xm == 2) orient -= 4;

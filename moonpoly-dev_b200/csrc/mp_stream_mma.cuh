@@ -38,6 +38,10 @@ struct StreamParams {
   const float* chan_scale; const float* tok_scale;
   int chan_scalar, tok_scalar, chan_on_r, out_bf16;
   const void* bias;                    // in the output type, indexed by channel; may be null
+  // Token split: t_split > 1 gives every block of W rows to t_split neighbouring CTAs, each against its own
+  // t_per rows of X (a multiple of 8).  W is then read t_split times, but the repeats hit L2 (neighbouring CTAs
+  // run together), HBM still sees it once, and every CTA keeps a narrow X that stays in L1.
+  int t_split, t_per;
   // fused all-gather of a column-parallel Linear: the same output buffer in the memory of the other GPUs
   // (peer-mapped pointers, same strides); every result is stored there too with plain stores
   void* peer_out[7];
@@ -130,11 +134,15 @@ stream_mma_kernel(const StreamParams p) {
   constexpr int kChunkElems = 16 / kElt;                   // elements per 16-byte chunk
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
-  const int r_begin = (int)((long long)blockIdx.x * p.R / gridDim.x);
-  const int r_end = (int)((long long)(blockIdx.x + 1) * p.R / gridDim.x);
+  const int t_split = p.t_split > 1 ? p.t_split : 1;
+  const int rb = (int)blockIdx.x / t_split, nrb = (int)gridDim.x / t_split;
+  const int t0 = ((int)blockIdx.x - rb * t_split) * p.t_per;          // first row of X of this CTA
+  const int Tl = t_split > 1 ? min(p.t_per, p.T - t0) : p.T;          // rows of X of this CTA
+  const int r_begin = (int)((long long)rb * p.R / nrb);
+  const int r_end = (int)((long long)(rb + 1) * p.R / nrb);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const char* Wb = reinterpret_cast<const char*>(p.W);
-  const char* Xb = reinterpret_cast<const char*>(p.X);
+  const char* Xb = reinterpret_cast<const char*>(p.X) + (long long)t0 * p.ldx * (KIND == STREAM_I8 ? 1 : 2);
 
   // Before the previous kernel of the stream is complete nothing may be read for real, but pulling
   // this CTA's rows of W towards L2 is harmless and joins back-to-back launches into one stream.
@@ -158,7 +166,7 @@ stream_mma_kernel(const StreamParams p) {
   bool x_ok[NT];
 #pragma unroll
   for (int nb = 0; nb < NT; ++nb) {
-    x_ok[nb] = nb * 8 + g < p.T;
+    x_ok[nb] = nb * 8 + g < Tl;
     xr[nb] = reinterpret_cast<const uint4*>(Xb + (long long)(nb * 8 + g) * p.ldx * kElt);
   }
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -221,10 +229,10 @@ stream_mma_kernel(const StreamParams p) {
     __syncthreads();
 
     // the faster-moving index of the output walks whichever of (row, narrow row) is contiguous
-    for (int i = threadIdx.x; i < kStreamRows * p.T; i += kStreamWarps * 32) {
+    for (int i = threadIdx.x; i < kStreamRows * Tl; i += kStreamWarps * 32) {
       int r, t;
       if (rows_contig) { r = i & (kStreamRows - 1); t = i >> 4; }
-      else { t = i % p.T; r = i / p.T; }
+      else { t = i % Tl; r = i / Tl; }
       if (row0 + r >= r_end) continue;
       uint32_t accw;
       if constexpr (KIND == STREAM_I8) {
@@ -238,7 +246,7 @@ stream_mma_kernel(const StreamParams p) {
         for (int w = 0; w < kStreamWarps; ++w) v += __uint_as_float(red[w][r][t]);
         accw = __float_as_uint(v);
       }
-      stream_finish<EPI>(p, accw, row0 + r, t);
+      stream_finish<EPI>(p, accw, row0 + r, t0 + t);
     }
   }
 }

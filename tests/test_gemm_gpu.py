@@ -838,3 +838,50 @@ def test_bf16_linear_exact_on_integers(api):
     y = api.linear(dev(x).to(torch.bfloat16), dev(w).to(torch.bfloat16))
     assert y.dtype == torch.bfloat16
     assert np.array_equal(y.float().cpu().numpy(), ref.astype(np.float32))
+
+
+# ------------------------------------------------------------------ token split of the streaming kernel
+@pytest.mark.parametrize("m,n,k,parts", [(16, 4096, 4096, 2), (32, 4096, 4096, 2), (32, 4096, 4096, 4), (64, 2048, 4096, 4),
+                                          (64, 1024, 2048, 8), (17, 1000, 1024, 2), (17, 1000, 1024, 4), (40, 513, 2056, 2),
+                                          (4096, 24, 4096, 2), (700, 33, 2048, 4), (9, 64, 8192, 2), (8, 300, 512, 4)])
+def test_fp16_streaming_kernel_token_split(api, oracle, m, n, k, parts):
+    """Every block of streamed rows is shared by `parts` neighbouring CTAs, each against its own rows of the narrow
+    operand: the same dot products, so the result equals the unsplit kernel's bit for bit; both mappings, ragged
+    parts, parts that would be empty are dropped, alpha / beta."""
+    a = rng.normal(200, 0, (m, k), 0.05)
+    b = rng.normal(200, 1, (n, k), 0.05)
+    c0 = rng.normal(200, 2, (n, m), 1.0)
+    A, B = dev(a), dev(b)
+    plain = api.gemm_rcc_tile(A, B, 3, 16, kc=-1, split_k=1).cpu().numpy()
+    split = api.gemm_rcc_tile(A, B, 3, 16, kc=-1, split_k=parts).cpu().numpy()
+    assert np.array_equal(split, plain)
+    close_f16(split, oracle.gemm_f16_rcc(a, b))
+    ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
+    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=-1, split_k=parts, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
+    assert api.device_status() == 0
+
+
+def test_int8_scaled_streaming_kernel_token_split(api, oracle, monkeypatch):
+    M, N, K = 40, 600, 4096
+    a = rng.int8_uniform(201, 0, (M, K))
+    b = rng.int8_uniform(201, 1, (N, K))
+    sa = rng.uniform(201, 2, (M,), 0.001, 0.02)
+    sb = rng.uniform(201, 3, (N,), 0.001, 0.02)
+    bias = rng.uniform(201, 4, (N,), -1.0, 1.0).astype(np.float16)
+    ref = oracle.scaled_mm_i8(a, b, sa, sb, bias)
+    L = api.lib()
+    A, B, SA, SB, BI = dev(a), dev(b), dev(sa), dev(sb), dev(bias)
+    for parts in ("1", "2", "4"):
+        monkeypatch.setenv("MOONPOLY_STREAM_TSPLIT", parts)
+        api.reload_env()
+        out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+        rc = L.mp_scaled_mm_i8_tile(3, 16, 1, M, N, K, A.data_ptr(), K, B.data_ptr(), K, SA.data_ptr(), 0, SB.data_ptr(), 0,
+                                    BI.data_ptr(), out.data_ptr(), N, 0, None)
+        assert rc == 0, L.mp_last_error_string()
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16)), parts
+        acc = api.gemm_rcc_pid(A, B, 1101, 1).cpu().numpy()
+        assert np.array_equal(acc, oracle.gemm_i8_rcc(a, b)), parts
+    monkeypatch.delenv("MOONPOLY_STREAM_TSPLIT")
+    api.reload_env()
+    assert api.device_status() == 0
