@@ -6,8 +6,11 @@
 A step is one pass over the sweep M in {1,2,4,8,16,32,64,127,128,255,512,1023,2048,4096}: every
 shape is launched `reps(M)` times back to back through the C ABI's online-selector entry
 (mp_gemm), rotating through 8 resident copies of the 32 MiB weight matrix (256 MiB > L2) so the
-weight stream comes from HBM.  Per-shape device time comes from CUDA events on the launching
-stream; `value` is the geometric mean over the sweep of 2*M*N*K / time, in TFLOP/s.  With N > 1
+weight stream comes from HBM.  By default those launches are captured once per shape in a CUDA graph
+(after the warm-up, through the same mp_gemm calls) and the timed steps replay the graphs, the way a
+serving engine's decode loop runs; `--launch stream` times one host call per GEMM instead, and the
+other mode is reported beside it (`roofline.stream_launch` / `roofline.cuda_graph_replay`).
+Per-shape device time comes from CUDA events on the launching stream; `value` is the geometric mean over the sweep of 2*M*N*K / time, in TFLOP/s.  With N > 1
 GPUs (torchrun, one rank per GPU) every rank owns its own 4096-column shard of a 4096*N wide
 weight (column-parallel, no data-path collective: weak scaling); per-shape time is the max over
 ranks and `value` counts the FLOPs of all ranks.
@@ -111,8 +114,10 @@ def cpu_inputs_sampled(m_list, seed=1):
     return a, b
 
 
-def sweep_config(world):
+def sweep_config(world, launch="graph"):
     return {"workload": WORKLOAD, "sweep_m": SWEEP_M, "n": N_DIM, "k": K_DIM,
+            "launch": ("per shape, the step's launches captured once in a CUDA graph and replayed" if launch == "graph"
+                       else "one host call per GEMM on the stream"),
             "reps_per_shape": {str(m): reps_for(m) for m in SWEEP_M},
             "l2": f"inputs larger than L2: {WEIGHT_COPIES} rotating copies of the 32 MiB weight (256 MiB)",
             "entry": "mp_gemm (online selector)", "parallelism": f"column-parallel x{world}, no collective"}
@@ -142,7 +147,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": sweep_config(world),
+        "config": sweep_config(world, args.launch),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
                          "per_shape_tflops": {str(m): round(per_tfl[m], 5) for m in SWEEP_M}},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -303,15 +308,19 @@ def extra_sections(api, L, st, dev, peaks):
     b32 = [torch.from_numpy(rng.uniform(0, rng.STREAM_B, (1024, 1024), -1.0, 1.0)).to(dev) for _ in range(2)]
     c32 = torch.empty((1024, 37), dtype=torch.float32, device=dev)
 
+    args32 = [(api.MP_FP32, 37, 1024, 1024, vp(a32.data_ptr()), 0, vp(b32[j].data_ptr()), 1, vp(c32.data_ptr()), 1,
+               ctypes.c_float(1.0), ctypes.c_float(0.0), st) for j in range(2)]
+
     def call32(i):
-        rc = L.mp_gemm(api.MP_FP32, 37, 1024, 1024, vp(a32.data_ptr()), 0, vp(b32[i & 1].data_ptr()), 1, vp(c32.data_ptr()), 1,
-                       1.0, 0.0, st)
+        rc = L.mp_gemm(*args32[i & 1])
         assert rc == 0, L.mp_last_error_string()
-    t32 = ev_time(call32, 50)
+    for i in range(4):
+        call32(i)
+    t32 = min(ev_time(call32, 100) for _ in range(3))
     b32_bytes = 4.0 * (37 * 1024 + 1024 * 1024 + 37 * 1024)
     out["fp32_m37"] = {"us": round(t32 * 1e6, 2), "gflops": round(2.0 * 37 * 1024 * 1024 / t32 / 1e9, 1),
                        "hbm_roofline_frac": round(b32_bytes / (peaks["hbm_gbs"] * 1e9) / t32, 4),
-                       "note": "4.5 MB problem: the HBM roofline is 0.7 us, below the launch-to-launch floor of any kernel",
+                       "note": "mp_gemm on the stream, 100 back-to-back calls, best of 3; 4.5 MB problem: the HBM roofline is 0.7 us, below the launch-to-launch floor of any kernel",
                        "plan": repr(api.select_plan(api.MP_FP32, 37, 1024, 1024))}
     # ---- host cost of a selection (mp_select_plan through ctypes; the empty-call cost of ctypes is measured with
     # mp_num_sms and subtracted): warm = the same shape again (plan cache hit), cold = shapes never seen before
@@ -392,6 +401,48 @@ def run_ours(args, rank, world, local_rank):
             if events is not None:
                 events[m][1].record(stream)
 
+    # The timed sweep replays CUDA graphs (what a serving engine's decode loop does): per shape, the launches of one
+    # step -- the same mp_gemm calls as sweep_device, weight copies rotating through all of them in replay order --
+    # are captured once after the warm-up and replayed every step between that shape's events.
+    graphs = {}
+    graph_launches = {}
+
+    def capture_graphs():
+        side = torch.cuda.Stream(device=dev)
+        side_st = ctypes.c_void_p(side.cuda_stream)
+        seq = 0
+        for m in SWEEP_M:
+            calls = []
+            for i in range(reps_for(m)):
+                calls.append((api.MP_FP16, m, N_DIM, K_DIM, ctypes.c_void_p(a_dev[m][i & 1].data_ptr()), 0,
+                              ctypes.c_void_p(weights[seq % WEIGHT_COPIES].data_ptr()), 1, ctypes.c_void_p(c_dev[m].data_ptr()), 1,
+                              ctypes.c_float(1.0), ctypes.c_float(0.0), side_st))
+                seq += 1
+
+            def launch_all():
+                for args_ in calls:
+                    if mp_gemm(*args_) != 0:
+                        raise RuntimeError(L.mp_last_error_string().decode())
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                launch_all()                       # scratch buffers and plans exist before the capture starts
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = api.launch_count()
+            with torch.cuda.graph(g, stream=side):
+                launch_all()
+            graph_launches[m] = api.launch_count() - n0
+            graphs[m] = g
+        torch.cuda.synchronize()
+
+    def sweep_graph(events):
+        for m in SWEEP_M:
+            if events is not None:
+                events[m][0].record(stream)
+            graphs[m].replay()
+            if events is not None:
+                events[m][1].record(stream)
+
     # e2e leg: activations come from pinned host memory and the result goes back to pinned host memory inside the
     # timed region.  Small problems run copy -> GEMM -> copy on one stream (the copies are a few microseconds and the
     # host calls dominate); from PIPELINE_MIN_M rows on, two staging slots and two copy streams overlap the upload
@@ -466,16 +517,25 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    use_graph = args.launch == "graph"
     for _ in range(max(3, args.warmup)):
         sweep_device(None)
     sweep_e2e(None)
+    capture_graphs()
+    sweep_main = sweep_graph if use_graph else sweep_device
+    for _ in range(max(3, args.warmup)):
+        sweep_main(None)
     t_load = time.perf_counter()
     while time.perf_counter() - t_load < 0.6:
-        sweep_device(None)
+        sweep_main(None)
         torch.cuda.synchronize()
     barrier()
-    total_ms, per_ms, launches = timed(sweep_device, args.steps)
+    total_ms, per_ms, launches = timed(sweep_main, args.steps)
+    if use_graph:
+        launches = args.steps * sum(graph_launches.values())
     clocks = sampler.stop() if rank == 0 else None
+    # the same sweep with one host call per GEMM (stream launches, online selector every call), a few steps
+    _, other_per_ms, _ = timed(sweep_device if use_graph else sweep_graph, max(3, args.steps // 5))      # this rank's
     e2e_total_ms, e2e_per_ms, _ = timed(sweep_e2e, max(1, args.steps // 2))
     code = api.device_status()
     assert code == 0
@@ -534,40 +594,12 @@ def run_ours(args, rank, world, local_rank):
         extras = {}
         if not args.no_extras:
             extras = extra_sections(api, L, st, dev, peaks)
-            # the same sweep replayed from a CUDA graph (what a serving engine's decode loop does): per shape, the
-            # launches of one step are captured once and replayed; host launch cost drops out
-            side = torch.cuda.Stream(device=dev)
-            side_st = ctypes.c_void_p(side.cuda_stream)
-            graph_tfl = []
-            for m in SWEEP_M:
-                r = reps_for(m)
-
-                def launch_all():
-                    for i in range(r):
-                        rc = mp_gemm(api.MP_FP16, m, N_DIM, K_DIM, ctypes.c_void_p(a_dev[m][i & 1].data_ptr()), 0,
-                                     ctypes.c_void_p(weights[i % WEIGHT_COPIES].data_ptr()), 1,
-                                     ctypes.c_void_p(c_dev[m].data_ptr()), 1, ctypes.c_float(1.0), ctypes.c_float(0.0), side_st)
-                        if rc != 0:
-                            raise RuntimeError(L.mp_last_error_string().decode())
-                side.wait_stream(stream)
-                with torch.cuda.stream(side):
-                    launch_all()
-                torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    launch_all()
-                g.replay()
-                torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(3):
-                    g.replay()
-                e1.record()
-                torch.cuda.synchronize()
-                graph_tfl.append(flops(m) / (e0.elapsed_time(e1) / (3 * r) * 1e-3) / 1e12)
-            extras["cuda_graph_replay"] = {"value": geomean(graph_tfl), "unit": "TFLOP/s",
-                                           "per_shape_us": {str(m): round(flops(m) / (t * 1e12) * 1e6, 2)
-                                                            for m, t in zip(SWEEP_M, graph_tfl)}}
+        other_key = "stream_launch" if use_graph else "cuda_graph_replay"
+        extras[other_key] = {"value": world * geomean([flops(m) / (other_per_ms[m] / reps_for(m) * 1e-3) / 1e12 for m in SWEEP_M]),
+                             "unit": "TFLOP/s",
+                             "per_shape_us": {str(m): round(other_per_ms[m] / reps_for(m) * 1e3, 2) for m in SWEEP_M},
+                             "note": ("rank 0's time; one mp_gemm host call per GEMM on the stream (online selector every call)"
+                                      if use_graph else "rank 0's time; the sweep replayed from CUDA graphs")}
         sweep_frac = geomean([p["frac"] for p in per_shape])
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                     "frac": achieved / peaks["tflops"], "traffic": traffic,
@@ -576,7 +608,7 @@ def run_ours(args, rank, world, local_rank):
                     "sweep_geomean_frac_nominal": round(geomean([p["frac_nominal"] for p in per_shape]), 4),
                     "per_shape_frac": {str(p["M"]): p["frac"] for p in per_shape},
                     "per_shape_us": {str(p["M"]): p["us"] for p in per_shape}}
-        for key in ("int8_scaled_mm", "fp16_splitk_decode", "fp32_m37", "selector_host_us", "cuda_graph_replay"):
+        for key in ("int8_scaled_mm", "fp16_splitk_decode", "fp32_m37", "selector_host_us", "cuda_graph_replay", "stream_launch"):
             if key in extras:
                 roofline[key] = extras.pop(key)
         if stack_line is not None:
@@ -585,7 +617,7 @@ def run_ours(args, rank, world, local_rank):
             roofline["stack"]["config"] = {k: stack_line["config"][k] for k in ("layers", "resident_layers", "gather", "parallelism")}
         if stack_nccl is not None:
             roofline["stack_nccl_allgather"] = {k: stack_nccl[k] for k in ("value", "ms_per_step", "roofline_frac", "decode", "prefill")}
-        cfg = sweep_config(world)
+        cfg = sweep_config(world, args.launch)
         line = {
             "metric": METRIC, "value": geomean([tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps,
@@ -656,6 +688,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--launch", default="graph", choices=["graph", "stream"],
+                    help="timed sweep: CUDA graphs replayed (default) or one host call per GEMM")
     ap.add_argument("--cpu-budget", type=float, default=15.0, dest="cpu_budget")
     ap.add_argument("--no-extras", action="store_true", dest="no_extras",
                     help="skip the INT8 scaled_mm and FP16 split-K side tables")

@@ -76,7 +76,7 @@ struct DeviceState {
   int sms = 0;
   int cc = 0;
   bool attrs[9] = {false, false, false, false, false, false, false, false, false};
-  bool skinny_attrs[2] = {false, false};
+  bool tile_f32_attrs[12] = {};
   bool stream_attrs[16] = {false, false, false, false, false, false, false, false, false, false, false, false,
                            false, false, false, false};
 };
@@ -819,20 +819,70 @@ int launch_skinny_f32(const SkinnyF32Params& sp, cudaStream_t stream) {
   return MP_OK;
 }
 
-template <int TMAX, int ROWS>
-int launch_skinny_f32_smem(DeviceState& d, int slot, const SkinnyF32Params& sp, cudaStream_t stream) {
-  auto kern = skinny_f32_smem_kernel<TMAX, ROWS>;
-  if (!d.skinny_attrs[slot]) {
-    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
-    d.skinny_attrs[slot] = true;
+template <int RH, int RI, int TJ>
+int launch_tile_f32(DeviceState& d, int slot, const SkinnyF32Params& sp, int ks, cudaStream_t stream) {
+  auto kern = tile_f32_kernel<RH, RI, TJ>;
+  constexpr int smem = tile_f32_smem_bytes<RH, RI, TJ>();
+  static_assert(smem <= kSmemBudget, "ring too large");
+  if (!d.tile_f32_attrs[slot]) {
+    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    d.tile_f32_attrs[slot] = true;
   }
-  const size_t smem = (size_t)sp.T * sp.K * 4;
-  const int rows_per_pass = kSkinnySmemWarps * ROWS;
-  const int grid = std::max(1, std::min(d.sms, (sp.R + rows_per_pass - 1) / rows_per_pass));
-  kern<<<grid, kSkinnySmemWarps * 32, smem, stream>>>(sp);
-  MP_CUDA_TRY(cudaGetLastError());
+  constexpr int rows = RH * 4 * RI;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((sp.R + rows - 1) / rows), (unsigned)ks, 1);
+  cfg.blockDim = dim3(kTileF32Threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (ks > 1) {                    // the K parts of a row block form one cluster
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = (unsigned)ks;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, sp));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
+}
+
+template <int RH, int RI>
+int launch_tile_f32_t(DeviceState& d, const SkinnyF32Params& sp, int ks, cudaStream_t stream) {
+  constexpr int base = RH == 2 ? 8 : (RI == 4 ? 4 : 0);
+  if (sp.T <= 16) return launch_tile_f32<RH, RI, 2>(d, base + 0, sp, ks, stream);
+  if (sp.T <= 24) return launch_tile_f32<RH, RI, 3>(d, base + 1, sp, ks, stream);
+  if (sp.T <= 40) return launch_tile_f32<RH, RI, 5>(d, base + 2, sp, ks, stream);
+  return launch_tile_f32<RH, RI, 8>(d, base + 3, sp, ks, stream);
+}
+
+// Shape of the FP32 tile launch: 32 rows per CTA (the squarest tile against up to 64 narrow rows keeps the bytes
+// an SM pulls from L2 per FMA lowest) and as many K parts per cluster (a power of two, at most 8, at least one
+// 128-float chunk each) as keep the grid within one wave.  Measured on 37 x 1024 x 1024: 32 rows x 4 parts 6.4 us,
+// 16 x 2 7.7 us, 8 x 1 9.8 us, one warp per row pair 33 us.  MOONPOLY_F32_TILE="rows,parts" (rows 8, 16 or 32)
+// overrides the shape for experiments.
+void tile_f32_rule(const SkinnyF32Params& sp, int sms, int* rows, int* ks) {
+  static const char* env = std::getenv("MOONPOLY_F32_TILE");
+  const int chunks = (sp.K + kTileF32KC - 1) / kTileF32KC;
+  int r = 32, k = 1;
+  if (env && std::sscanf(env, "%d,%d", &r, &k) >= 1 && (r == 8 || r == 16 || r == 32)) {
+    k = std::max(1, std::min(k, 8));
+  } else {
+    r = 32;
+    const int blocks = (sp.R + r - 1) / r;
+    k = 1;
+    while (k < 8 && blocks * k * 2 <= sms) k *= 2;
+  }
+  *rows = r;
+  *ks = std::max(1, std::min(k, chunks));
 }
 
 int run_skinny_f32(const Problem& p, cudaStream_t stream) {
@@ -851,17 +901,15 @@ int run_skinny_f32(const Problem& p, cudaStream_t stream) {
   sp.stride_r = narrow_is_a ? p.c_stride_n : p.c_stride_m;
   sp.stride_t = narrow_is_a ? p.c_stride_m : p.c_stride_n;
   sp.alpha = p.alpha; sp.beta = p.beta;
-  // X small enough for shared memory and wide enough that re-reading it through L1 hurts: the staged kernel
-  if (sp.T > 8 && sp.T <= 40 && (size_t)sp.T * sp.K * 4 <= 200u * 1024u && sp.R >= 64) {
-    if (sp.T <= 16) return launch_skinny_f32_smem<16, 2>(*d, 0, sp, stream);
-    return launch_skinny_f32_smem<40, 2>(*d, 1, sp, stream);
+  if (sp.T > 8) {
+    int rows = 32, ks = 1;
+    tile_f32_rule(sp, d->sms, &rows, &ks);
+    return rows == 32 ? launch_tile_f32_t<2, 4>(*d, sp, ks, stream)
+         : rows == 16 ? launch_tile_f32_t<1, 4>(*d, sp, ks, stream) : launch_tile_f32_t<1, 2>(*d, sp, ks, stream);
   }
   // two rows per warp halve the re-reads of X as long as there are rows enough to fill the GPU
   const bool two = sp.R >= 4 * kSkinnyF32Warps * d->sms;
-  if (sp.T <= 8) return two ? launch_skinny_f32<8, 2>(sp, stream) : launch_skinny_f32<8, 1>(sp, stream);
-  if (sp.T <= 16) return two ? launch_skinny_f32<16, 2>(sp, stream) : launch_skinny_f32<16, 1>(sp, stream);
-  if (sp.T <= 40) return two ? launch_skinny_f32<40, 2>(sp, stream) : launch_skinny_f32<40, 1>(sp, stream);
-  return launch_skinny_f32<64, 1>(sp, stream);
+  return two ? launch_skinny_f32<8, 2>(sp, stream) : launch_skinny_f32<8, 1>(sp, stream);
 }
 
 int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {

@@ -179,7 +179,7 @@ simt_splitk_reduce_kernel(const SimtParams p) {
 }  // namespace mp
 
 // ------------------------------------------------------------------------------------------------
-// FP32 streaming kernel for a narrow side of at most 64 rows: one warp per ROWS rows of the wide
+// FP32 streaming kernel for a narrow side of at most 8 rows: one warp per ROWS rows of the wide
 // operand W[R,K]; the lanes read the rows once with 16-byte loads and keep one accumulator per
 // (row, narrow row), the rows of X[T,K] come from L1/L2 (each X vector serves ROWS rows), and the
 // 32 partial sums of each output meet in a shuffle tree.  A small FP32 problem (37 x 1024 x 1024)
@@ -254,80 +254,164 @@ skinny_f32_kernel(const SkinnyF32Params p) {
   }
 }
 
-// The same computation with the narrow operand staged in shared memory: when X[T,K] fits (T * K * 4 bytes <= 200 KB,
-// e.g. 37 x 1024), one CTA of 16 warps per SM copies it in once and its warps then take ROWS rows of W at a time,
-// reading W straight from global memory and X from shared memory.  The plain kernel above pulls X through L1 once
-// per warp; its rows lie 4 KB apart, the loads of one K chunk fall into few cache sets and most of them miss, so the
-// 37 x 1024 x 1024 problem moved ~150 MB from L2 (27 us).  Staged, X crosses L2 once per SM.
-constexpr int kSkinnySmemWarps = 16;
+// ------------------------------------------------------------------------------------------------
+// FP32 tile kernel for a narrow side of 9..64 rows and a wide side too short to fill the GPU with one warp per row
+// pair (37 x 1024 x 1024).  What bounds such a problem is the rate at which one SM pulls operands out of L2 (about
+// 100 GB/s), so a CTA takes a tile that is as square as the shape allows -- RH*4*RI rows of W against all T rows of
+// X -- over one K part, and the K parts of a row block are the CTAs of one cluster (cluster dims (1, gridDim.y, 1)).
+// Operands arrive in K chunks of 128 floats through a four-slot cp.async ring (coalesced 16-byte copies, zero-filled
+// past the edges), so a CTA with at most four chunks has all of its input in flight at once.  Inside a chunk the
+// eight warps form RH row halves x 8/RH K lanes; the lanes of a warp form a 4 x 8 grid over (rows, narrow rows) with
+// an RI x TJ register tile each, accumulated with packed FP32 FMAs (even and odd k in the two halves of a pair), so
+// one 16-byte shared-memory read feeds 2*TJ (W) or 2*RI (X) packed FMAs.  The pitch of 132 floats puts the eight X
+// rows of a quarter-warp on different banks; the W address is the same across a quarter-warp (broadcast).  The
+// K lanes' partial sums meet in shared memory in lane order; with gridDim.y > 1 every CTA leaves its sums in its own
+// shared memory and each rank adds its share of the outputs over the ranks, in rank order, through distributed
+// shared memory -- the result does not depend on timing.
+// ------------------------------------------------------------------------------------------------
+constexpr int kTileF32Threads = 256;
+constexpr int kTileF32KC = 128;
+constexpr int kTileF32Pitch = kTileF32KC + 4;
+constexpr int kTileF32Stages = 4;
 
-template <int TMAX, int ROWS>
-__global__ void __launch_bounds__(kSkinnySmemWarps * 32, 1)
-skinny_f32_smem_kernel(const SkinnyF32Params p) {
-  extern __shared__ __align__(16) float xs_f32[];          // [T][K]
+__device__ __forceinline__ void f32t_cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;          // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void f32t_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void f32t_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ float f32t_ld_cluster(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ void f32t_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int RH, int RI, int TJ>
+constexpr int tile_f32_smem_bytes() { return kTileF32Stages * (RH * 4 * RI + 8 * TJ) * kTileF32Pitch * 4; }
+
+template <int RH, int RI, int TJ>
+__global__ void __launch_bounds__(kTileF32Threads)
+tile_f32_kernel(const SkinnyF32Params p) {
+  extern __shared__ __align__(16) float tf_smem[];
+  constexpr int KC = kTileF32KC, PITCH = kTileF32Pitch, NS = kTileF32Stages;
+  constexpr int KW = 8 / RH;                                  // K lanes (warps) per row half
+  constexpr int ROWS = RH * 4 * RI, TT = 8 * TJ, LINES = ROWS + TT, STAGE = LINES * PITCH, OUTS = ROWS * TT;
+  static_assert((KW + 1) * OUTS <= NS * STAGE, "the reduction area reuses the staging ring");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int chunks = p.K >> 2;
-  // rows of this CTA: a contiguous, balanced range
-  const int r_begin = (int)((long long)blockIdx.x * p.R / gridDim.x);
-  const int r_end = (int)((long long)(blockIdx.x + 1) * p.R / gridDim.x);
-  {
-    float4* dst = reinterpret_cast<float4*>(xs_f32);
-    for (int i = threadIdx.x; i < p.T * chunks; i += kSkinnySmemWarps * 32) {
-      const int t = i / chunks, c = i - t * chunks;
-      dst[i] = __ldg(reinterpret_cast<const float4*>(p.X + (long long)t * p.ldx) + c);
+  const int rg = lane >> 3, tg = lane & 7;
+  const int half = warp / KW, kw = warp % KW;
+  const int r_base = blockIdx.x * ROWS;
+  const int ks = (int)gridDim.y, rank = (int)blockIdx.y;
+  const int chunks_total = (p.K + KC - 1) / KC;
+  const int c_begin = (int)((long long)rank * chunks_total / ks);
+  const int n_chunks = (int)((long long)(rank + 1) * chunks_total / ks) - c_begin;
+
+  // one warp copies one 512-byte line piece per instruction
+  auto stage = [&](int ci, int slot) {
+    const int k = (c_begin + ci) * KC + lane * 4;
+    const bool k_ok = k < p.K;
+    float* base = tf_smem + slot * STAGE + lane * 4;
+    for (int line = warp; line < LINES; line += kTileF32Threads / 32) {
+      const float* src;
+      bool valid;
+      if (line < ROWS) {
+        const int r = r_base + line;
+        valid = k_ok && r < p.R;
+        src = p.W + (valid ? (long long)r * p.ldw + k : 0);
+      } else {
+        const int t = line - ROWS;
+        valid = k_ok && t < p.T;
+        src = p.X + (valid ? (long long)t * p.ldx + k : 0);
+      }
+      f32t_cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(base + line * PITCH)), src, valid);
+    }
+  };
+
+  float2 acc[RI][TJ];
+#pragma unroll
+  for (int i = 0; i < RI; ++i)
+#pragma unroll
+    for (int j = 0; j < TJ; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
+
+  asm volatile("griddepcontrol.wait;" ::: "memory");          // the previous kernel of the stream may produce W or X
+#pragma unroll
+  for (int s = 0; s < NS - 1; ++s) {
+    if (s < n_chunks) stage(s, s);
+    f32t_cp_async_commit();
+  }
+  for (int c = 0; c < n_chunks; ++c) {
+    f32t_cp_async_wait<NS - 2>();          // chunk c has landed (this thread's copies) ...
+    __syncthreads();                       // ... everyone's; and everyone is done with the slot refilled below
+    if (c + NS - 1 < n_chunks) stage(c + NS - 1, (c + NS - 1) % NS);
+    f32t_cp_async_commit();
+    const float* wb = tf_smem + (c % NS) * STAGE + (half * 4 * RI + rg) * PITCH;
+    const float* xb = tf_smem + (c % NS) * STAGE + (ROWS + tg) * PITCH;
+#pragma unroll 2
+    for (int s = 0; s < KC / 4 / KW; ++s) {
+      const int f4 = (kw + KW * s) * 4;
+      float4 a[RI], x[TJ];
+#pragma unroll
+      for (int i = 0; i < RI; ++i) a[i] = *reinterpret_cast<const float4*>(wb + 4 * i * PITCH + f4);
+#pragma unroll
+      for (int j = 0; j < TJ; ++j) x[j] = *reinterpret_cast<const float4*>(xb + 8 * j * PITCH + f4);
+#pragma unroll
+      for (int i = 0; i < RI; ++i)
+#pragma unroll
+        for (int j = 0; j < TJ; ++j) {
+          acc[i][j] = __ffma2_rn(make_float2(a[i].x, a[i].y), make_float2(x[j].x, x[j].y), acc[i][j]);
+          acc[i][j] = __ffma2_rn(make_float2(a[i].z, a[i].w), make_float2(x[j].z, x[j].w), acc[i][j]);
+        }
     }
   }
+  f32t_cp_async_wait<0>();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  __syncthreads();                         // the ring is free: it becomes the reduction area
+
+  // partial sums of the K lanes -> red[kw][row * TT + t]; summed in lane order into part[]
+  float* red = tf_smem;
+  float* part = tf_smem + KW * OUTS;
+#pragma unroll
+  for (int i = 0; i < RI; ++i)
+#pragma unroll
+    for (int j = 0; j < TJ; ++j)
+      red[kw * OUTS + (half * 4 * RI + rg + 4 * i) * TT + tg + 8 * j] = acc[i][j].x + acc[i][j].y;
   __syncthreads();
-  const float4* xs4 = reinterpret_cast<const float4*>(xs_f32);
-  for (int r0 = r_begin + warp * ROWS; r0 < r_end; r0 += kSkinnySmemWarps * ROWS) {
-    const float4* w[ROWS];
-    bool ok[ROWS];
+  for (int o = threadIdx.x; o < OUTS; o += kTileF32Threads) {
+    float v = red[o];
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-      ok[i] = r0 + i < r_end;
-      w[i] = reinterpret_cast<const float4*>(p.W + (long long)(ok[i] ? r0 + i : r0) * p.ldw);
-    }
-    float acc[ROWS][TMAX];
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i)
-#pragma unroll
-      for (int t = 0; t < TMAX; ++t) acc[i][t] = 0.0f;
-    for (int c = lane; c < chunks; c += 32) {
-      float4 a[ROWS];
-#pragma unroll
-      for (int i = 0; i < ROWS; ++i) a[i] = __ldcs(w[i] + c);
-#pragma unroll
-      for (int t = 0; t < TMAX; ++t) {
-        if (t < p.T) {
-          const float4 x = xs4[t * chunks + c];
-#pragma unroll
-          for (int i = 0; i < ROWS; ++i) {
-            acc[i][t] = fmaf(a[i].x, x.x, acc[i][t]);
-            acc[i][t] = fmaf(a[i].y, x.y, acc[i][t]);
-            acc[i][t] = fmaf(a[i].z, x.z, acc[i][t]);
-            acc[i][t] = fmaf(a[i].w, x.w, acc[i][t]);
-          }
-        }
+    for (int w = 1; w < KW; ++w) v += red[w * OUTS + o];
+    part[o] = v;
+  }
+  if (ks > 1) f32t_cluster_sync();        // every rank's part[] is complete and visible in the cluster
+  else __syncthreads();
+  {
+    // rank q finishes outputs [q * OUTS / ks, (q + 1) * OUTS / ks)
+    const int o_begin = rank * OUTS / ks, o_end = (rank + 1) * OUTS / ks;
+    const uint32_t part_addr = static_cast<uint32_t>(__cvta_generic_to_shared(part));
+    for (int o = o_begin + threadIdx.x; o < o_end; o += kTileF32Threads) {
+      const int row = r_base + o / TT, t = o % TT;
+      float v = 0.0f;
+      if (ks > 1) {
+        for (int q = 0; q < ks; ++q) v += f32t_ld_cluster(part_addr + 4u * o, (uint32_t)q);
+      } else {
+        v = part[o];
       }
-    }
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-#pragma unroll
-      for (int t = 0; t < TMAX; ++t) {
-        if (t < p.T) {
-          float v = acc[i][t];
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-          if (ok[i] && lane == (t & 31)) {
-            float* o = p.out + (long long)(r0 + i) * p.stride_r + (long long)t * p.stride_t;
-            float res = p.alpha * v;
-            if (p.beta != 0.0f) res += p.beta * (*o);
-            *o = res;
-          }
-        }
+      if (row < p.R && t < p.T) {
+        float* dst = p.out + (long long)row * p.stride_r + (long long)t * p.stride_t;
+        float res = p.alpha * v;
+        if (p.beta != 0.0f) res += p.beta * (*dst);
+        *dst = res;
       }
     }
   }
+  if (ks > 1) f32t_cluster_sync();        // a CTA's shared memory stays alive until its peers have read it
 }
 
 }  // namespace mp

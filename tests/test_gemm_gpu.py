@@ -541,7 +541,8 @@ def test_int8_gemm_follows_measured_plans_bit_exact(api, m):
 
 
 @pytest.mark.parametrize("m,n,k", [(37, 1024, 1024), (1, 300, 512), (64, 129, 2052), (700, 5, 1024), (9, 40, 8),
-                                   (16, 500, 2000), (33, 2000, 1280), (40, 64, 1024), (12, 4096, 4096), (1000, 20, 2560)])
+                                   (16, 500, 2000), (33, 2000, 1280), (40, 64, 1024), (12, 4096, 4096), (1000, 20, 2560),
+                                   (17, 1001, 260), (24, 77, 516), (41, 1500, 1028), (64, 4000, 768), (25, 9, 4)])
 def test_fp32_streaming_kernel(api, oracle, m, n, k):
     """Library-native pid 1101 for FP32 (one warp per row of the wide operand): within 1e-4 of the oracle on
     uniform inputs, exact on small integers, alpha/beta, both mappings; the selector names it for these shapes."""
@@ -558,6 +559,37 @@ def test_fp32_streaming_kernel(api, oracle, m, n, k):
     assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1).cpu().numpy(), exact.astype(np.float32))
     got = api.gemm_rcc_pid(dev(ai), dev(bi), 1101, 1, c_nm=dev(c0).clone(), alpha=2.0, beta=-1.0).cpu().numpy()
     assert np.array_equal(got, (2 * exact - c0.astype(np.int64)).astype(np.float32))
+
+
+_F32_TILE_CHILD = r"""
+import sys, numpy as np, torch
+sys.path[:0] = [sys.argv[1], sys.argv[2]]
+from moonpoly_b200 import api, rng
+from oracle import oracle
+for (m, n, k) in [(37, 1024, 1024), (64, 129, 2052), (9, 40, 8), (33, 2000, 1280), (1000, 20, 2560), (17, 1001, 260)]:
+    a = rng.uniform(97, 0, (m, k), -1.0, 1.0)
+    b = rng.uniform(97, 1, (n, k), -1.0, 1.0)
+    c0 = rng.uniform(97, 2, (n, m), -1.0, 1.0)
+    ref = oracle.gemm_f32_rcc(a, b, 0.5, -1.5, c0)
+    got = api.gemm_rcc_pid(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), 1101, 1,
+                           c_nm=torch.from_numpy(c0).cuda(), alpha=0.5, beta=-1.5).cpu().numpy()
+    assert np.all(np.abs(got - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref))), (m, n, k)
+assert api.device_status() == 0
+print("ok")
+"""
+
+
+@pytest.mark.parametrize("shape", ["8,1", "8,2", "16,1", "16,4", "8,8", "32,1", "32,2", "32,8"])
+def test_fp32_tile_kernel_launch_shapes(shape):
+    """The FP32 tile kernel with 8, 16 or 32 rows per CTA and K split over a cluster of 1, 2, 4 or 8 CTAs (the launch
+    shape is read from MOONPOLY_F32_TILE once per process, hence the child process)."""
+    import subprocess
+    import sys
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+    env = dict(os.environ, MOONPOLY_F32_TILE=shape)
+    out = subprocess.run([sys.executable, "-c", _F32_TILE_CHILD, root, os.path.join(root, "moonpoly-dev_b200", "py")],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr
 
 
 def test_scaled_mm_padded_leading_dimensions_and_ragged_k(api, oracle):
