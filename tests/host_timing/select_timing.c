@@ -14,7 +14,7 @@ static double now_ns(void) {
 }
 
 int main(void) {
-  const int count = 1500, passes = 6;
+  const int count = 1500, passes = 24;
   mp_plan p;
   double cold = 1e30, warm = 1e30;
   for (int pass = 0; pass < passes; ++pass) {

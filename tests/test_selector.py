@@ -145,7 +145,7 @@ def test_bad_arguments(api):
 
 def test_selection_overhead_budget(api, tmp_path):
     """<= 5 us per shape on the host at first sight of a shape, <= 1 us memoised: timed in C around mp_select_plan
-    (tests/host_timing/select_timing.c), best of six passes so a busy host does not fail the test."""
+    (tests/host_timing/select_timing.c), best of 24 passes so a busy host does not fail the test."""
     here = os.path.dirname(os.path.abspath(__file__))
     exe = str(tmp_path / "select_timing")
     lib_dir = os.path.dirname(api.LIB_PATH)
