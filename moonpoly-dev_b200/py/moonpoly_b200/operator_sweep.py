@@ -18,7 +18,7 @@ LLM projections, irregular and unaligned shapes down to 1x1x1, and the DeepBench
 is torch.matmul for FP16 / FP32 and torch._int_mm for INT8 where it accepts the shape: harness only, the library
 itself never calls a vendor GEMM.
 
-    python -m moonpoly_b200.operator_sweep --outdir gpurun_out/operator_level [--shapes gemm_trick.csv] [--limit N]
+    python -m moonpoly_b200.operator_sweep --outdir out/operator_level [--shapes gemm_trick.csv] [--limit N]
 """
 from __future__ import annotations
 
@@ -227,7 +227,7 @@ def run_sweep(shapes, outdir: str, force: bool = False, log_every: int = 100):
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default=None, help="CSV with qid,m,n,k; default: a seeded synthetic list")
-    ap.add_argument("--outdir", default="gpurun_out/operator_level")
+    ap.add_argument("--outdir", default="out/operator_level")
     ap.add_argument("--limit", type=int, default=0)
     ap.add_argument("--synthetic-count", type=int, default=200, dest="synthetic_count")
     ap.add_argument("--force", action="store_true")
