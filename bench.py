@@ -547,8 +547,8 @@ def run_ours(args, rank, world, local_rank):
     stack_line = stack_nccl = None
     if not args.no_stack:
         from moonpoly_b200 import stack as stack_mod
-        stack_line = stack_mod.run_stack(rank, world, dev, dist, steps=args.stack_steps, warmup=2, gather="fused", root=ROOT)
-        if world > 1:      # the same steps with ncclAllGather instead of the fused peer stores, for comparison
+        stack_line = stack_mod.run_stack(rank, world, dev, dist, steps=args.stack_steps, warmup=2, gather="auto", root=ROOT)
+        if world > 1:      # the same steps with ncclAllGather everywhere (auto: fused peer stores for small slabs), for comparison
             stack_nccl = stack_mod.run_stack(rank, world, dev, dist, steps=args.stack_steps, warmup=2, gather="nccl", root=ROOT)
 
     def reduce_max(d):

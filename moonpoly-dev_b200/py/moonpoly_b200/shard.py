@@ -25,6 +25,16 @@ def shard_bounds(n: int, world: int, rank: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
+# Slab bytes a rank pushes to its peers up to which the fused gather beats ncclAllGather (measured on B200 over
+# NVSwitch: plain peer stores from the epilogue hide under the GEMM while they are small, but a large slab leaves
+# through the epilogue warps at a fraction of the NVLink rate and stalls the accumulator drain).
+FUSED_GATHER_MAX_BYTES = 8 << 20
+
+
+def fused_gather_pays(rows: int, n_shard: int, world: int, itemsize: int = 2, limit: int = FUSED_GATHER_MAX_BYTES) -> bool:
+    return (world - 1) * rows * n_shard * itemsize <= limit
+
+
 class _DevicePointer:
     """Lets torch view memory this module allocated through the library (cuda array interface)."""
 
@@ -124,6 +134,16 @@ class ColumnParallelLinear:
         out.linear_gather(x, self.w, lo)
         out.barrier(timeout_us)
         return out.tensor(x.shape[0])
+
+    def forward_gather(self, x: torch.Tensor, out: PeerOutput, fused_max_bytes: int = None) -> torch.Tensor:
+        """Full Y[M, N] on every rank by whichever way is faster for this many rows: the fused peer stores while the
+        bytes this rank sends to its peers, (world - 1) * M * N_r * itemsize, stay within `fused_max_bytes`
+        (default FUSED_GATHER_MAX_BYTES), ncclAllGather beyond.  Every rank sees the same M, so all ranks take the
+        same branch."""
+        limit = FUSED_GATHER_MAX_BYTES if fused_max_bytes is None else fused_max_bytes
+        if fused_gather_pays(x.shape[0], self.w.shape[0], self.world, x.element_size(), limit):
+            return self.forward_gather_fused(x, out)
+        return self.gather(self.forward(x))
 
     def gather(self, y_local: torch.Tensor) -> torch.Tensor:
         """Full Y[M, N] on every rank (one all-gather).  Equal shards (N % world == 0, true for every

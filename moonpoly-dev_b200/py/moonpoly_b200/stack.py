@@ -49,7 +49,8 @@ def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3
     """Runs the stack on an initialised process group (dist is None on one GPU) and returns the result line on
     rank 0 (None elsewhere).  gather: "fused" = the GEMM epilogue stores each slab into every GPU's copy of the
     full output through peer-mapped pointers, then one flag-barrier kernel; "nccl" = ncclAllGather after o_proj and
-    down; "none" = GEMMs only."""
+    down; "auto" = fused while the slab a rank pushes to its peers is small (shard.fused_gather_pays), NCCL beyond;
+    "none" = GEMMs only."""
     import torch
     from . import api
 
@@ -79,10 +80,11 @@ def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3
     tokens = draw_tokens(4, warmup + steps)
 
     fused = {}
-    if do_gather and gather == "fused":
+    auto = gather == "auto"
+    if do_gather and gather in ("fused", "auto"):
         # peer-mapped copies of the two gathered outputs; when any rank cannot map its peers (no peer access between
         # the GPUs, IPC refused) every rank falls back to ncclAllGather together
-        from .shard import PeerOutput
+        from .shard import PeerOutput, fused_gather_pays
         err = ""
         try:
             for j, (_, n, _, g) in enumerate(shard):
@@ -104,7 +106,7 @@ def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3
         for layer in range(layers):
             ws = weights[layer % resident]
             for j, (_, n, k, g) in enumerate(shard):
-                if g and j in fused:
+                if g and j in fused and (not auto or fused_gather_pays(m, n, world)):
                     _, dst, flag_table = fused[j]
                     rc = L.mp_linear_gather(api.MP_FP16, m, n, k, vp(x_in[k].data_ptr()), vp(ws[j].data_ptr()), dst, world,
                                             n * world, rank * n, st)
@@ -173,7 +175,7 @@ def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3
             "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": warmup,
             "ms_per_step": sum(ms) / len(ms), "higher_is_better": True, "scaling": "strong", "dtype": "f16",
             "data": "synthetic", "roofline_frac": sum(roof_ms) / sum(ms), "decode": agg(decode), "prefill": agg(prefill),
-            "host_wall_ms_per_step": wall / steps * 1e3,
+            "host_wall_ms_per_step": wall / steps * 1e3, "per_step_tokens_ms": [[int(m), round(t, 3)] for m, t in zip(ms_steps, ms)],
             "config": {"workload": "Llama-3-70B-shaped FP16 linear stack", "layers": layers, "resident_layers": resident,
                        "gather": gather if world > 1 else "none",
                        "parallelism": f"column-parallel x{world}, all-gather after o_proj and down" if do_gather
@@ -186,7 +188,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl", "none"])
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl", "none"])
     args = ap.parse_args()
 
     import torch

@@ -152,3 +152,20 @@ def test_peer_output_maps_every_rank_and_orders_destinations(monkeypatch):
         out.close()
         assert len(apis[r].closed) == 2 * (world - 1) and sorted(apis[r].freed) == [own, own + 1]
     assert real_tensor is torch.tensor
+
+
+def test_forward_gather_picks_the_fused_path_by_the_bytes_a_rank_sends(monkeypatch):
+    """forward_gather: fused peer stores while (world - 1) * M * N_r * itemsize stays within the limit, the collective
+    beyond; the decision depends only on values every rank shares (M, shard width, world)."""
+    from moonpoly_b200 import shard
+    assert shard.fused_gather_pays(64, 1024, 8)                                  # a decode step of a 70B o_proj on 8 GPUs
+    assert not shard.fused_gather_pays(4096, 1024, 8)                            # a prefill step: 58 MB to push
+    assert shard.fused_gather_pays(4096, 1024, 8, limit=1 << 30)
+    assert shard.fused_gather_pays(1, 1, 1, limit=0)                             # one rank sends nothing
+    taken = []
+    layer = shard.ColumnParallelLinear(torch.zeros((8, 4)), 24, 1, 3, compute=lambda x, w: "local")
+    monkeypatch.setattr(layer, "forward_gather_fused", lambda x, out, timeout_us=0: taken.append("fused") or "fused")
+    monkeypatch.setattr(layer, "gather", lambda y: taken.append("nccl") or "gathered")
+    assert layer.forward_gather(torch.zeros((5, 4), dtype=torch.float16), None) == "fused"
+    assert layer.forward_gather(torch.zeros((5, 4), dtype=torch.float16), None, fused_max_bytes=100) == "gathered"   # 2*5*8*2 = 160 B
+    assert taken == ["fused", "nccl"]

@@ -51,6 +51,14 @@ def _worker(rank, world, port, tmp):
                 ref = api.linear(xs, w).float()
                 assert torch.all((got.float() - ref).abs() <= 1e-3 + 1e-2 * ref.abs()), rows
                 dist.barrier()               # nobody overwrites the buffer while a peer still compares
+            # forward_gather takes either way by the bytes a rank pushes; both give the same bits
+            xs = torch.from_numpy(rng.normal(77, 0, (96, K), 0.05)).cuda()
+            want = layer.gather(layer.forward(xs))
+            for limit in (None, 0):          # default limit: fused for this size; 0: the collective
+                got = layer.forward_gather(xs, out, fused_max_bytes=limit)
+                torch.cuda.synchronize()
+                assert torch.equal(got, want), limit
+                dist.barrier()
         finally:
             out.close()
         assert api.device_status() == 0
