@@ -243,11 +243,14 @@ def extra_sections(api, L, st, dev, peaks):
             sa = sa_all[:M]
             o = torch.empty((M, N), dtype=torch.float16, device=dev)
 
+            # argument tuples built once per weight copy: the Python side of a call stays ~1 us
+            i8_args = [(M, N, K, vp(a.data_ptr()), K, vp(ws[j].data_ptr()), K, vp(sa.data_ptr()), 0,
+                        vp(sb.data_ptr()), 0, vp(0), vp(o.data_ptr()), N, 0, st) for j in range(copies)]
+
             def call(i):
-                rc = L.mp_scaled_mm_i8(M, N, K, vp(a.data_ptr()), K, vp(ws[i % copies].data_ptr()), K, vp(sa.data_ptr()), 0,
-                                       vp(sb.data_ptr()), 0, vp(0), vp(o.data_ptr()), N, 0, st)
+                rc = L.mp_scaled_mm_i8(*i8_args[i % copies])
                 assert rc == 0, L.mp_last_error_string()
-            t = ev_time(call, 6 if M <= 1024 else 3)
+            t = ev_time(call, 24 if M <= 256 else 6 if M <= 1024 else 3)
             ops = 2.0 * M * N * K
             byts = M * K + N * K + 2.0 * M * N + 4.0 * (M + N)
             roof = max(ops / (int8_peak * 1e12), byts / (peaks["hbm_gbs"] * 1e9))
@@ -283,21 +286,25 @@ def extra_sections(api, L, st, dev, peaks):
             best = None
             for pid in (400, 407, 413, 425, 439):
                 for S in (1, 2, 4, 8):
+                    pid_args = [(api.MP_FP16, pid, S, N, M, K, vp(ws[j].data_ptr()), vp(x.data_ptr()), vp(y.data_ptr()),
+                                 ctypes.c_float(1.0), ctypes.c_float(0.0), vp(0), 0, st) for j in range(copies)]
+
                     def call(i):
-                        rc = L.mp_gemm_rcc_pid(api.MP_FP16, pid, S, N, M, K, vp(ws[i % copies].data_ptr()), vp(x.data_ptr()),
-                                               vp(y.data_ptr()), 1.0, 0.0, vp(0), 0, st)
+                        rc = L.mp_gemm_rcc_pid(*pid_args[i % copies])
                         assert rc == 0, L.mp_last_error_string()
-                    t = ev_time(call, 6)
+                    t = ev_time(call, 12)
                     if best is None or t < best[0]:
                         best = (t, pid, S)
             byts = 2.0 * (M * K + N * K + M * N)
             roof = max(2.0 * M * N * K / (peaks["tflops"] * 1e12), byts / (peaks["hbm_gbs"] * 1e9))
             fr.append(roof / best[0])
 
+            sel_args = [(api.MP_FP16, M, N, K, vp(x.data_ptr()), vp(ws[j].data_ptr()), vp(y.data_ptr()), st) for j in range(copies)]
+
             def call_sel(i):       # the same Linear through the online selector (free to leave the pids-400+ family)
-                rc = L.mp_linear(api.MP_FP16, M, N, K, vp(x.data_ptr()), vp(ws[i % copies].data_ptr()), vp(y.data_ptr()), st)
+                rc = L.mp_linear(*sel_args[i % copies])
                 assert rc == 0, L.mp_last_error_string()
-            t_sel = ev_time(call_sel, 12)
+            t_sel = ev_time(call_sel, 24)
             fr_sel.append(roof / t_sel)
             rows.append({"M": M, "N": N, "K": K, "best_us": round(best[0] * 1e6, 2), "pid": best[1], "split_k": best[2],
                          "frac": round(roof / best[0], 4),
