@@ -162,6 +162,51 @@ int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes,
   return MP_OK;
 }
 
+// Second pool, same rules: padded copies of operands whose rows miss the tensor path's 16-byte alignment.
+std::vector<Scratch> g_pad_scratch;
+
+int get_pad_scratch(cudaStream_t stream, size_t bytes, uint8_t** out) {
+  int dev = 0;
+  MP_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> g(g_mu);
+  Scratch* s = nullptr;
+  for (auto& e : g_pad_scratch)
+    if (e.dev == dev && e.stream == stream) { s = &e; break; }
+  if (s == nullptr || s->bytes < bytes) {
+    // a fresh buffer with head-room; the old one is kept (work already queued may still read it)
+    const size_t total = std::max<size_t>(round_up(bytes + bytes / 2, 1 << 20), 16 << 20);
+    uint8_t* p = nullptr;
+    if (cudaMalloc(&p, total) != cudaSuccess) {
+      cudaGetLastError();           // not an error of the call: the caller falls back to the CUDA-core kernels
+      return MP_ERR_WORKSPACE;
+    }
+    if (s == nullptr) {
+      g_pad_scratch.push_back(Scratch{dev, stream, p, total, 0});
+      s = &g_pad_scratch.back();
+    } else {
+      s->ptr = p; s->bytes = total;
+    }
+  }
+  *out = s->ptr;
+  return MP_OK;
+}
+
+// dst[r][0..kp) = src[r][0..k) followed by zeros; kp * sizeof(T) is a multiple of 16 and dst is 16-byte aligned.
+// One thread builds one 16-byte word from scalar loads (the source rows have no alignment beyond the element's).
+template <typename T>
+__global__ void pad_rows_kernel(const T* __restrict__ src, long long ld, T* __restrict__ dst, int rows, int k, int kp) {
+  constexpr int kPer = 16 / (int)sizeof(T);
+  const int words = kp / kPer;
+  const long long total = (long long)rows * words;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / words), c0 = (int)(i - (long long)r * words) * kPer;
+    alignas(16) T v[kPer];
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) v[e] = c0 + e < k ? src[(long long)r * ld + c0 + e] : T(0);
+    *reinterpret_cast<uint4*>(dst + (long long)r * kp + c0) = *reinterpret_cast<const uint4*>(v);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Built-in scratch of mp_gemm_rcc_pid_static_scratch: lives in every GPU that loads the library,
 // from load to exit.  The name is a host-side stand-in; kernels get the address that
@@ -254,6 +299,45 @@ bool tma_compatible(const Problem& p) {
   if (p.k <= 0) return false;
   if ((reinterpret_cast<uintptr_t>(p.A) & 15) || (reinterpret_cast<uintptr_t>(p.B) & 15)) return false;
   if ((p.lda * eb) % 16 != 0 || (p.ldb * eb) % 16 != 0) return false;
+  return true;
+}
+
+// FP16 / INT8 operands whose rows miss the 16-byte alignment (K * element size not a multiple of 16, an odd leading
+// dimension or base address) cannot be described to TMA.  Entries that own their scratch copy such operands once
+// into zero-padded, aligned rows (K rounded up to 128 bytes: zeros add nothing to a dot product) and run the tensor
+// path on the copies; the CUDA-core tiles remain the fall-back when the copy cannot be allocated and for entries
+// whose memory the caller manages.  MOONPOLY_DISABLE_PAD=1 turns the copies off.
+bool pad_disabled() {
+  const char* v = std::getenv("MOONPOLY_DISABLE_PAD");
+  return v && v[0] && v[0] != '0';
+}
+
+bool pad_operands(Problem& p, cudaStream_t stream) {
+  if (p.dtype != MP_FP16 && p.dtype != MP_INT8) return false;
+  if (p.k <= 0 || p.m <= 0 || p.n <= 0 || tma_compatible(p) || pad_disabled()) return false;
+  const int eb = elem_bytes(p.dtype);
+  const int per128 = 128 / eb;
+  const long long kp = ((long long)p.k + per128 - 1) / per128 * per128;
+  const size_t a_bytes = round_up((size_t)p.m * kp * eb, 256), b_bytes = round_up((size_t)p.n * kp * eb, 256);
+  uint8_t* buf = nullptr;
+  if (get_pad_scratch(stream, a_bytes + b_bytes, &buf) != MP_OK) return false;
+  const auto launch = [&](const void* src, long long ld, void* dst, int rows) {
+    const long long words = (long long)rows * (kp * eb / 16);
+    const int grid = (int)std::min<long long>((words + 255) / 256, 148 * 16);
+    if (eb == 2)
+      pad_rows_kernel<uint16_t><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(src), ld,
+                                                          reinterpret_cast<uint16_t*>(dst), rows, p.k, (int)kp);
+    else
+      pad_rows_kernel<uint8_t><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint8_t*>(src), ld,
+                                                         reinterpret_cast<uint8_t*>(dst), rows, p.k, (int)kp);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  };
+  launch(p.A, p.lda, buf, p.m);
+  launch(p.B, p.ldb, buf + a_bytes, p.n);
+  if (cudaGetLastError() != cudaSuccess) return false;
+  p.A = buf; p.lda = kp;
+  p.B = buf + a_bytes; p.ldb = kp;
+  p.k = (int)kp;
   return true;
 }
 
@@ -610,33 +694,59 @@ int run_gemv(const Problem& p, cudaStream_t stream) {
 
 // Streaming warp-MMA path: one side of the problem has at most 64 rows; the other operand is streamed once.
 template <int KIND, int EPI, int NT, int UNROLL, int MINB>
-int launch_stream_t(const StreamParams& sp, int sms, cudaStream_t stream) {
-  // a whole multiple of the SM count when the rows allow it, else one CTA per 8 rows; with a token split every
-  // block of rows is taken by t_split neighbouring CTAs
-  const int per_sm = std::min(MINB, sp.R / (8 * sms));
-  const int grid = (per_sm >= 1 ? per_sm * sms : std::max(1, (sp.R + 7) / 8)) * std::max(1, sp.t_split);
+int launch_stream_t(const StreamParams& sp, int row_ctas, cudaStream_t stream) {
+  // every block of rows is taken by t_split neighbouring token parts, each of them by k_split consecutive CTAs
+  // (one cluster) that cut K
+  const int ks = std::max(1, sp.k_split);
+  const int grid = row_ctas * std::max(1, sp.t_split) * ks;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(kStreamWarps * 32);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (g_use_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  if (ks > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)ks;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  cfg.numAttrs = na;
   MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, stream_mma_kernel<KIND, EPI, NT, UNROLL, MINB>, sp));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
 }
 
 template <int KIND, int EPI>
-int launch_stream_nt(const StreamParams& sp, int sms, cudaStream_t stream) {
+int launch_stream_nt(const StreamParams& sp, int row_ctas, cudaStream_t stream) {
   const int rows = sp.t_split > 1 ? sp.t_per : sp.T;       // rows of X one CTA works against
-  if (rows <= 8) return launch_stream_t<KIND, EPI, 1, 8, 2>(sp, sms, stream);
-  if (rows <= 16) return launch_stream_t<KIND, EPI, 2, 8, 2>(sp, sms, stream);
-  if (rows <= 32) return launch_stream_t<KIND, EPI, 4, 8, 2>(sp, sms, stream);
-  return launch_stream_t<KIND, EPI, 8, 4, 2>(sp, sms, stream);
+  if (rows <= 8) return launch_stream_t<KIND, EPI, 1, 8, 2>(sp, row_ctas, stream);
+  if (rows <= 16) return launch_stream_t<KIND, EPI, 2, 8, 2>(sp, row_ctas, stream);
+  if (rows <= 32) return launch_stream_t<KIND, EPI, 4, 8, 2>(sp, row_ctas, stream);
+  return launch_stream_t<KIND, EPI, 8, 4, 2>(sp, row_ctas, stream);
 }
+
+// CTAs along the rows of W: a whole multiple of the SM count (at most two per SM) when the rows allow it, else one
+// CTA per `rows_per_cta` rows.
+int stream_row_ctas(int R, int sms, int rows_per_cta) {
+  const int per_sm = std::min(2, R / (8 * sms));
+  return per_sm >= 1 ? per_sm * sms : std::max(1, (R + rows_per_cta - 1) / rows_per_cta);
+}
+
+// K split of the streaming kernel (see StreamParams::k_split).  0 = the library's rule, 1 = off, 2 / 4 / 8 = forced;
+// MOONPOLY_STREAM_KSPLIT overrides the rule the same way.
+int stream_ksplit_from_env() {
+  const char* v = std::getenv("MOONPOLY_STREAM_KSPLIT");
+  return v && v[0] ? std::atoi(v) : 0;
+}
+std::atomic<int> g_stream_ksplit{stream_ksplit_from_env()};
 
 // Token split of the streaming kernel (see StreamParams::t_split).  0 = the library's rule below, 1 = off,
 // 2 / 4 / 8 = forced; MOONPOLY_STREAM_TSPLIT overrides the rule the same way.
@@ -730,10 +840,27 @@ int launch_stream_ck_nt(DeviceState& d, int base_slot, const StreamCkParams& cp,
 // and the same holds for every layer with enough rows to give each SM a CTA.  The split pays only when the rows are
 // too few to fill the GPU (N = 1024, K = 8192: M = 16 10.0 -> 8.0 us, M = 32 14.7 -> 10.6 us), where it doubles the
 // number of CTAs: two parts when one CTA per 8 rows leaves SMs idle and there are more than 8 rows of X.
-int stream_tsplit_rule(int R, int T, int K, int elt) {
-  (void)K; (void)elt;
-  const int sms = mp::num_sms_for_model();
-  return (T > 8 && (R + 7) / 8 < sms) ? 2 : 1;
+int stream_tsplit_rule(int ctas, int T, int sms) {
+  return (T > 8 && ctas < sms) ? 2 : 1;
+}
+
+// When to split K over a cluster.  A whole-K CTA keeps at most 64 KB of W in flight (8 warps x 32 lanes x 16 loads
+// of 16 bytes), and the HBM queue needs about two such CTAs per SM to stay full; a weight with fewer than
+// 8 * 2 * SMs rows cannot give that many.  The K parts (a power of two) multiply the CTAs up to two per SM, as long
+// as every CTA still streams at least 192 KB of W: below that the cluster's start-up and exchange cost more than
+// the extra loads in flight bring.  Measured on B200 (FP16, Linear mapping): (M, N, K) = (1, 1024, 28672) 24.0 us
+// whole-K, 18.2 / 16.8 / 29.2 us with 2 / 4 / 8 parts; (8, 1024, 28672) 25.8 -> 18.0 us with 4; (1, 2048, 28672)
+// 28.6 -> 25.6 us with 2 (4 parts: 39.2 us, four CTAs per SM no longer run together); (1, 1024, 8192) 6.5 us
+// whole-K against 6.8 / 6.9 us with 2 / 4 parts, (8, 2048, 8192) 9.3 against 9.9 us: too short to pay.
+int stream_ksplit_rule(int R, int K, int elt, int sms) {
+  if (R / (8 * sms) >= 2) return 1;
+  const bool one_per_sm = R / (8 * sms) >= 1;
+  const int row_ctas = one_per_sm ? sms : (R + kStreamRows - 1) / kStreamRows;
+  const double rows_per_cta = one_per_sm ? (double)R / sms : (double)std::min(R, kStreamRows);
+  const double bytes_per_cta = rows_per_cta * K * elt;
+  int ks = 1;
+  while (ks < 8 && row_ctas * ks * 2 <= 2 * sms && bytes_per_cta / (ks * 2) >= 192.0 * 1024.0) ks *= 2;
+  return ks;
 }
 
 bool stream_compatible(const Problem& p) {
@@ -743,8 +870,8 @@ bool stream_compatible(const Problem& p) {
          tma_compatible(p);      // same rule: 16-byte aligned rows
 }
 
-// forced_ck: 0 = the library decides between the two streaming kernels; > 0 = the cluster-K kernel with that
-// many K ranges (1, 2, 4 or 8); < 0 = the one-CTA-per-row-block kernel.
+// forced_ck: 0 = the library decides; > 0 = the staged cluster-K kernel with that many K ranges (1, 2, 4 or 8);
+// < 0 = the streaming kernel with -forced_ck K parts (-1: whole-K CTAs).
 int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int forced_tsplit = 0) {
   DeviceState* d = nullptr;
   if (int rc = device_state(&d)) return rc;
@@ -785,10 +912,18 @@ int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int for
       return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_SCALED>(*d, 8, cp, stream);
     }
   }
+  // K split first (it cuts both operands per CTA), then the token split for what is still short of one wave
+  const int elt = elem_bytes(p.dtype);
+  int ks = forced_ck < 0 ? -forced_ck : g_stream_ksplit.load(std::memory_order_relaxed);
+  if (ks == 0) ks = stream_ksplit_rule(sp.R, sp.K, elt, d->sms);
+  while (ks > 1 && (long long)sp.K * elt < 4096ll * ks) ks >>= 1;      // every warp keeps a full batch of loads
+  ks = std::max(1, std::min(ks, 8));
+  sp.k_split = ks;
+  const int row_ctas = stream_row_ctas(sp.R, d->sms, ks > 1 ? kStreamRows : 8);
   // token split: parts of 8 or 16 rows of X per CTA, never an empty part
   {
     int ts = forced_tsplit > 0 ? forced_tsplit : g_stream_tsplit.load(std::memory_order_relaxed);
-    if (ts == 0) ts = stream_tsplit_rule(sp.R, sp.T, sp.K, elem_bytes(p.dtype));
+    if (ts == 0) ts = stream_tsplit_rule(row_ctas * ks, sp.T, d->sms);
     ts = std::max(1, std::min(ts, (sp.T + 7) / 8));
     if (ts > 1) {
       sp.t_per = ((sp.T + ts - 1) / ts + 7) / 8 * 8;
@@ -796,10 +931,10 @@ int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int for
     }
     sp.t_split = ts;
   }
-  if (p.dtype == MP_FP16 && p.bf16) return launch_stream_nt<STREAM_BF16, STREAM_EPI_F16>(sp, d->sms, stream);
-  if (p.dtype == MP_FP16) return launch_stream_nt<STREAM_F16, STREAM_EPI_F16>(sp, d->sms, stream);
-  if (p.epi == EPI_I32) return launch_stream_nt<STREAM_I8, STREAM_EPI_I32>(sp, d->sms, stream);
-  return launch_stream_nt<STREAM_I8, STREAM_EPI_SCALED>(sp, d->sms, stream);
+  if (p.dtype == MP_FP16 && p.bf16) return launch_stream_nt<STREAM_BF16, STREAM_EPI_F16>(sp, row_ctas, stream);
+  if (p.dtype == MP_FP16) return launch_stream_nt<STREAM_F16, STREAM_EPI_F16>(sp, row_ctas, stream);
+  if (p.epi == EPI_I32) return launch_stream_nt<STREAM_I8, STREAM_EPI_I32>(sp, row_ctas, stream);
+  return launch_stream_nt<STREAM_I8, STREAM_EPI_SCALED>(sp, row_ctas, stream);
 }
 
 // FP32 streaming kernel: one side of the problem has at most 64 rows.
@@ -1018,6 +1153,7 @@ int mp_reload_env(void) {
   g_use_cluster_splitk.store(cluster_splitk_from_env(), std::memory_order_relaxed);
   g_use_stream_cluster.store(stream_cluster_from_env(), std::memory_order_relaxed);
   g_stream_tsplit.store(stream_tsplit_from_env(), std::memory_order_relaxed);
+  g_stream_ksplit.store(stream_ksplit_from_env(), std::memory_order_relaxed);
   return MP_OK;
 }
 
@@ -1126,8 +1262,8 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
   if (orient == 3) {            // the streaming warp-MMA kernels (bn unused; split_k = K ranges of the cluster-K variant)
     const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
     if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16 or INT8, min(m,n) <= 64 and 16-byte aligned rows");
-    if (kc != 0 && kc != 1 && kc != 2 && kc != 4 && kc != 8 && kc != -1)
-      return fail(MP_ERR_INVALID_ARG, "streaming kernel: kc selects the K ranges of the cluster variant (1, 2, 4, 8), -1 the plain kernel, 0 lets the library choose");
+    if (kc != 0 && kc != 1 && kc != 2 && kc != 4 && kc != 8 && kc != -1 && kc != -2 && kc != -4 && kc != -8)
+      return fail(MP_ERR_INVALID_ARG, "streaming kernel: kc selects the K ranges of the staged cluster variant (1, 2, 4, 8), -1 / -2 / -4 / -8 the streaming kernel with that many K parts, 0 lets the library choose");
     return run_stream(pg, reinterpret_cast<cudaStream_t>(stream), kc, split_k > 1 ? split_k : 0);
   }
   const int xm = (orient == 4 || orient == 5) ? 2 : 1;       // orient 4 / 5: orient 0 / 1 with 256-row tiles
@@ -1158,10 +1294,11 @@ int mp_gemm_rcc(int dtype, int m, int n, int k, const void* A, const void* B, vo
                 void* stream) {
   if (int rc = check_rcc_args(dtype, m, n, k, A, B, C)) return rc;
   if (m == 0 || n == 0) return MP_OK;
-  const Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
+  Problem p = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (k == 0) return run_simt(p, 64, 64, 1, nullptr, 0, s);
-  const mp_plan plan = mp::select_plan(dtype, m, n, k);
+  pad_operands(p, s);                              // unaligned rows: the plan is then made for the padded K
+  const mp_plan plan = mp::select_plan(dtype, m, n, p.k);
   if (dtype == MP_FP16 && plan.pattern == MP_PATTERN_COMBINE) return run_twin(p, plan.split_n, s);
   return run_pid(p, plan.pid, plan.split_k, nullptr, 0, s);
 }
@@ -1220,7 +1357,8 @@ int mp_linear_bias(int dtype, int M, int N, int K, const void* X, const void* W,
   if (dtype == MP_BF16) { p.bf16 = 1; p.out_bf16 = 1; }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (K == 0) return run_simt(p, 64, 64, 1, nullptr, 0, s);
-  const mp_plan plan = mp::select_plan(MP_FP16, N, M, K);
+  pad_operands(p, s);
+  const mp_plan plan = mp::select_plan(MP_FP16, N, M, p.k);
   if (plan.pattern == MP_PATTERN_COMBINE) return run_twin(p, plan.split_n, s);
   return run_pid(p, plan.pid, plan.split_k, nullptr, 0, s);
 }
@@ -1338,8 +1476,9 @@ int mp_scaled_mm_i8(int M, int N, int K, const int8_t* A, int lda, const int8_t*
                                 out_dtype);
   if (rc != MP_OK) return rc < 0 ? MP_OK : rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (K > 0) pad_operands(p, s);
   if (K == 0 || !tma_compatible(p)) return run_simt(p, 64, 64, 1, nullptr, 0, s);
-  const mp::ScaledCfg cfg = mp::scaled_mm_select(M, N, K);
+  const mp::ScaledCfg cfg = mp::scaled_mm_select(M, N, p.k);
   if (cfg.stream && stream_compatible(p)) return run_stream(p, s);
   Launch l;
   l.orient = cfg.orient; l.bn = cfg.bn; l.split_k = cfg.split_k; l.xm = cfg.xm;

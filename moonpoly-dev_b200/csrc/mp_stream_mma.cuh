@@ -42,6 +42,11 @@ struct StreamParams {
   // t_per rows of X (a multiple of 8).  W is then read t_split times, but the repeats hit L2 (neighbouring CTAs
   // run together), HBM still sees it once, and every CTA keeps a narrow X that stays in L1.
   int t_split, t_per;
+  // K split: k_split > 1 gives every (row block, token part) to k_split consecutive CTAs -- one thread-block cluster
+  // -- each streaming its own contiguous range of K; the partial 16 x T blocks meet through distributed shared
+  // memory in rank order (deterministic).  For weights with so few rows that whole-K CTAs cannot keep enough loads
+  // in flight to fill the HBM queue (R ~ 1024..2048: the projections of a model sharded over 4-8 GPUs).
+  int k_split;
   // fused all-gather of a column-parallel Linear: the same output buffer in the memory of the other GPUs
   // (peer-mapped pointers, same strides); every result is stored there too with plain stores
   void* peer_out[7];
@@ -121,6 +126,22 @@ __device__ __forceinline__ void stream_finish(const StreamParams& p, uint32_t ac
   for (int d = 0; d < p.num_peers; ++d) stream_finish_to<EPI>(p, p.peer_out[d], accw, r, t);
 }
 
+__device__ __forceinline__ uint32_t stream_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void stream_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t stream_ld_dsmem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // NT = number of 8-row groups of X covered (T <= 8 * NT); UNROLL = K blocks (64 bytes of each row)
 // in flight per warp; MINB = CTAs that must fit on an SM.  The grid is a whole multiple of the SM
 // count whenever there are enough rows, and CTA i takes the contiguous rows [i*R/G, (i+1)*R/G):
@@ -134,9 +155,13 @@ stream_mma_kernel(const StreamParams p) {
   constexpr int kChunkElems = 16 / kElt;                   // elements per 16-byte chunk
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
+  __shared__ uint32_t part[kStreamRows][NT * 8];
   const int t_split = p.t_split > 1 ? p.t_split : 1;
-  const int rb = (int)blockIdx.x / t_split, nrb = (int)gridDim.x / t_split;
-  const int t0 = ((int)blockIdx.x - rb * t_split) * p.t_per;          // first row of X of this CTA
+  const int ks = p.k_split > 1 ? p.k_split : 1;
+  const int kq = (int)blockIdx.x % ks;                                 // rank in the cluster = K range
+  const int bid = (int)blockIdx.x / ks, nbid = (int)gridDim.x / ks;
+  const int rb = bid / t_split, nrb = nbid / t_split;
+  const int t0 = (bid - rb * t_split) * p.t_per;                      // first row of X of this CTA
   const int Tl = t_split > 1 ? min(p.t_per, p.T - t0) : p.T;          // rows of X of this CTA
   const int r_begin = (int)((long long)rb * p.R / nrb);
   const int r_end = (int)((long long)(rb + 1) * p.R / nrb);
@@ -158,9 +183,10 @@ stream_mma_kernel(const StreamParams p) {
 
   const int chunks = p.K / kChunkElems;                 // 16-byte chunks per row
   const int blocks = (chunks + 3) >> 2;                 // K blocks of 4 chunks
-  const int per_warp = (blocks + kStreamWarps - 1) / kStreamWarps;
-  const int blk_begin = warp * per_warp;
-  const int blk_end = min(blocks, blk_begin + per_warp);
+  const int cta_blk0 = (int)((long long)blocks * kq / ks), cta_blk1 = (int)((long long)blocks * (kq + 1) / ks);
+  const int per_warp = (cta_blk1 - cta_blk0 + kStreamWarps - 1) / kStreamWarps;
+  const int blk_begin = cta_blk0 + warp * per_warp;
+  const int blk_end = min(cta_blk1, blk_begin + per_warp);
 
   const uint4* xr[NT];
   bool x_ok[NT];
@@ -246,7 +272,34 @@ stream_mma_kernel(const StreamParams p) {
         for (int w = 0; w < kStreamWarps; ++w) v += __uint_as_float(red[w][r][t]);
         accw = __float_as_uint(v);
       }
-      stream_finish<EPI>(p, accw, row0 + r, t0 + t);
+      if (ks == 1) stream_finish<EPI>(p, accw, row0 + r, t0 + t);
+      else part[r][t] = accw;
+    }
+    if (ks > 1) {
+      // every K range's 16 x Tl block is in its CTA's shared memory; rank kq finishes its share of the outputs,
+      // adding the ranks' partial sums in rank order
+      stream_cluster_sync();
+      const int n_out = kStreamRows * Tl;
+      const int i_begin = n_out * kq / ks, i_end = n_out * (kq + 1) / ks;
+      for (int i = i_begin + threadIdx.x; i < i_end; i += kStreamWarps * 32) {
+        int r, t;
+        if (rows_contig) { r = i & (kStreamRows - 1); t = i >> 4; }
+        else { t = i % Tl; r = i / Tl; }
+        if (row0 + r >= r_end) continue;
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(&part[r][t]));
+        uint32_t accw;
+        if constexpr (KIND == STREAM_I8) {
+          int v = 0;
+          for (int q = 0; q < ks; ++q) v += (int)stream_ld_dsmem(addr, (uint32_t)q);
+          accw = (uint32_t)v;
+        } else {
+          float v = 0.0f;
+          for (int q = 0; q < ks; ++q) v += __uint_as_float(stream_ld_dsmem(addr, (uint32_t)q));
+          accw = __float_as_uint(v);
+        }
+        stream_finish<EPI>(p, accw, row0 + r, t0 + t);
+      }
+      stream_cluster_sync();          // the peers have read this CTA's block: it may be overwritten or go away
     }
   }
 }
@@ -273,22 +326,6 @@ struct StreamCkParams {
   int stage_x;         // 1: this CTA's K range of X is staged in shared memory
   int x_row_bytes;     // padded bytes per staged X row (a multiple of 16, odd multiple keeps the banks apart)
 };
-
-__device__ __forceinline__ uint32_t stream_cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void stream_cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t stream_ld_dsmem(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote, v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
-  return v;
-}
 
 template <int KIND, int EPI, int NT, int UNROLL>
 __global__ void __launch_bounds__(kStreamWarps * 32, 1)

@@ -592,6 +592,62 @@ def test_fp32_tile_kernel_launch_shapes(shape):
     assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stdout + out.stderr
 
 
+@pytest.mark.parametrize("m,n,k", [(438, 10, 3695), (83, 286, 3269), (1, 300, 1001), (256, 512, 130), (37, 64, 7), (700, 900, 2)])
+def test_unaligned_k_runs_on_padded_copies(api, oracle, m, n, k, monkeypatch):
+    """FP16 rows that miss TMA's 16-byte rule (K not a multiple of 8): the selector entries copy both operands into
+    zero-padded aligned rows and run the tensor path; same results as the CUDA-core fall-back within FP16 tolerance,
+    exact on small integers, alpha / beta, and a second call of another size re-uses or regrows the copy buffer."""
+    a = rng.normal(220, 0, (m, k), 0.05)
+    b = rng.normal(220, 1, (n, k), 0.05)
+    c0 = rng.normal(220, 2, (n, m), 1.0)
+    ref = oracle.gemm_f16_rcc(a, b)
+    n0 = api.launch_count()
+    got = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    assert api.launch_count() - n0 >= 3                  # two copies and the GEMM
+    close_f16(got, ref)
+    close_f16(api.gemm_rcc(dev(a), dev(b), c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0))
+    monkeypatch.setenv("MOONPOLY_DISABLE_PAD", "1")
+    n0 = api.launch_count()
+    close_f16(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), ref)
+    assert api.launch_count() - n0 <= 2                  # the CUDA-core tiles (and their split-K pass)
+    monkeypatch.delenv("MOONPOLY_DISABLE_PAD")
+    ai = rng.small_ints(221, 0, (m, k), lo=-1, hi=1)
+    bi = rng.small_ints(221, 1, (n, k))
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T.astype(np.float16)
+    assert np.array_equal(api.gemm_rcc(dev(ai), dev(bi)).cpu().numpy(), exact)
+    # a base address that is only element-aligned (a view one element into a buffer) takes the same route
+    L = api.lib()
+    out = torch.empty((n, m), dtype=torch.float16, device=DEV)
+    B = dev(b)
+    flat = torch.zeros((m * k + 1,), dtype=torch.float16, device=DEV)
+    a_mis = flat[1:].view(m, k)
+    a_mis.copy_(dev(a))
+    assert a_mis.data_ptr() % 16 != 0
+    rc = L.mp_gemm_rcc(api.MP_FP16, m, n, k, a_mis.data_ptr(), B.data_ptr(), out.data_ptr(), 1.0, 0.0, None)
+    assert rc == 0, L.mp_last_error_string()
+    torch.cuda.synchronize()
+    close_f16(out.cpu().numpy(), ref)
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 1024, 1032), (579, 1560, 3160), (5, 200, 1000), (64, 64, 24)])
+def test_int8_unaligned_k_padded_copies_bit_exact(api, oracle, M, N, K):
+    """INT8 with K not a multiple of 16: int32 accumulators stay exact and the scaled matmul bit-identical to the
+    oracle through the padded copies."""
+    a = rng.int8_uniform(222, 0, (M, K))
+    b = rng.int8_uniform(222, 1, (N, K))
+    assert np.array_equal(api.gemm_rcc(dev(a), dev(b)).cpu().numpy(), oracle.gemm_i8_rcc(a, b))
+    sa = rng.uniform(222, 2, (M,), 0.001, 0.02)
+    sb = rng.uniform(222, 3, (N,), 0.001, 0.02)
+    bias = rng.uniform(222, 4, (N,), -1.0, 1.0).astype(np.float16)
+    ref = oracle.scaled_mm_i8(a, b, sa, sb, bias)
+    n0 = api.launch_count()
+    got = api.scaled_int8_mm(dev(a), dev(b).t(), dev(sa), dev(sb), dev(bias)).cpu().numpy()
+    assert api.launch_count() - n0 >= 3
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+    assert api.device_status() == 0
+
+
 def test_scaled_mm_padded_leading_dimensions_and_ragged_k(api, oracle):
     """Rows that are padded to a 16-byte multiple while K itself is not (K = 100, lda = ldb = 112): the streaming
     kernels walk K in whole 16-byte chunks and must not be chosen; the tensor tiles zero-fill the K tail."""
@@ -890,6 +946,65 @@ def test_fp16_streaming_kernel_token_split(api, oracle, m, n, k, parts):
     close_f16(split, oracle.gemm_f16_rcc(a, b))
     ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
     close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=-1, split_k=parts, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
+    assert api.device_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1024, 8192), (8, 1024, 28672), (24, 1000, 4096), (64, 2048, 8192), (1280, 12, 8192),
+                                   (40, 37, 2048), (5, 3000, 4104)])
+@pytest.mark.parametrize("kparts", [2, 4, 8])
+def test_fp16_streaming_kernel_k_split(api, oracle, m, n, k, kparts):
+    """K cut over a cluster of 2, 4 or 8 CTAs, partial blocks added in rank order through distributed shared memory:
+    within FP16 tolerance of the oracle (the summation order differs from the whole-K kernel), identical from run to
+    run, exact on small integers, both mappings, with and without a token split, alpha / beta."""
+    a = rng.normal(210, 0, (m, k), 0.05)
+    b = rng.normal(210, 1, (n, k), 0.05)
+    c0 = rng.normal(210, 2, (n, m), 1.0)
+    A, B = dev(a), dev(b)
+    ref = oracle.gemm_f16_rcc(a, b)
+    first = api.gemm_rcc_tile(A, B, 3, 16, kc=-kparts, split_k=1).cpu().numpy()
+    close_f16(first, ref)
+    assert np.array_equal(api.gemm_rcc_tile(A, B, 3, 16, kc=-kparts, split_k=1).cpu().numpy(), first)
+    if min(m, n) > 8:
+        both = api.gemm_rcc_tile(A, B, 3, 16, kc=-kparts, split_k=2).cpu().numpy()
+        assert np.array_equal(both, first)          # the token split changes no dot product
+    ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
+    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=-kparts, split_k=1, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
+    ai = rng.small_ints(211, 0, (m, k), lo=-1, hi=1)
+    bi = rng.small_ints(211, 1, (n, k))
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T.astype(np.float16)
+    assert np.array_equal(api.gemm_rcc_tile(dev(ai), dev(bi), 3, 16, kc=-kparts, split_k=1).cpu().numpy(), exact)
+    assert api.device_status() == 0
+
+
+def test_streaming_kernel_k_split_rule_and_int8(api, oracle, monkeypatch):
+    """The library's own rule (few rows: K parts until there are two CTAs per SM) on the shapes it is for, checked
+    through the public entry; INT8 accumulators stay bit-exact and the scaled epilogue bit-identical to the oracle under
+    every forced number of K parts."""
+    for (M, N, K) in [(1, 1024, 8192), (16, 1024, 28672), (32, 2048, 8192), (8, 1280, 8192)]:
+        x = rng.normal(212, 0, (M, K), 0.05)
+        w = rng.normal(212, 1, (N, K), 0.05)
+        got = api.gemm_rcc_pid(dev(w), dev(x), 1101, 1).cpu().numpy()          # Linear mapping: m = N rows of W
+        close_f16(got, oracle.gemm_f16_rcc(w, x))
+    M, N, K = 24, 1024, 8192
+    a = rng.int8_uniform(213, 0, (M, K))
+    b = rng.int8_uniform(213, 1, (N, K))
+    sa = rng.uniform(213, 2, (M,), 0.001, 0.02)
+    sb = rng.uniform(213, 3, (N,), 0.001, 0.02)
+    ref = oracle.scaled_mm_i8(a, b, sa, sb, None)
+    L = api.lib()
+    A, B, SA, SB = dev(a), dev(b), dev(sa), dev(sb)
+    for parts in ("0", "1", "2", "4", "8"):
+        monkeypatch.setenv("MOONPOLY_STREAM_KSPLIT", parts)
+        api.reload_env()
+        out = torch.empty((M, N), dtype=torch.float16, device=DEV)
+        rc = L.mp_scaled_mm_i8_tile(3, 16, 1, M, N, K, A.data_ptr(), K, B.data_ptr(), K, SA.data_ptr(), 0, SB.data_ptr(), 0,
+                                    None, out.data_ptr(), N, 0, None)
+        assert rc == 0, L.mp_last_error_string()
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy().view(np.uint16), ref.view(np.uint16)), parts
+        assert np.array_equal(api.gemm_rcc_pid(A, B, 1101, 1).cpu().numpy(), oracle.gemm_i8_rcc(a, b)), parts
+    monkeypatch.delenv("MOONPOLY_STREAM_KSPLIT")
+    api.reload_env()
     assert api.device_status() == 0
 
 
