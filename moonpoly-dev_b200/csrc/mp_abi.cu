@@ -591,8 +591,30 @@ int launch_simt_t(const SimtParams& sp, cudaStream_t stream) {
   return MP_OK;
 }
 
+// FP32: tiles of 64 / 128 on 16-byte aligned rows take the throughput kernel (same sums, same order)
 template <int TI, int TJ>
-int launch_simt_f32(const SimtParams& sp, cudaStream_t s) { return launch_simt_t<float, SEPI_F32, TI, TJ>(sp, s); }
+int launch_simt_f32(const SimtParams& sp, cudaStream_t stream) {
+  constexpr bool big = (TI == 64 || TI == 128) && (TJ == 64 || TJ == 128);
+  if constexpr (big) {
+    const bool aligned = sp.lda % 4 == 0 && sp.ldb % 4 == 0 && (reinterpret_cast<uintptr_t>(sp.A) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(sp.B) & 15) == 0;
+    if (aligned) {
+      dim3 grid((sp.m + TI - 1) / TI, (sp.n + TJ - 1) / TJ, sp.split_k);
+      sgemm_f32_kernel<TI / 16, TJ / 16><<<grid, 256, 0, stream>>>(sp);
+      MP_CUDA_TRY(cudaGetLastError());
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      if (sp.split_k > 1) {
+        const size_t total = (size_t)sp.m * sp.n;
+        const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 8);
+        simt_splitk_reduce_kernel<float, SEPI_F32><<<blocks, 256, 0, stream>>>(sp);
+        MP_CUDA_TRY(cudaGetLastError());
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+      }
+      return MP_OK;
+    }
+  }
+  return launch_simt_t<float, SEPI_F32, TI, TJ>(sp, stream);
+}
 
 int run_simt(const Problem& p, int ti, int tj, int split_k, void* workspace, size_t workspace_bytes,
              cudaStream_t stream) {

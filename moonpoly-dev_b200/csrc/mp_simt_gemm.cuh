@@ -161,6 +161,153 @@ simt_gemm_kernel(const SimtParams p) {
     }
 }
 
+// FP32 tile kernel for operands whose rows are 16-byte aligned (lda, ldb multiples of 4, aligned bases): the same
+// computation as simt_gemm_kernel<float, SEPI_F32, 16*RI, 16*RJ> with every sum formed in the same order (ascending
+// k, one fused multiply-add per term), built for throughput.  Global loads are 16 bytes along K, stored transposed
+// into shared memory ([k][row], conflict-free), the next K step of 16 is fetched into registers while the current
+// one is multiplied (two shared-memory buffers, one barrier per step), a thread owns RI x RJ outputs as rows
+// {4*tx..4*tx+3, 64+4*tx..} x columns {4*ty.., 64+4*ty..} so that both operands arrive as 16-byte shared-memory reads,
+// and the products go through packed FP32 FMAs (two neighbouring rows per instruction).
+template <int RI, int RJ>
+__global__ void __launch_bounds__(256)
+sgemm_f32_kernel(const SimtParams p) {
+  constexpr int TK = 16, TI = 16 * RI, TJ = 16 * RJ;
+  constexpr int NA = TI * 4 / 256, NB = TJ * 4 / 256;           // 16-byte global loads per thread and K step
+  static_assert((RI == 4 || RI == 8) && (RJ == 4 || RJ == 8), "tiles of 64 or 128");
+  __shared__ __align__(16) float As[2][TK][TI];
+  __shared__ __align__(16) float Bs[2][TK][TJ];
+  const float* A = reinterpret_cast<const float*>(p.A);
+  const float* B = reinterpret_cast<const float*>(p.B);
+  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+  const int i0 = blockIdx.x * TI, j0 = blockIdx.y * TJ;
+  const int k_begin = blockIdx.z * p.k_per_slice;
+  const int k_end = min(p.k, k_begin + p.k_per_slice);
+
+  float4 ra[NA], rb[NB];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int u = 0; u < NA; ++u) {
+      const int f = t + 256 * u, row = f % TI, kq = f / TI;
+      const int gi = i0 + row, gk = k0 + kq * 4;
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (gi < p.m) {
+        const float* src = A + (long long)gi * p.lda + gk;
+        if (gk + 3 < k_end) v = __ldg(reinterpret_cast<const float4*>(src));
+        else {
+          if (gk < k_end) v.x = __ldg(src);
+          if (gk + 1 < k_end) v.y = __ldg(src + 1);
+          if (gk + 2 < k_end) v.z = __ldg(src + 2);
+        }
+      }
+      ra[u] = v;
+    }
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      const int f = t + 256 * u, row = f % TJ, kq = f / TJ;
+      const int gj = j0 + row, gk = k0 + kq * 4;
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (gj < p.n) {
+        const float* src = B + (long long)gj * p.ldb + gk;
+        if (gk + 3 < k_end) v = __ldg(reinterpret_cast<const float4*>(src));
+        else {
+          if (gk < k_end) v.x = __ldg(src);
+          if (gk + 1 < k_end) v.y = __ldg(src + 1);
+          if (gk + 2 < k_end) v.z = __ldg(src + 2);
+        }
+      }
+      rb[u] = v;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int u = 0; u < NA; ++u) {
+      const int f = t + 256 * u, row = f % TI, kq = f / TI;
+      As[buf][kq * 4 + 0][row] = ra[u].x; As[buf][kq * 4 + 1][row] = ra[u].y;
+      As[buf][kq * 4 + 2][row] = ra[u].z; As[buf][kq * 4 + 3][row] = ra[u].w;
+    }
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      const int f = t + 256 * u, row = f % TJ, kq = f / TJ;
+      Bs[buf][kq * 4 + 0][row] = rb[u].x; Bs[buf][kq * 4 + 1][row] = rb[u].y;
+      Bs[buf][kq * 4 + 2][row] = rb[u].z; Bs[buf][kq * 4 + 3][row] = rb[u].w;
+    }
+  };
+
+  float2 acc[RI / 2][RJ];
+#pragma unroll
+  for (int a = 0; a < RI / 2; ++a)
+#pragma unroll
+    for (int b = 0; b < RJ; ++b) acc[a][b] = make_float2(0.0f, 0.0f);
+
+  int cur = 0;
+  if (k_begin < k_end) {
+    fetch(k_begin);
+    stash(0);
+  }
+  __syncthreads();
+  for (int k0 = k_begin; k0 < k_end; k0 += TK) {
+    const bool more = k0 + TK < k_end;
+    if (more) fetch(k0 + TK);
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      float2 a2[RI / 2];
+      float bv[RJ];
+#pragma unroll
+      for (int h = 0; h < RI / 4; ++h) {
+        const float4 v = *reinterpret_cast<const float4*>(&As[cur][kk][64 * h + 4 * tx]);
+        a2[2 * h] = make_float2(v.x, v.y);
+        a2[2 * h + 1] = make_float2(v.z, v.w);
+      }
+#pragma unroll
+      for (int h = 0; h < RJ / 4; ++h) {
+        const float4 v = *reinterpret_cast<const float4*>(&Bs[cur][kk][64 * h + 4 * ty]);
+        bv[4 * h] = v.x; bv[4 * h + 1] = v.y; bv[4 * h + 2] = v.z; bv[4 * h + 3] = v.w;
+      }
+#pragma unroll
+      for (int b = 0; b < RJ; ++b) {
+        const float2 bb = make_float2(bv[b], bv[b]);
+#pragma unroll
+        for (int a = 0; a < RI / 2; ++a) acc[a][b] = __ffma2_rn(a2[a], bb, acc[a][b]);
+      }
+    }
+    if (more) stash(cur ^ 1);
+    __syncthreads();
+    cur ^= 1;
+  }
+
+  // thread's rows: i0 + 64*h + 4*tx + e; columns: j0 + 64*h + 4*ty + e
+  const bool vec_out = p.split_k > 1 ? (p.m % 4 == 0)
+                                     : (p.c_stride_i == 1 && p.c_stride_j % 4 == 0 &&
+                                        (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+#pragma unroll
+  for (int b = 0; b < RJ; ++b) {
+    const int j = j0 + 64 * (b / 4) + 4 * ty + (b & 3);
+    if (j >= p.n) continue;
+#pragma unroll
+    for (int h = 0; h < RI / 4; ++h) {
+      const int i = i0 + 64 * h + 4 * tx;
+      if (i >= p.m) continue;
+      const float v[4] = {acc[2 * h][b].x, acc[2 * h][b].y, acc[2 * h + 1][b].x, acc[2 * h + 1][b].y};
+      if (p.split_k > 1) {
+        float* dst = reinterpret_cast<float*>(p.partials) + ((size_t)blockIdx.z * p.n + j) * (size_t)p.m + i;
+        if (vec_out && i + 3 < p.m) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        else
+          for (int e = 0; e < 4 && i + e < p.m; ++e) dst[e] = v[e];
+      } else if (vec_out && i + 3 < p.m) {
+        float* dst = reinterpret_cast<float*>(p.C) + (long long)i + (long long)j * p.c_stride_j;
+        float4 o = make_float4(p.alpha * v[0], p.alpha * v[1], p.alpha * v[2], p.alpha * v[3]);
+        if (p.beta != 0.0f) {
+          const float4 old = *reinterpret_cast<const float4*>(dst);
+          o.x += p.beta * old.x; o.y += p.beta * old.y; o.z += p.beta * old.z; o.w += p.beta * old.w;
+        }
+        *reinterpret_cast<float4*>(dst) = o;
+      } else {
+        for (int e = 0; e < 4 && i + e < p.m; ++e) simt_finish<SEPI_F32, float>(p, v[e], i + e, j);
+      }
+    }
+  }
+}
+
 // Sums split-K partials in slice order s = 0..S-1 and applies the epilogue.
 template <typename TAcc, int EPI>
 __global__ void __launch_bounds__(256)

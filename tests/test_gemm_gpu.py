@@ -228,6 +228,33 @@ def test_fp32_ctest_shapes_and_forced_splitk(api, m, n, k, monkeypatch):
     assert repr(api.select_plan(api.MP_FP32, m, n, k)) == free_plan     # the flag is re-read on every call
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 520, 1000), (129, 257, 1004), (128, 128, 16), (64, 1000, 4100), (513, 70, 2048),
+                                   (200, 200, 1001)])
+def test_fp32_throughput_tiles(api, oracle, m, n, k):
+    """The FP32 tile kernel for 16-byte aligned rows (64 / 128 tiles, packed FMAs, double-buffered shared memory): every
+    pid, ragged edges, K tails that are not a multiple of 16, forced split-K, alpha / beta; K = 1001 has unaligned rows
+    and takes the plain kernel.  Within 1e-4 of the oracle on uniform inputs, exact on small integers."""
+    a = rng.uniform(230, 0, (m, k), -1.0, 1.0)
+    b = rng.uniform(230, 1, (n, k), -1.0, 1.0)
+    c0 = rng.uniform(230, 2, (n, m), -1.0, 1.0)
+    ref = oracle.gemm_f32_rcc(a, b)
+    ref_ab = oracle.gemm_f32_rcc(a, b, 0.5, -1.5, c0)
+    A, B = dev(a), dev(b)
+    for pid in (0, 7, 15, 23, 31, 39):
+        for split in (1, 3):
+            c = api.gemm_rcc_pid(A, B, pid, split).cpu().numpy()
+            assert np.all(np.abs(c - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref))), (pid, split)
+        c = api.gemm_rcc_pid(A, B, pid, 1, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy()
+        assert np.all(np.abs(c - ref_ab) <= 1e-4 * np.maximum(1.0, np.abs(ref_ab))), pid
+    ai = rng.small_ints(231, 0, (m, k), dtype=np.float32)
+    bi = rng.small_ints(231, 1, (n, k), dtype=np.float32)
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T.astype(np.float32)
+    for pid in (23, 31):
+        assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), pid, 1).cpu().numpy(), exact), pid
+        assert np.array_equal(api.gemm_rcc_pid(dev(ai), dev(bi), pid, 2).cpu().numpy(), exact), pid
+    assert api.device_status() == 0
+
+
 def test_fp32_every_pid(api, oracle):
     m, n, k = 70, 150, 96
     a = rng.uniform(18, 0, (m, k), -1.0, 1.0)
