@@ -302,18 +302,18 @@ bool tma_compatible(const Problem& p) {
   return true;
 }
 
-// FP16 / INT8 operands whose rows miss the 16-byte alignment (K * element size not a multiple of 16, an odd leading
-// dimension or base address) cannot be described to TMA.  Entries that own their scratch copy such operands once
-// into zero-padded, aligned rows (K rounded up to 128 bytes: zeros add nothing to a dot product) and run the tensor
-// path on the copies; the CUDA-core tiles remain the fall-back when the copy cannot be allocated and for entries
-// whose memory the caller manages.  MOONPOLY_DISABLE_PAD=1 turns the copies off.
+// Operands whose rows miss the 16-byte alignment (K * element size not a multiple of 16, an odd leading dimension
+// or base address) cannot be described to TMA (FP16, INT8) or read with 16-byte loads (the FP32 tile kernels).
+// Entries that own their scratch copy such operands once into zero-padded, aligned rows (K rounded up to 128 bytes:
+// zeros add nothing to a dot product) and run the fast path on the copies; the plain CUDA-core tiles remain the
+// fall-back when the copy cannot be allocated and for entries whose memory the caller manages.
+// MOONPOLY_DISABLE_PAD=1 turns the copies off.
 bool pad_disabled() {
   const char* v = std::getenv("MOONPOLY_DISABLE_PAD");
   return v && v[0] && v[0] != '0';
 }
 
 bool pad_operands(Problem& p, cudaStream_t stream) {
-  if (p.dtype != MP_FP16 && p.dtype != MP_INT8) return false;
   if (p.k <= 0 || p.m <= 0 || p.n <= 0 || tma_compatible(p) || pad_disabled()) return false;
   const int eb = elem_bytes(p.dtype);
   const int per128 = 128 / eb;
@@ -324,7 +324,10 @@ bool pad_operands(Problem& p, cudaStream_t stream) {
   const auto launch = [&](const void* src, long long ld, void* dst, int rows) {
     const long long words = (long long)rows * (kp * eb / 16);
     const int grid = (int)std::min<long long>((words + 255) / 256, 148 * 16);
-    if (eb == 2)
+    if (eb == 4)
+      pad_rows_kernel<uint32_t><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(src), ld,
+                                                          reinterpret_cast<uint32_t*>(dst), rows, p.k, (int)kp);
+    else if (eb == 2)
       pad_rows_kernel<uint16_t><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(src), ld,
                                                           reinterpret_cast<uint16_t*>(dst), rows, p.k, (int)kp);
     else

@@ -255,6 +255,29 @@ def test_fp32_throughput_tiles(api, oracle, m, n, k):
     assert api.device_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(200, 300, 1001), (37, 1024, 1023), (5, 64, 3), (640, 130, 2050)])
+def test_fp32_unaligned_k_padded_copies(api, oracle, m, n, k, monkeypatch):
+    """FP32 rows that are not 16-byte aligned (K not a multiple of 4): the selector entry runs the aligned kernels on
+    zero-padded copies; the added terms are +0, so the result equals the plain kernel's to within the tolerance of the
+    oracle and is exact on small integers."""
+    a = rng.uniform(232, 0, (m, k), -1.0, 1.0)
+    b = rng.uniform(232, 1, (n, k), -1.0, 1.0)
+    ref = oracle.gemm_f32_rcc(a, b)
+    n0 = api.launch_count()
+    c = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    assert api.launch_count() - n0 >= 3
+    assert np.all(np.abs(c - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref)))
+    monkeypatch.setenv("MOONPOLY_DISABLE_PAD", "1")
+    c2 = api.gemm_rcc(dev(a), dev(b)).cpu().numpy()
+    monkeypatch.delenv("MOONPOLY_DISABLE_PAD")
+    assert np.all(np.abs(c2 - ref) <= 1e-4 * np.maximum(1.0, np.abs(ref)))
+    ai = rng.small_ints(233, 0, (m, k), dtype=np.float32)
+    bi = rng.small_ints(233, 1, (n, k), dtype=np.float32)
+    exact = (ai.astype(np.int64) @ bi.astype(np.int64).T).T.astype(np.float32)
+    assert np.array_equal(api.gemm_rcc(dev(ai), dev(bi)).cpu().numpy(), exact)
+    assert api.device_status() == 0
+
+
 def test_fp32_every_pid(api, oracle):
     m, n, k = 70, 150, 96
     a = rng.uniform(18, 0, (m, k), -1.0, 1.0)
