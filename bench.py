@@ -460,49 +460,12 @@ def run_ours(args, rank, world, local_rank):
     c_slot = {m: [torch.empty((N_DIM, m), dtype=torch.float16, device=dev) for _ in range(2)] for m in SWEEP_M if m >= PIPELINE_MIN_M}
     c_host2 = {m: [c_host[m], torch.empty((N_DIM, m), dtype=torch.float16).pin_memory()] for m in SWEEP_M if m >= PIPELINE_MIN_M}
 
-    # Small problems: the three host calls per GEMM (copy, GEMM, copy) cost more than the device work, so with
-    # --launch graph their copy -> GEMM -> copy chains are captured once per shape (memcpy nodes from / to the pinned
-    # host buffers, the library's kernel between them) and replayed; every replay moves the bytes again.
-    e2e_graphs = {}
-
-    def capture_e2e_graphs():
-        side = torch.cuda.Stream(device=dev)
-        side_st = ctypes.c_void_p(side.cuda_stream)
-        seq = 0
-        for m in SWEEP_M:
-            if m >= PIPELINE_MIN_M:
-                continue
-            calls = []
-            for i in range(max(2, reps_for(m) // 4)):
-                calls.append((api.MP_FP16, m, N_DIM, K_DIM, ctypes.c_void_p(a_stage[m].data_ptr()), 0,
-                              ctypes.c_void_p(weights[seq % WEIGHT_COPIES].data_ptr()), 1, ctypes.c_void_p(c_dev[m].data_ptr()), 1,
-                              ctypes.c_float(1.0), ctypes.c_float(0.0), side_st))
-                seq += 1
-
-            def chain():
-                for args_ in calls:
-                    a_stage[m].copy_(a_host[m], non_blocking=True)
-                    if mp_gemm(*args_) != 0:
-                        raise RuntimeError(L.mp_last_error_string().decode())
-                    c_host[m].copy_(c_dev[m], non_blocking=True)
-            side.wait_stream(stream)
-            with torch.cuda.stream(side):
-                chain()
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                chain()
-            e2e_graphs[m] = g
-        torch.cuda.synchronize()
-
     def sweep_e2e(events):
         for m in SWEEP_M:
             r = max(2, reps_for(m) // 4)
             if events is not None:
                 events[m][0].record(stream)
-            if m in e2e_graphs:
-                e2e_graphs[m].replay()
-            elif m < PIPELINE_MIN_M:
+            if m < PIPELINE_MIN_M:
                 for i in range(r):
                     counter[0] += 1
                     a_stage[m].copy_(a_host[m], non_blocking=True)
@@ -566,9 +529,6 @@ def run_ours(args, rank, world, local_rank):
         sweep_device(None)
     sweep_e2e(None)
     capture_graphs()
-    if use_graph:
-        capture_e2e_graphs()
-        sweep_e2e(None)
     sweep_main = sweep_graph if use_graph else sweep_device
     for _ in range(max(3, args.warmup)):
         sweep_main(None)
@@ -684,7 +644,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": geomean([e2e_tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "per_shape_us": {str(m): round(e2e_launch_ms[m] * 1e3, 2) for m in SWEEP_M},
-                    "note": "A copied from pinned host and C copied back to pinned host per GEMM, weight resident; M >= 256: two staging slots, uploads and downloads on their own streams overlap the GEMMs; M < 256: copy -> GEMM -> copy chains" + (" replayed from a CUDA graph per shape" if use_graph else " issued call by call")},
+                    "note": "A copied from pinned host and C copied back to pinned host per GEMM, weight resident; M >= 256: two staging slots, uploads and downloads on their own streams overlap the GEMMs; M < 256: copy -> GEMM -> copy on one stream (each small copy costs ~10 us of DMA latency: replaying the chain from a CUDA graph was measured and changes nothing)"},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
