@@ -134,6 +134,13 @@ int mp_debug_schedule(int dtype, int orient, int bn, int kc, int split_k, int m,
 int mp_debug_scratch_must_grow(size_t have_bytes, size_t have_counter_bytes, size_t want_counter_bytes,
                                size_t partial_bytes);
 
+/* Test aids (no counterpart in the reference; need no GPU): the launch shape the library's rules give the
+ * streaming warp-MMA kernel for an FP16 / INT8 problem with min(m, n) <= 64 -- out = {CTAs along the rows of the
+ * wide operand, K parts per cluster, token parts, grid size} -- and the FP32 tile kernel for a problem with
+ * 9 <= min(m, n) <= 64 -- out = {rows per CTA, K parts per cluster, grid size}. */
+int mp_debug_stream_launch(int dtype, int m, int n, int k, int out[4]);
+int mp_debug_f32_tile_launch(int m, int n, int k, int out[3]);
+
 /* get_gemm_workspace_size_fp16_row_col_col (core/fp16/fp16_rcc.cu:3306-3316), extended to every
  * pid and dtype: bytes of scratch mp_gemm_rcc_pid needs for this problem (0 when split_k == 1). */
 int mp_workspace_size(int dtype, int pid, int m, int n, int k, int split_k, size_t* bytes);

@@ -173,7 +173,7 @@ int get_pad_scratch(cudaStream_t stream, size_t bytes, uint8_t** out) {
   for (auto& e : g_pad_scratch)
     if (e.dev == dev && e.stream == stream) { s = &e; break; }
   if (s == nullptr || s->bytes < bytes) {
-    // a fresh buffer with head-room; the old one is kept (work already queued may still read it)
+    // a fresh buffer with head-room
     const size_t total = std::max<size_t>(round_up(bytes + bytes / 2, 1 << 20), 16 << 20);
     uint8_t* p = nullptr;
     if (cudaMalloc(&p, total) != cudaSuccess) {
@@ -184,6 +184,10 @@ int get_pad_scratch(cudaStream_t stream, size_t bytes, uint8_t** out) {
       g_pad_scratch.push_back(Scratch{dev, stream, p, total, 0});
       s = &g_pad_scratch.back();
     } else {
+      // only work of this stream reads the old copies: once it has drained, the buffer can go (operand copies can
+      // be gigabytes, so unlike the split-K scratch the old buffer is not kept)
+      if (cudaStreamSynchronize(stream) == cudaSuccess) cudaFree(s->ptr);
+      cudaGetLastError();
       s->ptr = p; s->bytes = total;
     }
   }
@@ -888,6 +892,31 @@ int stream_ksplit_rule(int R, int K, int elt, int sms) {
   return ks;
 }
 
+// Launch shape of the streaming kernel: K split first (it cuts both operands per CTA), then the token split for
+// what is still short of one wave.  forced_ck < 0 forces -forced_ck K parts, forced_tsplit > 0 the token parts.
+struct StreamShape { int row_ctas, k_split, t_split, t_per; };
+
+StreamShape stream_launch_shape(int R, int T, int K, int elt, int sms, int forced_ck, int forced_tsplit) {
+  StreamShape sh{};
+  int ks = forced_ck < 0 ? -forced_ck : g_stream_ksplit.load(std::memory_order_relaxed);
+  if (ks == 0) ks = stream_ksplit_rule(R, K, elt, sms);
+  while (ks > 1 && (long long)K * elt < 4096ll * ks) ks >>= 1;      // every warp keeps a full batch of loads
+  ks = std::max(1, std::min(ks, 8));
+  sh.k_split = ks;
+  sh.row_ctas = stream_row_ctas(R, sms, ks > 1 ? kStreamRows : 8);
+  // token split: parts of 8 or 16 rows of X per CTA, never an empty part
+  int ts = forced_tsplit > 0 ? forced_tsplit : g_stream_tsplit.load(std::memory_order_relaxed);
+  if (ts == 0) ts = stream_tsplit_rule(sh.row_ctas * ks, T, sms);
+  ts = std::max(1, std::min(ts, (T + 7) / 8));
+  sh.t_per = 0;
+  if (ts > 1) {
+    sh.t_per = ((T + ts - 1) / ts + 7) / 8 * 8;
+    ts = (T + sh.t_per - 1) / sh.t_per;
+  }
+  sh.t_split = ts;
+  return sh;
+}
+
 bool stream_compatible(const Problem& p) {
   if (!(p.dtype == MP_FP16 && p.epi == EPI_F16) && p.dtype != MP_INT8) return false;
   return std::min(p.m, p.n) <= 64 && std::min(p.m, p.n) >= 1 && p.k >= 16 &&
@@ -937,25 +966,11 @@ int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int for
       return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_SCALED>(*d, 8, cp, stream);
     }
   }
-  // K split first (it cuts both operands per CTA), then the token split for what is still short of one wave
-  const int elt = elem_bytes(p.dtype);
-  int ks = forced_ck < 0 ? -forced_ck : g_stream_ksplit.load(std::memory_order_relaxed);
-  if (ks == 0) ks = stream_ksplit_rule(sp.R, sp.K, elt, d->sms);
-  while (ks > 1 && (long long)sp.K * elt < 4096ll * ks) ks >>= 1;      // every warp keeps a full batch of loads
-  ks = std::max(1, std::min(ks, 8));
-  sp.k_split = ks;
-  const int row_ctas = stream_row_ctas(sp.R, d->sms, ks > 1 ? kStreamRows : 8);
-  // token split: parts of 8 or 16 rows of X per CTA, never an empty part
-  {
-    int ts = forced_tsplit > 0 ? forced_tsplit : g_stream_tsplit.load(std::memory_order_relaxed);
-    if (ts == 0) ts = stream_tsplit_rule(row_ctas * ks, sp.T, d->sms);
-    ts = std::max(1, std::min(ts, (sp.T + 7) / 8));
-    if (ts > 1) {
-      sp.t_per = ((sp.T + ts - 1) / ts + 7) / 8 * 8;
-      ts = (sp.T + sp.t_per - 1) / sp.t_per;
-    }
-    sp.t_split = ts;
-  }
+  const StreamShape shape = stream_launch_shape(sp.R, sp.T, sp.K, elem_bytes(p.dtype), d->sms, forced_ck, forced_tsplit);
+  sp.k_split = shape.k_split;
+  sp.t_split = shape.t_split;
+  sp.t_per = shape.t_per;
+  const int row_ctas = shape.row_ctas;
   if (p.dtype == MP_FP16 && p.bf16) return launch_stream_nt<STREAM_BF16, STREAM_EPI_F16>(sp, row_ctas, stream);
   if (p.dtype == MP_FP16) return launch_stream_nt<STREAM_F16, STREAM_EPI_F16>(sp, row_ctas, stream);
   if (p.epi == EPI_I32) return launch_stream_nt<STREAM_I8, STREAM_EPI_I32>(sp, row_ctas, stream);
@@ -1225,6 +1240,26 @@ int mp_cost_predict_pid(int dtype, int m, int n, int k, int* pid, float* ms) {
 int mp_debug_scratch_must_grow(size_t have_bytes, size_t have_counter_bytes, size_t want_counter_bytes,
                                size_t partial_bytes) {
   return scratch_must_grow(have_bytes, have_counter_bytes, want_counter_bytes, partial_bytes) ? 1 : 0;
+}
+
+int mp_debug_stream_launch(int dtype, int m, int n, int k, int out[4]) {
+  if (out == nullptr || (dtype != MP_FP16 && dtype != MP_INT8) || m < 1 || n < 1 || k < 1)
+    return fail(MP_ERR_INVALID_ARG, "mp_debug_stream_launch: FP16 or INT8, positive sizes");
+  const int R = std::max(m, n), T = std::min(m, n);
+  const StreamShape sh = stream_launch_shape(R, T, k, elem_bytes(dtype), mp::num_sms_for_model(), 0, 0);
+  out[0] = sh.row_ctas; out[1] = sh.k_split; out[2] = sh.t_split;
+  out[3] = sh.row_ctas * sh.k_split * sh.t_split;
+  return MP_OK;
+}
+
+int mp_debug_f32_tile_launch(int m, int n, int k, int out[3]) {
+  if (out == nullptr || m < 1 || n < 1 || k < 1) return fail(MP_ERR_INVALID_ARG, "mp_debug_f32_tile_launch: positive sizes");
+  SkinnyF32Params sp{};
+  sp.R = std::max(m, n); sp.T = std::min(m, n); sp.K = k;
+  int rows = 32, ks = 1;
+  tile_f32_rule(sp, mp::num_sms_for_model(), &rows, &ks);
+  out[0] = rows; out[1] = ks; out[2] = (sp.R + rows - 1) / rows * ks;
+  return MP_OK;
 }
 
 int mp_elite_fp16_pids(int* pids, int capacity) { return mp::elite_fp16_pids(pids, capacity); }
