@@ -984,12 +984,18 @@ bool skinny_f32_compatible(const Problem& p) {
          p.lda % 4 == 0 && p.ldb % 4 == 0 && al(p.A) && al(p.B);
 }
 
-template <int TMAX, int ROWS>
-int launch_skinny_f32(const SkinnyF32Params& sp, cudaStream_t stream) {
-  const int rows_per_cta = kSkinnyF32Warps * ROWS;
-  const int grid = (sp.R + rows_per_cta - 1) / rows_per_cta;
-  skinny_f32_kernel<TMAX, ROWS><<<grid, kSkinnyF32Warps * 32, 0, stream>>>(sp);
-  MP_CUDA_TRY(cudaGetLastError());
+template <int ROWS, int UNROLL>
+int launch_gemv_f32(const SkinnyF32Params& sp, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((sp.R + ROWS - 1) / ROWS));
+  cfg.blockDim = dim3(kGemvF32Warps * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_f32_kernel<ROWS, UNROLL>, sp));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return MP_OK;
 }
@@ -1082,9 +1088,9 @@ int run_skinny_f32(const Problem& p, cudaStream_t stream) {
     return rows == 32 ? launch_tile_f32_t<2, 4>(*d, sp, ks, stream)
          : rows == 16 ? launch_tile_f32_t<1, 4>(*d, sp, ks, stream) : launch_tile_f32_t<1, 2>(*d, sp, ks, stream);
   }
-  // two rows per warp halve the re-reads of X as long as there are rows enough to fill the GPU
-  const bool two = sp.R >= 4 * kSkinnyF32Warps * d->sms;
-  return two ? launch_skinny_f32<8, 2>(sp, stream) : launch_skinny_f32<8, 1>(sp, stream);
+  // at most 8 narrow rows: the streaming kernel; four rows per CTA once two rows per CTA are more than 16 CTAs per SM
+  if (sp.R >= 32 * d->sms) return launch_gemv_f32<4, 4>(sp, stream);
+  return launch_gemv_f32<2, 8>(sp, stream);
 }
 
 int check_rcc_args(int dtype, int m, int n, int k, const void* A, const void* B, const void* C) {

@@ -326,11 +326,7 @@ simt_splitk_reduce_kernel(const SimtParams p) {
 }  // namespace mp
 
 // ------------------------------------------------------------------------------------------------
-// FP32 streaming kernel for a narrow side of at most 8 rows: one warp per ROWS rows of the wide
-// operand W[R,K]; the lanes read the rows once with 16-byte loads and keep one accumulator per
-// (row, narrow row), the rows of X[T,K] come from L1/L2 (each X vector serves ROWS rows), and the
-// 32 partial sums of each output meet in a shuffle tree.  A small FP32 problem (37 x 1024 x 1024)
-// is one short wave of such warps instead of a few 64x64 tiles with a split-K pass behind them.
+// FP32 streaming kernel for a narrow side of at most 8 rows of X[T,K] against the rows of the wide operand W[R,K].
 //   out[r * stride_r + t * stride_t] = alpha * sum_k W[r,k] * X[t,k] + beta * out[...]
 // ------------------------------------------------------------------------------------------------
 namespace mp {
@@ -343,14 +339,19 @@ struct SkinnyF32Params {
   float alpha, beta;
 };
 
-constexpr int kSkinnyF32Warps = 4;
+constexpr int kGemvF32Warps = 8;
 
-template <int TMAX, int ROWS>
-__global__ void __launch_bounds__(kSkinnyF32Warps * 32)
-skinny_f32_kernel(const SkinnyF32Params p) {
+// A CTA of 8 warps owns ROWS rows of W; warp w owns the w-th eighth of K and keeps ROWS * UNROLL 16-byte loads of W
+// in flight per lane (the same arrangement that lets the FP16 streaming kernel fill the HBM queue), X comes from
+// L1/L2 (every X vector serves ROWS rows), the lanes' partial sums meet in a shuffle tree and the eight warps' in
+// shared memory, in warp order.  T <= 8.
+template <int ROWS, int UNROLL>
+__global__ void __launch_bounds__(kGemvF32Warps * 32)
+gemv_f32_kernel(const SkinnyF32Params p) {
+  __shared__ float red[kGemvF32Warps][ROWS][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r0 = (blockIdx.x * kSkinnyF32Warps + warp) * ROWS;
-  if (r0 >= p.R) return;
+  const int r0 = blockIdx.x * ROWS;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const float4* w[ROWS];
   bool ok[ROWS];
 #pragma unroll
@@ -359,44 +360,63 @@ skinny_f32_kernel(const SkinnyF32Params p) {
     w[i] = reinterpret_cast<const float4*>(p.W + (long long)(ok[i] ? r0 + i : r0) * p.ldw);
   }
   const int chunks = p.K >> 2;
-  float acc[ROWS][TMAX];
+  const int per_warp = (chunks + kGemvF32Warps - 1) / kGemvF32Warps;
+  const int c_begin = warp * per_warp, c_end = min(chunks, c_begin + per_warp);
+  float acc[ROWS][8];
 #pragma unroll
   for (int i = 0; i < ROWS; ++i)
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) acc[i][t] = 0.0f;
-  for (int c = lane; c < chunks; c += 32) {
-    float4 a[ROWS];
+    for (int t = 0; t < 8; ++t) acc[i][t] = 0.0f;
+  asm volatile("griddepcontrol.wait;" ::: "memory");          // the previous kernel of the stream may produce W or X
+  const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (int c0 = c_begin + lane; c0 < c_end; c0 += 32 * UNROLL) {
+    float4 a[ROWS][UNROLL];
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i) a[i] = __ldcs(w[i] + c);
+    for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) {
-      if (t < p.T) {
-        const float4 x = __ldg(reinterpret_cast<const float4*>(p.X + (long long)t * p.ldx) + c);
+      for (int i = 0; i < ROWS; ++i) a[i][u] = (c0 + 32 * u < c_end && ok[i]) ? __ldcs(w[i] + c0 + 32 * u) : zero4;
 #pragma unroll
-        for (int i = 0; i < ROWS; ++i) {
-          acc[i][t] = fmaf(a[i].x, x.x, acc[i][t]);
-          acc[i][t] = fmaf(a[i].y, x.y, acc[i][t]);
-          acc[i][t] = fmaf(a[i].z, x.z, acc[i][t]);
-          acc[i][t] = fmaf(a[i].w, x.w, acc[i][t]);
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + 32 * u;
+      if (c < c_end) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          if (t < p.T) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(p.X + (long long)t * p.ldx) + c);
+#pragma unroll
+            for (int i = 0; i < ROWS; ++i) {
+              acc[i][t] = fmaf(a[i][u].x, x.x, acc[i][t]);
+              acc[i][t] = fmaf(a[i][u].y, x.y, acc[i][t]);
+              acc[i][t] = fmaf(a[i][u].z, x.z, acc[i][t]);
+              acc[i][t] = fmaf(a[i][u].w, x.w, acc[i][t]);
+            }
+          }
         }
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < ROWS; ++i) {
+  for (int i = 0; i < ROWS; ++i)
 #pragma unroll
-    for (int t = 0; t < TMAX; ++t) {
+    for (int t = 0; t < 8; ++t) {
       if (t < p.T) {
         float v = acc[i][t];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        if (ok[i] && lane == (t & 31)) {
-          float* o = p.out + (long long)(r0 + i) * p.stride_r + (long long)t * p.stride_t;
-          float res = p.alpha * v;
-          if (p.beta != 0.0f) res += p.beta * (*o);
-          *o = res;
-        }
+        if (lane == 0) red[warp][i][t] = v;
       }
+    }
+  __syncthreads();
+  if (threadIdx.x < ROWS * 8) {
+    const int i = threadIdx.x >> 3, t = threadIdx.x & 7;
+    if (t < p.T && r0 + i < p.R) {
+      float v = red[0][i][t];
+#pragma unroll
+      for (int q = 1; q < kGemvF32Warps; ++q) v += red[q][i][t];
+      float* o = p.out + (long long)(r0 + i) * p.stride_r + (long long)t * p.stride_t;
+      float res = p.alpha * v;
+      if (p.beta != 0.0f) res += p.beta * (*o);
+      *o = res;
     }
   }
 }
