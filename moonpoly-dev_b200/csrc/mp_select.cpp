@@ -634,6 +634,28 @@ mp_plan select_fp16(int m, int n, int k, const LiveFlags& lf) {
       consider(best, MP_PATTERN_COMBINE, -1, 1, split_n, ms, e.p2_margin);
     }
   }
+
+  // (5) Library-native refinements of a cost-model choice (never of a measured row), with the tile kept:
+  //  - an RCC m that is not a multiple of 8 leaves the rows of C[n, m] unaligned; with the rows of A on the TMEM
+  //    lanes (orient 0) a warp still writes 64 contiguous bytes per column, the other way round every lane writes
+  //    2-byte pieces of 16 different rows (2047 x 2048 x 2048: 55 us against 20 us);
+  //  - 256-row tiles (pids 1200+) once a tile at least 192 wide fills half the GPU that way: a third less operand
+  //    traffic per FLOP (4096 x 4096 x 4104: 177 -> 135 us, 2297 x 5120 x 5120: 184 -> 96 us with both).
+  if (lf.gen && !matched && k % 8 == 0 && best.pid >= 0 && best.pid < 440 &&
+      (best.pattern == MP_PATTERN_SINGLE || best.pattern == MP_PATTERN_SPLITK)) {
+    const TileCfg c = tile_cfg(MP_FP16, best.pid);
+    if (c.valid && (c.orient == 0 || c.orient == 1) && c.bn >= 16 && c.bn <= 256 && c.bn % 16 == 0) {
+      const int orient = m % 8 != 0 ? 0 : c.orient;
+      const int P = orient == 0 ? m : n, Q = orient == 0 ? n : m;
+      const int sms = g_num_sms.load(std::memory_order_relaxed);
+      const bool wide = best.pattern == MP_PATTERN_SINGLE && c.bn >= 192 && P >= 512 &&
+                        cdiv(P, 256) * cdiv(Q, c.bn) >= sms / 2;
+      if (wide || orient != c.orient) {
+        best.pid = (wide ? 1200 : 1000) + 32 * orient + c.bn / 16;
+        if (wide) best.estimated_ms *= 0.88f;
+      }
+    }
+  }
   return best;
 }
 

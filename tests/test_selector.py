@@ -71,8 +71,17 @@ def test_measured_plan_table(api, monkeypatch):
     a = api.select_plan(api.MP_FP16, 1024, 4096, 4096)
     b = api.select_plan(api.MP_FP16, 1023, 4096, 4096)
     assert (a.pid, a.split_k) != (b.pid, b.split_k) or a.estimated_ms != b.estimated_ms
-    # a shape outside the table goes through the cost model
-    assert api.select_plan(api.MP_FP16, 500, 3000, 4096).pid < 1000
+    # a shape outside the table goes through the cost model ...
+    assert api.select_plan(api.MP_FP16, 2048, 2048, 2048).pid < 1000
+    # ... whose choice is refined, tile kept: rows of A on the TMEM lanes when m leaves the rows of C unaligned,
+    # 256-row tiles once a wide tile fills half the GPU that way
+    base = api.select_plan(api.MP_FP16, 2048, 2048, 2048)
+    odd = api.select_plan(api.MP_FP16, 2047, 2048, 2048)
+    assert 1000 <= odd.pid < 1032 and api.pid_info(api.MP_FP16, odd.pid)[0][1] == 128            # orient 0: m on the 128 side
+    assert sorted(api.pid_info(api.MP_FP16, odd.pid)[0][:2]) == sorted(api.pid_info(api.MP_FP16, base.pid)[0][:2])
+    big = api.select_plan(api.MP_FP16, 4096, 4096, 4104)
+    assert 1200 <= big.pid < 1264 and 256 in api.pid_info(api.MP_FP16, big.pid)[0][:2]
+    assert 1200 <= api.select_plan(api.MP_FP16, 2297, 5120, 5120).pid < 1232                        # both: orient 0, 256 rows
     # switching the table off is honoured on the next call
     monkeypatch.setenv("MOONPOLY_ENABLE_GENERATED_SELECTOR", "0")
     assert api.select_plan(api.MP_FP16, 1, 4096, 4096).pid < 1000
