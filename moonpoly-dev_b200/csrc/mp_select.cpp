@@ -641,11 +641,17 @@ mp_plan select_fp16(int m, int n, int k, const LiveFlags& lf) {
   //    2-byte pieces of 16 different rows (2047 x 2048 x 2048: 55 us against 20 us);
   //  - 256-row tiles (pids 1200+) once a tile at least 192 wide fills half the GPU that way: a third less operand
   //    traffic per FLOP (4096 x 4096 x 4104: 177 -> 135 us, 2297 x 5120 x 5120: 184 -> 96 us with both).
+  //  - at most 16 rows on the narrow side: the streaming kernel (pid 1101), which the measured tables pick for every
+  //    such bucket of every tuned layer (3 x 5120 x 5120: 10 us; the best tile needs a split-K pass).
+  if (lf.gen && !matched && k % 8 == 0 && k >= 16 && std::min(m, n) <= 16 && best.pattern != MP_PATTERN_COMBINE) {
+    const double bytes = 2.0 * ((double)m * k + (double)n * k + (double)m * n);
+    return mp_plan{MP_PATTERN_SINGLE, 1101, 1, 0, (float)(bytes / 6.0e9 + 2.5e-3)};
+  }
   if (lf.gen && !matched && k % 8 == 0 && best.pid >= 0 && best.pid < 440 &&
       (best.pattern == MP_PATTERN_SINGLE || best.pattern == MP_PATTERN_SPLITK)) {
     const TileCfg c = tile_cfg(MP_FP16, best.pid);
     if (c.valid && (c.orient == 0 || c.orient == 1) && c.bn >= 16 && c.bn <= 256 && c.bn % 16 == 0) {
-      const int orient = m % 8 != 0 ? 0 : c.orient;
+      const int orient = (m % 8 != 0 && m >= 128) ? 0 : c.orient;      // a short m belongs on the bn side whatever its alignment
       const int P = orient == 0 ? m : n, Q = orient == 0 ? n : m;
       const int sms = g_num_sms.load(std::memory_order_relaxed);
       const bool wide = best.pattern == MP_PATTERN_SINGLE && c.bn >= 192 && P >= 512 &&
