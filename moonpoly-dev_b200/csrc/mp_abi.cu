@@ -134,6 +134,12 @@ bool scratch_must_grow(size_t have_bytes, size_t have_counters, size_t want_coun
   return have_counters < want_counters || have_bytes < std::max(have_counters, want_counters) + partial_bytes;
 }
 
+bool stream_is_capturing(cudaStream_t stream) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) { cudaGetLastError(); return false; }
+  return st != cudaStreamCaptureStatusNone;
+}
+
 int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes, uint8_t** counters,
                 uint8_t** partials) {
   int dev = 0;
@@ -144,7 +150,11 @@ int get_scratch(cudaStream_t stream, size_t counter_bytes, size_t partial_bytes,
     if (e.dev == dev && e.stream == stream) { s = &e; break; }
   const size_t want_counters = std::max<size_t>(round_up(counter_bytes, 256), 1 << 16);
   if (s == nullptr || scratch_must_grow(s->bytes, s->counter_bytes, want_counters, partial_bytes)) {
-    // Grow: a fresh, larger buffer.  The old one is kept (work already queued may still use it).
+    // Grow: a fresh, larger buffer.  The old one is kept (work already queued may still use it).  Allocating would
+    // invalidate a stream capture in progress: refuse instead, the caller runs the shape once before capturing.
+    if (stream_is_capturing(stream))
+      return fail(MP_ERR_WORKSPACE, "the split-K scratch must grow, which cannot happen while the stream is being "
+                                    "captured: run this shape once before the capture");
     const size_t cb = std::max(want_counters, s ? s->counter_bytes : 0);
     const size_t total = cb + std::max<size_t>(round_up(partial_bytes, 1 << 20) * 2, 8 << 20);
     uint8_t* p = nullptr;
@@ -173,7 +183,8 @@ int get_pad_scratch(cudaStream_t stream, size_t bytes, uint8_t** out) {
   for (auto& e : g_pad_scratch)
     if (e.dev == dev && e.stream == stream) { s = &e; break; }
   if (s == nullptr || s->bytes < bytes) {
-    // a fresh buffer with head-room
+    // a fresh buffer with head-room; never while the stream is being captured (the call then keeps the plain tiles)
+    if (stream_is_capturing(stream)) return MP_ERR_WORKSPACE;
     const size_t total = std::max<size_t>(round_up(bytes + bytes / 2, 1 << 20), 16 << 20);
     uint8_t* p = nullptr;
     if (cudaMalloc(&p, total) != cudaSuccess) {

@@ -1,4 +1,5 @@
 """Parity of the CUDA path with the CPU oracle, through the C ABI (needs a B200)."""
+import ctypes
 import os
 
 import numpy as np
@@ -1081,4 +1082,56 @@ def test_int8_scaled_streaming_kernel_token_split(api, oracle, monkeypatch):
         assert np.array_equal(acc, oracle.gemm_i8_rcc(a, b)), parts
     monkeypatch.delenv("MOONPOLY_STREAM_TSPLIT")
     api.reload_env()
+    assert api.device_status() == 0
+
+
+def test_scratch_never_grows_inside_a_stream_capture(api, oracle):
+    """A stream that is being captured must not see an allocation: a split-K call whose scratch does not exist yet is
+    refused with the workspace error (the capture stays valid), an unaligned-K call keeps the plain tiles instead of
+    allocating padded copies, and the same calls made once before the capture are captured and replay correctly."""
+    L = api.lib()
+    m, n, k = 2048, 512, 8192            # 8 slices of 2048 x 512 partial sums: 33 MB of scratch, more than any stream holds
+    a = rng.normal(240, 0, (m, k), 0.05)
+    b = rng.normal(240, 1, (n, k), 0.05)
+    au = rng.normal(241, 0, (130, 1001), 0.05)
+    bu = rng.normal(241, 1, (70, 1001), 0.05)
+    A, B, AU, BU = dev(a), dev(b), dev(au), dev(bu)
+    C = torch.empty((n, m), dtype=torch.float16, device=DEV)
+    CU = torch.empty((70, 130), dtype=torch.float16, device=DEV)
+    side = torch.cuda.Stream()
+    st = ctypes.c_void_p(side.cuda_stream)
+
+    def split_call():
+        return L.mp_gemm_rcc_pid(api.MP_FP16, 400, 8, m, n, k, A.data_ptr(), B.data_ptr(), C.data_ptr(), 1.0, 0.0, None, 0, st)
+
+    def unaligned_call():
+        return L.mp_gemm_rcc(api.MP_FP16, 130, 70, 1001, AU.data_ptr(), BU.data_ptr(), CU.data_ptr(), 1.0, 0.0, st)
+
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        rc_split = split_call()               # this stream has no scratch yet: refused, nothing allocated
+        n0 = api.launch_count()
+        rc_un = unaligned_call()              # no padded copies: one plain-tile launch
+        launches_un = api.launch_count() - n0
+    assert rc_split == 5 and b"captur" in L.mp_last_error_string()          # MP_ERR_WORKSPACE
+    assert rc_un == 0 and launches_un <= 2
+    g.replay()
+    torch.cuda.synchronize()
+    close_f16(CU.cpu().numpy(), oracle.gemm_f16_rcc(au, bu))
+    # warmed up outside a capture, both are captured as they run
+    with torch.cuda.stream(side):
+        assert split_call() == 0 and unaligned_call() == 0
+    torch.cuda.synchronize()
+    C.zero_(); CU.zero_()
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2, stream=side):
+        assert split_call() == 0
+        n0 = api.launch_count()
+        assert unaligned_call() == 0
+        assert api.launch_count() - n0 >= 3   # the padded copies and the GEMM
+    g2.replay()
+    torch.cuda.synchronize()
+    close_f16(C.cpu().numpy(), oracle.gemm_f16_rcc(a, b))
+    close_f16(CU.cpu().numpy(), oracle.gemm_f16_rcc(au, bu))
     assert api.device_status() == 0
