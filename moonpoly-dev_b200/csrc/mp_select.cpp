@@ -749,10 +749,12 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
     }
     // the measured scaled-matmul plans describe the same int8 main loop on the same (m, n, k): use them for the
     // plain int32-output GEMM as well (the epilogues differ, the ranking of the tiles hardly does)
+    bool int8_row = false;
     if (lf.gen && lf.int8_force <= 1 && k % 16 == 0) {
       for (int i = 0; i < kScaledPlanCount; ++i) {
         const ScaledPlanRow& r = kScaledPlans[i];
         if (r.n != n || r.k != k || m < r.m_lo || m > r.m_hi) continue;
+        int8_row = true;
         if (r.orient == 3) {
           if (std::min(m, n) <= 64) plan = mp_plan{MP_PATTERN_SINGLE, 1101, 1, 0, r.ms};
         } else {
@@ -761,6 +763,20 @@ mp_plan select_plan(int dtype, int m, int n, int k) {
           plan = mp_plan{S > 1 ? MP_PATTERN_SPLITK : MP_PATTERN_SINGLE, pid, S, 0, r.ms};
         }
         break;
+      }
+    }
+    // a cost-model choice with a tile at least 192 wide moves to its 256-row version once that fills half the GPU
+    // (the same refinement as for FP16: a third less operand traffic per MAC)
+    if (lf.gen && !int8_row && lf.int8_force <= 1 && k % 16 == 0 && plan.pattern == MP_PATTERN_SINGLE && plan.pid >= 0 &&
+        plan.pid < 46) {
+      const TileCfg c = tile_cfg(MP_INT8, plan.pid);
+      if (c.valid && (c.orient == 0 || c.orient == 1) && c.bn >= 192 && c.bn <= 256 && c.bn % 16 == 0) {
+        const int P = c.orient == 0 ? m : n, Q = c.orient == 0 ? n : m;
+        const int sms = g_num_sms.load(std::memory_order_relaxed);
+        if (P >= 512 && cdiv(P, 256) * cdiv(Q, c.bn) >= sms / 2) {
+          plan.pid = 1200 + 32 * c.orient + c.bn / 16;
+          plan.estimated_ms *= 0.88f;
+        }
       }
     }
   }
@@ -820,6 +836,11 @@ ScaledCfg scaled_mm_select(int M, int N, int K) {
     }
   }
   best.stream = int8_prefers_stream(std::min(M, N), std::max(M, N), K);
+  {
+    // 256-row tiles once a tile at least 192 wide fills half the GPU that way (measured rows below may override)
+    const int P = best.orient == 0 ? M : N, Q = best.orient == 0 ? N : M;
+    if (best.split_k == 1 && best.bn >= 192 && P >= 512 && ceil_div(P, 256) * ceil_div(Q, best.bn) >= sms / 2) best.xm = 2;
+  }
   // measured rows win over the model; `id` stays the model's choice among the six public configurations
   if (env_flag("MOONPOLY_ENABLE_GENERATED_SELECTOR", true)) {
     for (int i = 0; i < kScaledPlanCount; ++i) {
