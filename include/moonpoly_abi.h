@@ -109,11 +109,12 @@ int mp_gemm_rcc_pid_static_scratch(int dtype, int pid, int split_k, int m, int n
  * tiles n by bn; orient 1 puts the rows of B there and tiles m by bn.  bn: multiple of 16 in
  * [16,256].  kc: K blocks (of 128 bytes) per pipeline stage, 1, 2 or 4; 0 lets the library choose.
  * orient 2 and 3 select the streaming kernels instead (2: FP16 CUDA-core, narrow side <= 8 rows;
- * 3: FP16 / INT8 warp-MMA, narrow side <= 64 rows); bn, kc and split_k are ignored there and
- * MP_ERR_INVALID_ARG is returned when the problem does not fit the kernel.  orient 4 and 5 are
- * orient 0 and 1 with 256-row tiles (two 128-row halves share every bn-wide tile of the other
- * operand; single K slice).
- * The refit tool (per-tile k_iter sweeps) and the profiling driver use it. */
+ * 3: FP16 / INT8 warp-MMA, narrow side <= 64 rows); bn is ignored there, for orient 3 kc = -1, -2,
+ * -4, -8 forces that many K parts per cluster and split_k > 1 that many token parts (0 / 1: the
+ * library's rules), and MP_ERR_INVALID_ARG is returned when the problem does not fit the kernel.
+ * orient 4 and 5 are orient 0 and 1 with 256-row tiles (two 128-row halves share every bn-wide
+ * tile of the other operand).
+ * The refit tool (per-tile k_iter sweeps) and the tests use it. */
 int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, int n, int k,
                      const void* A, const void* B, void* C, float alpha, float beta, void* stream);
 

@@ -77,8 +77,6 @@ struct DeviceState {
   int cc = 0;
   bool attrs[9] = {false, false, false, false, false, false, false, false, false};
   bool tile_f32_attrs[12] = {};
-  bool stream_attrs[16] = {false, false, false, false, false, false, false, false, false, false, false, false,
-                           false, false, false, false};
 };
 constexpr int kMaxDevices = 32;
 DeviceState g_dev[kMaxDevices];
@@ -796,85 +794,6 @@ int stream_tsplit_from_env() {
 }
 std::atomic<int> g_stream_tsplit{stream_tsplit_from_env()};
 
-// Cluster-K variant of the streaming kernel: a cluster of `ck` CTAs shares a block of W rows and cuts K.
-// Measured on B200 it loses to the one-CTA-per-row-block kernel on every benchmark shape but one (its tiles run
-// one after the other, so every tile pays a full memory latency: M = 32, N = K = 4096: 24.6 us against 11.2 us;
-// only (1, 1024, 28672) gains, 17.3 us against 24.1 us), so the library never picks it by itself unless
-// MOONPOLY_ENABLE_STREAM_CLUSTER=1; the tuning entry reaches it with an explicit number of K ranges.
-bool stream_cluster_from_env() {
-  const char* v = std::getenv("MOONPOLY_ENABLE_STREAM_CLUSTER");
-  return v && v[0] && v[0] != '0';
-}
-std::atomic<bool> g_use_stream_cluster{stream_cluster_from_env()};
-
-struct StreamCkChoice { int ck, row_blocks; };
-
-// ck: every warp should own at least one full batch of loads (8 K blocks of 64 bytes) of its CTA's K range, and
-// a CTA should hold about 4 T rows so that its share of X is small against its share of W; row blocks: one CTA
-// per SM where the rows allow it, never more than kCkMaxTiles tiles per CTA.
-StreamCkChoice choose_stream_ck(int R, int T, int K, int elt, int sms, int forced_ck) {
-  const int max_ck_by_k = std::max(1, (int)(((long long)K * elt) / 4096));
-  int ck = 1;
-  if (forced_ck > 0) {
-    ck = forced_ck;
-  } else {
-    const int want_rows = std::min(kCkMaxTiles * kStreamRows, std::max(kStreamRows, 4 * T));
-    while (ck < 8 && ck * 2 <= max_ck_by_k && (long long)R * ck / sms < want_rows) ck *= 2;
-  }
-  int row_blocks = std::max(1, sms / ck);
-  row_blocks = std::max(row_blocks, (R + kCkMaxTiles * kStreamRows - 1) / (kCkMaxTiles * kStreamRows));
-  row_blocks = std::min(row_blocks, std::max(1, R));
-  return {ck, row_blocks};
-}
-
-template <int KIND, int EPI, int NT, int UNROLL>
-int launch_stream_ck_t(DeviceState& d, int attr_slot, StreamCkParams cp, cudaStream_t stream) {
-  auto kern = stream_mma_ck_kernel<KIND, EPI, NT, UNROLL>;
-  constexpr int TP = NT * 8 + 1;
-  const size_t fixed = (size_t)(kCkMaxTiles + kStreamWarps) * kStreamRows * TP * 4 + 16;
-  const int elt = KIND == STREAM_I8 ? 1 : 2;
-  const long long chunks = (long long)cp.s.K * elt / 16, blocks = (chunks + 3) / 4;
-  const long long max_cta_chunks = 4 * ((blocks + cp.ck - 1) / cp.ck);
-  cp.x_row_bytes = (int)((max_cta_chunks + 1) * 16);
-  const size_t x_bytes = (size_t)cp.s.T * cp.x_row_bytes;
-  cp.stage_x = fixed + x_bytes <= (size_t)kSmemBudget ? 1 : 0;
-  const size_t smem = fixed + (cp.stage_x ? x_bytes : 0);
-  if (!d.stream_attrs[attr_slot]) {
-    MP_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
-    d.stream_attrs[attr_slot] = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(cp.row_blocks * cp.ck));
-  cfg.blockDim = dim3(kStreamWarps * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  int na = 0;
-  if (g_use_pdl) {
-    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
-  }
-  attr[na].id = cudaLaunchAttributeClusterDimension;
-  attr[na].val.clusterDim.x = (unsigned)cp.ck;
-  attr[na].val.clusterDim.y = 1;
-  attr[na].val.clusterDim.z = 1;
-  ++na;
-  cfg.attrs = attr;
-  cfg.numAttrs = na;
-  MP_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, cp));
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return MP_OK;
-}
-
-template <int KIND, int EPI>
-int launch_stream_ck_nt(DeviceState& d, int base_slot, const StreamCkParams& cp, cudaStream_t stream) {
-  if (cp.s.T <= 8) return launch_stream_ck_t<KIND, EPI, 1, 8>(d, base_slot + 0, cp, stream);
-  if (cp.s.T <= 16) return launch_stream_ck_t<KIND, EPI, 2, 8>(d, base_slot + 1, cp, stream);
-  if (cp.s.T <= 32) return launch_stream_ck_t<KIND, EPI, 4, 8>(d, base_slot + 2, cp, stream);
-  return launch_stream_ck_t<KIND, EPI, 8, 4>(d, base_slot + 3, cp, stream);
-}
-
 // When to split the tokens.  Measured on B200 (Linear mapping, FP16): with N = K = 4096 the repeated reads of W
 // cost more than the narrower X saves (M = 16: 12.2 us split in two against 8.3 us; M = 32: 15.2 against 11.1),
 // and the same holds for every layer with enough rows to give each SM a CTA.  The split pays only when the rows are
@@ -935,8 +854,7 @@ bool stream_compatible(const Problem& p) {
          tma_compatible(p);      // same rule: 16-byte aligned rows
 }
 
-// forced_ck: 0 = the library decides; > 0 = the staged cluster-K kernel with that many K ranges (1, 2, 4 or 8);
-// < 0 = the streaming kernel with -forced_ck K parts (-1: whole-K CTAs).
+// forced_ck: 0 = the library decides; < 0 = -forced_ck K parts (-1: whole-K CTAs).
 int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int forced_tsplit = 0) {
   DeviceState* d = nullptr;
   if (int rc = device_state(&d)) return rc;
@@ -960,23 +878,6 @@ int run_stream(const Problem& p, cudaStream_t stream, int forced_ck = 0, int for
   sp.bias = p.bias; sp.out_bf16 = p.out_bf16;
   sp.num_peers = p.num_peers;
   for (int i = 0; i < p.num_peers; ++i) sp.peer_out[i] = p.peers[i];
-  // The cluster-K kernel pays when the narrow side is wide enough for X to weigh against W (T > 8), or when the
-  // rows are too few to give every SM two CTAs of the plain kernel; it needs a K range per warp worth streaming.
-  if (forced_ck >= 0 && (forced_ck > 0 || g_use_stream_cluster.load(std::memory_order_relaxed))) {
-    const int elt = elem_bytes(p.dtype);
-    const StreamCkChoice ch = choose_stream_ck(sp.R, sp.T, sp.K, elt, d->sms, forced_ck);
-    const bool few_rows = sp.R < 8 * 2 * d->sms;
-    const bool enough_k = (long long)sp.K * elt >= 4096ll * ch.ck;
-    const bool rows_fit = (sp.R + ch.row_blocks - 1) / ch.row_blocks <= kCkMaxTiles * kStreamRows;
-    if (rows_fit && (forced_ck > 0 || (enough_k && (sp.T > 8 || (few_rows && ch.ck > 1))))) {
-      StreamCkParams cp{};
-      cp.s = sp; cp.ck = ch.ck; cp.row_blocks = ch.row_blocks;
-      if (p.dtype == MP_FP16 && p.bf16) return launch_stream_ck_nt<STREAM_BF16, STREAM_EPI_F16>(*d, 12, cp, stream);
-      if (p.dtype == MP_FP16) return launch_stream_ck_nt<STREAM_F16, STREAM_EPI_F16>(*d, 0, cp, stream);
-      if (p.epi == EPI_I32) return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_I32>(*d, 4, cp, stream);
-      return launch_stream_ck_nt<STREAM_I8, STREAM_EPI_SCALED>(*d, 8, cp, stream);
-    }
-  }
   const StreamShape shape = stream_launch_shape(sp.R, sp.T, sp.K, elem_bytes(p.dtype), d->sms, forced_ck, forced_tsplit);
   sp.k_split = shape.k_split;
   sp.t_split = shape.t_split;
@@ -1208,7 +1109,6 @@ int mp_reload_env(void) {
   mp::reload_env();
   g_use_streamk.store(streamk_from_env(), std::memory_order_relaxed);
   g_use_cluster_splitk.store(cluster_splitk_from_env(), std::memory_order_relaxed);
-  g_use_stream_cluster.store(stream_cluster_from_env(), std::memory_order_relaxed);
   g_stream_tsplit.store(stream_tsplit_from_env(), std::memory_order_relaxed);
   g_stream_ksplit.store(stream_ksplit_from_env(), std::memory_order_relaxed);
   return MP_OK;
@@ -1336,11 +1236,11 @@ int mp_gemm_rcc_tile(int dtype, int orient, int bn, int kc, int split_k, int m, 
     if (!gemv_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the skinny kernel needs FP16, min(m,n) <= 8 and 16-byte aligned rows");
     return run_gemv(pg, reinterpret_cast<cudaStream_t>(stream));
   }
-  if (orient == 3) {            // the streaming warp-MMA kernels (bn unused; split_k = K ranges of the cluster-K variant)
+  if (orient == 3) {            // the streaming warp-MMA kernel (bn unused; kc = -K parts, split_k = token parts)
     const Problem pg = rcc_problem(dtype, m, n, k, A, B, C, alpha, beta);
     if (!stream_compatible(pg)) return fail(MP_ERR_INVALID_ARG, "the streaming kernel needs FP16 or INT8, min(m,n) <= 64 and 16-byte aligned rows");
-    if (kc != 0 && kc != 1 && kc != 2 && kc != 4 && kc != 8 && kc != -1 && kc != -2 && kc != -4 && kc != -8)
-      return fail(MP_ERR_INVALID_ARG, "streaming kernel: kc selects the K ranges of the staged cluster variant (1, 2, 4, 8), -1 / -2 / -4 / -8 the streaming kernel with that many K parts, 0 lets the library choose");
+    if (kc != 0 && kc != -1 && kc != -2 && kc != -4 && kc != -8)
+      return fail(MP_ERR_INVALID_ARG, "streaming kernel: kc = -1 / -2 / -4 / -8 selects that many K parts, 0 lets the library choose");
     return run_stream(pg, reinterpret_cast<cudaStream_t>(stream), kc, split_k > 1 ? split_k : 0);
   }
   const int xm = (orient == 4 || orient == 5) ? 2 : 1;       // orient 4 / 5: orient 0 / 1 with 256-row tiles

@@ -305,199 +305,4 @@ stream_mma_kernel(const StreamParams p) {
 }
 
 
-// ------------------------------------------------------------------------------------------------
-// Cluster-K variant.  The kernel above gives every CTA whole rows of W, so every CTA walks all of K
-// and pulls all of X[T,K] through L1/L2 once per 16-row tile: with T >= 16 that traffic (T*K*e bytes
-// per CTA) is as large as the W stream itself, and with few rows (R ~ 1024) there are not enough CTAs
-// to fill the GPU.  Here a thread-block cluster of CK CTAs shares one block of rows and cuts K into CK
-// contiguous ranges: each CTA stages only its K range of X in shared memory (padded rows, so the B
-// fragments load without bank conflicts), streams its K range of W against it for up to kCkMaxTiles
-// 16-row tiles, and keeps the 16 x T partial blocks in shared memory.  At the end the CTAs of the
-// cluster read each other's partial blocks through distributed shared memory (plain loads) and rank
-// r finishes the r-th share of the rows, adding the CK partials in rank order: results are
-// deterministic.  The only waits are hardware cluster barriers that every thread reaches.
-// ------------------------------------------------------------------------------------------------
-constexpr int kCkMaxTiles = 8;         // 16-row tiles per CTA (rows per CTA <= 128)
-
-struct StreamCkParams {
-  StreamParams s;
-  int ck;              // CTAs per cluster = K ranges
-  int row_blocks;      // gridDim.x / ck
-  int stage_x;         // 1: this CTA's K range of X is staged in shared memory
-  int x_row_bytes;     // padded bytes per staged X row (a multiple of 16, odd multiple keeps the banks apart)
-};
-
-template <int KIND, int EPI, int NT, int UNROLL>
-__global__ void __launch_bounds__(kStreamWarps * 32, 1)
-stream_mma_ck_kernel(const StreamCkParams cp) {
-  const StreamParams& p = cp.s;
-  extern __shared__ __align__(16) uint8_t ck_smem[];
-  constexpr int kElt = KIND == STREAM_I8 ? 1 : 2;
-  constexpr int kChunkElems = 16 / kElt;
-  constexpr int TP = NT * 8 + 1;                         // padded width of a partial block row
-  // shared memory: part[kCkMaxTiles][16][TP] | red[8][16][TP] | staged X rows
-  uint32_t* part = reinterpret_cast<uint32_t*>(ck_smem);
-  uint32_t* red = part + kCkMaxTiles * kStreamRows * TP;
-  uint8_t* xs = reinterpret_cast<uint8_t*>(red + kStreamWarps * kStreamRows * TP);
-  xs = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(xs) + 15) & ~uintptr_t(15));
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t4 = lane & 3;
-  const int rank = (int)stream_cluster_rank();
-  const int rb = (int)blockIdx.x / cp.ck;
-  const int r_begin = (int)((long long)rb * p.R / cp.row_blocks);
-  const int r_end = (int)((long long)(rb + 1) * p.R / cp.row_blocks);
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const char* Wb = reinterpret_cast<const char*>(p.W);
-  const char* Xb = reinterpret_cast<const char*>(p.X);
-
-  // this CTA's K range, in K blocks of four 16-byte chunks
-  const int chunks = p.K / kChunkElems;
-  const int blocks = (chunks + 3) >> 2;
-  const int cta_blk0 = (int)((long long)rank * blocks / cp.ck);
-  const int cta_blk1 = (int)((long long)(rank + 1) * blocks / cp.ck);
-  const int per_warp = (cta_blk1 - cta_blk0 + kStreamWarps - 1) / kStreamWarps;
-  const int blk_begin = cta_blk0 + warp * per_warp;
-  const int blk_end = min(cta_blk1, blk_begin + per_warp);
-
-  // pull this CTA's part of W towards L2 while the previous kernel of the stream drains (a hint only)
-  {
-    const int b0 = cta_blk0 * 64, b1 = min(cta_blk1 * 64, p.K * kElt);          // byte range inside a row
-    const int lines_per_row = (b1 - b0 + 127) >> 7;
-    for (int i = threadIdx.x; i < (r_end - r_begin) * lines_per_row; i += kStreamWarps * 32) {
-      const int r = i / lines_per_row, l = i - r * lines_per_row;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(Wb + (long long)(r_begin + r) * p.ldw * kElt + b0 + (size_t)l * 128));
-    }
-  }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-
-  // stage X[0..T) x [K range] (16-byte chunks; rows padded by 16 bytes)
-  const int cta_chunk0 = cta_blk0 * 4;
-  const int cta_chunks = min(cta_blk1 * 4, chunks) - cta_chunk0;
-  if (cp.stage_x) {
-    for (int i = threadIdx.x; i < p.T * cta_chunks; i += kStreamWarps * 32) {
-      const int t = i / cta_chunks, c = i - t * cta_chunks;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(Xb + (long long)t * p.ldx * kElt) + cta_chunk0 + c);
-      *reinterpret_cast<uint4*>(xs + (size_t)t * cp.x_row_bytes + (size_t)c * 16) = v;
-    }
-    __syncthreads();
-  }
-
-  const uint4* xr[NT];
-  const uint8_t* xsr[NT];
-  bool x_ok[NT];
-#pragma unroll
-  for (int nb = 0; nb < NT; ++nb) {
-    x_ok[nb] = nb * 8 + g < p.T;
-    xr[nb] = reinterpret_cast<const uint4*>(Xb + (long long)(nb * 8 + g) * p.ldx * kElt);
-    xsr[nb] = xs + (size_t)(nb * 8 + g) * cp.x_row_bytes;
-  }
-  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-
-  int tile = 0;
-  for (int row0 = r_begin; row0 < r_end; row0 += kStreamRows, ++tile) {
-    const bool row_lo_ok = row0 + g < r_end, row_hi_ok = row0 + g + 8 < r_end;
-    const uint4* w_lo = reinterpret_cast<const uint4*>(Wb + (long long)(row0 + g) * p.ldw * kElt);
-    const uint4* w_hi = reinterpret_cast<const uint4*>(Wb + (long long)(row0 + g + 8) * p.ldw * kElt);
-    float accf[NT][4];
-    int acci[NT][4];
-#pragma unroll
-    for (int nb = 0; nb < NT; ++nb)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { accf[nb][i] = 0.0f; acci[nb][i] = 0; }
-
-    for (int b0 = blk_begin; b0 < blk_end; b0 += UNROLL) {
-      uint4 lo[UNROLL], hi[UNROLL];
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int c = (b0 + u) * 4 + t4;
-        const bool ok = b0 + u < blk_end && c < chunks;
-        lo[u] = ok && row_lo_ok ? __ldcs(w_lo + c) : zero4;
-        hi[u] = ok && row_hi_ok ? __ldcs(w_hi + c) : zero4;
-      }
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) {
-        const int c = (b0 + u) * 4 + t4;
-        const bool ok = b0 + u < blk_end && c < chunks;
-#pragma unroll
-        for (int nb = 0; nb < NT; ++nb) {
-          uint4 xv = zero4;
-          if (ok && x_ok[nb]) {
-            if (cp.stage_x) xv = *reinterpret_cast<const uint4*>(xsr[nb] + (size_t)(c - cta_chunk0) * 16);
-            else xv = __ldg(xr[nb] + c);
-          }
-          if constexpr (KIND == STREAM_I8) {
-            mma_m16n8k32_s8(acci[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
-            mma_m16n8k32_s8(acci[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
-          } else if constexpr (KIND == STREAM_BF16) {
-            mma_m16n8k16_bf16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
-            mma_m16n8k16_bf16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
-          } else {
-            mma_m16n8k16_f16(accf[nb], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
-            mma_m16n8k16_f16(accf[nb], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
-          }
-        }
-      }
-    }
-
-    if (tile != 0) __syncthreads();                     // the previous tile's warp sums have been read
-#pragma unroll
-    for (int nb = 0; nb < NT; ++nb) {
-      uint32_t w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) w[i] = KIND == STREAM_I8 ? (uint32_t)acci[nb][i] : __float_as_uint(accf[nb][i]);
-      uint32_t* rw = red + (size_t)warp * kStreamRows * TP;
-      rw[g * TP + nb * 8 + 2 * t4] = w[0];
-      rw[g * TP + nb * 8 + 2 * t4 + 1] = w[1];
-      rw[(g + 8) * TP + nb * 8 + 2 * t4] = w[2];
-      rw[(g + 8) * TP + nb * 8 + 2 * t4 + 1] = w[3];
-    }
-    __syncthreads();
-    // this CTA's partial block of the tile: the eight warp sums in warp order
-    for (int i = threadIdx.x; i < kStreamRows * NT * 8; i += kStreamWarps * 32) {
-      const int r = i / (NT * 8), t = i - r * (NT * 8);
-      uint32_t accw;
-      if constexpr (KIND == STREAM_I8) {
-        int v = 0;
-#pragma unroll
-        for (int w = 0; w < kStreamWarps; ++w) v += (int)red[((size_t)w * kStreamRows + r) * TP + t];
-        accw = (uint32_t)v;
-      } else {
-        float v = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kStreamWarps; ++w) v += __uint_as_float(red[((size_t)w * kStreamRows + r) * TP + t]);
-        accw = __float_as_uint(v);
-      }
-      part[((size_t)tile * kStreamRows + r) * TP + t] = accw;
-    }
-  }
-
-  // exchange: every CTA of the cluster has parked its partial blocks; rank r finishes the r-th share of the rows
-  stream_cluster_sync();
-  {
-    const int rows = r_end - r_begin;
-    const int my0 = (int)((long long)rank * rows / cp.ck), my1 = (int)((long long)(rank + 1) * rows / cp.ck);
-    const bool rows_contig = p.stride_r == 1;
-    const uint32_t part_addr = static_cast<uint32_t>(__cvta_generic_to_shared(part));
-    for (int i = threadIdx.x; i < (my1 - my0) * p.T; i += kStreamWarps * 32) {
-      int r, t;
-      if (rows_contig) { r = my0 + i % (my1 - my0); t = i / (my1 - my0); }
-      else { t = i % p.T; r = my0 + i / p.T; }
-      const uint32_t off = part_addr + (uint32_t)((r * TP + t) * 4);       // r = tile * 16 + row in tile
-      uint32_t accw;
-      if constexpr (KIND == STREAM_I8) {
-        int v = 0;
-        for (int c = 0; c < cp.ck; ++c) v += (int)stream_ld_dsmem(off, (uint32_t)c);
-        accw = (uint32_t)v;
-      } else {
-        float v = 0.0f;
-        for (int c = 0; c < cp.ck; ++c) v += __uint_as_float(stream_ld_dsmem(off, (uint32_t)c));
-        accw = __float_as_uint(v);
-      }
-      stream_finish<EPI>(p, accw, r_begin + r, t);
-    }
-  }
-  stream_cluster_sync();          // nobody's shared memory goes away while a peer may still read it
-}
-
 }  // namespace mp

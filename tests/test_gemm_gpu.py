@@ -819,65 +819,6 @@ def test_int8_cluster_splitk_exact(api, oracle, monkeypatch, split):
     assert api.device_status() == 0
 
 
-# ------------------------------------------------------------------ cluster-K streaming kernel
-@pytest.mark.parametrize("m,n,k,ck", [
-    (16, 4096, 4096, 2), (32, 4096, 4096, 2), (32, 4096, 4096, 1), (9, 1024, 8192, 4), (1, 1024, 8192, 4), (8, 1024, 28672, 8),
-    (32, 1024, 8192, 4), (24, 1000, 8200, 4), (64, 2048, 4096, 2), (40, 513, 2056, 2), (4096, 20, 4096, 2), (700, 3, 16384, 8),
-    (5, 130, 72, 1), (17, 33, 4096, 4)])
-def test_fp16_cluster_k_streaming_kernel(api, oracle, m, n, k, ck):
-    """The streaming kernel whose clusters cut K: staged X ranges, partial blocks exchanged through distributed shared
-    memory and added in rank order.  Against the oracle, exact on integers, reproducible, with alpha / beta, both
-    mappings (narrow side on m or on n), ragged rows, ragged K ranges."""
-    a = rng.normal(140, 0, (m, k), 0.05)
-    b = rng.normal(140, 1, (n, k), 0.05)
-    c0 = rng.normal(140, 2, (n, m), 1.0)
-    ref = oracle.gemm_f16_rcc(a, b)
-    A, B = dev(a), dev(b)
-    got = api.gemm_rcc_tile(A, B, 3, 16, kc=ck).cpu().numpy()
-    close_f16(got, ref)
-    assert np.array_equal(got, api.gemm_rcc_tile(A, B, 3, 16, kc=ck).cpu().numpy())
-    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=-1).cpu().numpy(), ref)            # the plain streaming kernel
-    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=0).cpu().numpy(), ref)             # the library's own choice
-    ref_ab = oracle.gemm_f16_rcc(a, b, 0.5, -1.5, c0)
-    close_f16(api.gemm_rcc_tile(A, B, 3, 16, kc=ck, c_nm=dev(c0), alpha=0.5, beta=-1.5).cpu().numpy(), ref_ab)
-    ai = rng.small_ints(141, 0, (m, k), lo=-1, hi=1)
-    bi = rng.small_ints(141, 1, (n, k))
-    exact = _exact_ref(ai, bi)
-    if np.abs(exact).max() < 2048:
-        assert np.array_equal(api.gemm_rcc_tile(dev(ai), dev(bi), 3, 16, kc=ck).cpu().numpy(), exact.astype(np.float16))
-    assert api.device_status() == 0
-
-
-@pytest.mark.parametrize("m,n,k,ck", [(32, 1024, 8192, 2), (16, 4096, 16384, 4), (9, 600, 4096, 1), (2000, 12, 8192, 2)])
-def test_int8_cluster_k_streaming_kernel_bit_exact(api, oracle, monkeypatch, m, n, k, ck):
-    a = rng.int8_uniform(142, 0, (m, k))
-    b = rng.int8_uniform(142, 1, (n, k))
-    c0 = rng.int8_uniform(142, 2, (n, m)).astype(np.int32) * 37
-    ref = oracle.gemm_i8_rcc(a, b)
-    got = api.gemm_rcc_tile(dev(a), dev(b), 3, 16, kc=ck).cpu().numpy()
-    assert np.array_equal(got, ref)
-    got_ab = api.gemm_rcc_tile(dev(a), dev(b), 3, 16, kc=ck, c_nm=dev(c0), alpha=2.0, beta=-3.0).cpu().numpy()
-    assert np.array_equal(got_ab, oracle.gemm_i8_rcc(a, b, 2, -3, c0))
-    # the scaled epilogue reaches the cluster-K kernel when the library is allowed to pick it by itself
-    monkeypatch.setenv("MOONPOLY_ENABLE_STREAM_CLUSTER", "1")
-    api.reload_env()
-    M, N = (m, n)
-    sa = rng.uniform(142, 3, (M,), 0.001, 0.02)
-    sb = rng.uniform(142, 4, (N,), 0.001, 0.02)
-    bias = rng.uniform(142, 5, (N,), -1.0, 1.0).astype(np.float16)
-    L = api.lib()
-    out = torch.empty((M, N), dtype=torch.float16, device=DEV)
-    A, B, SA, SB, BI = dev(a), dev(b), dev(sa), dev(sb), dev(bias)
-    rc = L.mp_scaled_mm_i8_tile(3, 16, 1, M, N, k, A.data_ptr(), k, B.data_ptr(), k, SA.data_ptr(), 0, SB.data_ptr(), 0,
-                                BI.data_ptr(), out.data_ptr(), N, 0, None)
-    assert rc == 0, L.mp_last_error_string()
-    torch.cuda.synchronize()
-    monkeypatch.delenv("MOONPOLY_ENABLE_STREAM_CLUSTER")
-    api.reload_env()
-    assert np.array_equal(out.cpu().numpy().view(np.uint16), oracle.scaled_mm_i8(a, b, sa, sb, bias).view(np.uint16))
-    assert api.device_status() == 0
-
-
 # ------------------------------------------------------------------ 256-row tiles with K slices
 @pytest.mark.parametrize("orient,bn,split,m,n,k", [(4, 256, 4, 512, 4096, 4096), (5, 256, 2, 1000, 1023, 4096),
                                                     (4, 128, 8, 257, 300, 2120), (5, 192, 3, 600, 700, 1096),
