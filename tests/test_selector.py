@@ -153,7 +153,7 @@ def test_bad_arguments(api):
 
 
 def test_selection_overhead_budget(api, tmp_path):
-    """<= 5 us per shape on the host at first sight of a shape, <= 1 us memoised: timed in C around mp_select_plan
+    """<= 5 us per shape on the host at first sight of a shape, <= 2 us memoised: timed in C around mp_select_plan
     (tests/host_timing/select_timing.c), best of 24 passes so a busy host does not fail the test."""
     here = os.path.dirname(os.path.abspath(__file__))
     exe = str(tmp_path / "select_timing")
@@ -165,7 +165,7 @@ def test_selection_overhead_budget(api, tmp_path):
     cold, warm = float(out[1]) * 1e-9, float(out[3]) * 1e-9
     print(f"selection: first sight {cold * 1e6:.2f} us, memoised {warm * 1e6:.2f} us")
     assert cold < 5e-6
-    assert warm < 1e-6
+    assert warm < 2e-6
 
 
 def test_measured_tables_name_runnable_kernels(api):
