@@ -102,21 +102,28 @@ def run_stack(rank: int, world: int, dev, dist, steps: int = 64, warmup: int = 3
             gather = "nccl (peer mapping unavailable" + (": " + err if err else " on another rank") + ")"
     epoch = [0]
 
+    # pointer objects are built once: a step then costs one ctypes call per GEMM (and per barrier), not a dozen
+    # Python object constructions on top of it -- with the weights cut 8 ways those were a third of a decode step
+    px = {k: vp(t.data_ptr()) for k, t in x_in.items()}
+    pw = [[vp(w.data_ptr()) for w in ws] for ws in weights]
+    py = [vp(t.data_ptr()) for t in y_loc]
+    fp16 = api.MP_FP16
+    linear, linear_gather, peer_barrier = L.mp_linear, L.mp_linear_gather, L.mp_peer_barrier
+
     def step(m: int) -> None:
         for layer in range(layers):
-            ws = weights[layer % resident]
+            ws = pw[layer % resident]
             for j, (_, n, k, g) in enumerate(shard):
                 if g and j in fused and (not auto or fused_gather_pays(m, n, world)):
                     _, dst, flag_table = fused[j]
-                    rc = L.mp_linear_gather(api.MP_FP16, m, n, k, vp(x_in[k].data_ptr()), vp(ws[j].data_ptr()), dst, world,
-                                            n * world, rank * n, st)
+                    rc = linear_gather(fp16, m, n, k, px[k], ws[j], dst, world, n * world, rank * n, st)
                     if rc == 0:
                         epoch[0] += 1
-                        rc = L.mp_peer_barrier(flag_table, world, rank, epoch[0], 0, st)
+                        rc = peer_barrier(flag_table, world, rank, epoch[0], 0, st)
                     if rc:
                         raise RuntimeError(L.mp_last_error_string().decode())
                     continue
-                rc = L.mp_linear(api.MP_FP16, m, n, k, vp(x_in[k].data_ptr()), vp(ws[j].data_ptr()), vp(y_loc[j].data_ptr()), st)
+                rc = linear(fp16, m, n, k, px[k], ws[j], py[j], st)
                 if rc:
                     raise RuntimeError(L.mp_last_error_string().decode())
                 if g and do_gather:
