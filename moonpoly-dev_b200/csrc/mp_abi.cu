@@ -616,7 +616,8 @@ int launch_simt_f32(const SimtParams& sp, cudaStream_t stream) {
                          (reinterpret_cast<uintptr_t>(sp.B) & 15) == 0;
     if (aligned) {
       dim3 grid((sp.m + TI - 1) / TI, (sp.n + TJ - 1) / TJ, sp.split_k);
-      sgemm_f32_kernel<TI / 16, TJ / 16><<<grid, 256, 0, stream>>>(sp);
+      if constexpr (TI == 64 && TJ == 64) sgemm_f32_kernel<16, 16, 4, 4><<<grid, 256, 0, stream>>>(sp);
+      else sgemm_f32_kernel<TI / 8, TJ / 8, 8, 8><<<grid, (TI / 8) * (TJ / 8), 0, stream>>>(sp);
       MP_CUDA_TRY(cudaGetLastError());
       g_launches.fetch_add(1, std::memory_order_relaxed);
       if (sp.split_k > 1) {

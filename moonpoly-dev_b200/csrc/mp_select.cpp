@@ -87,7 +87,9 @@ struct Env {
   int p2_min_n = 512;
   float p2_max_tail_ratio = 0.25f, p2_margin = 0.90f, p3_margin = 0.97f;
   float gen_margin = 1.0f;
-  int fp32_p3_min_k = 1024, fp32_p3_min_part_k = 256;
+  // FP32 split-K gates: the reference's defaults are 1024 / 256 (its split pays later); these kernels gain from
+  // K = 256 on (510 x 512 x 512: 35 -> 23 us with 4 slices), the cost model decides above the gate
+  int fp32_p3_min_k = 256, fp32_p3_min_part_k = 64;
   float fp32_p3_margin = 0.97f;
   int int8_p3_min_k = 2048, int8_p3_min_part_k = 512;
   float int8_p3_margin = 0.97f;
@@ -131,8 +133,8 @@ void load_env() {
   e.p2_margin = env_float("MOONPOLY_PATTERN2_MARGIN", 0.90f);
   e.p3_margin = env_float("MOONPOLY_PATTERN3_MARGIN", 0.97f);
   e.gen_margin = env_float("MOONPOLY_GENERATED_SELECTOR_MARGIN", 1.0f);
-  e.fp32_p3_min_k = env_int("MOONPOLY_FP32_PATTERN3_MIN_K", 1024);
-  e.fp32_p3_min_part_k = env_int("MOONPOLY_FP32_PATTERN3_MIN_PART_K", 256);
+  e.fp32_p3_min_k = env_int("MOONPOLY_FP32_PATTERN3_MIN_K", 256);
+  e.fp32_p3_min_part_k = env_int("MOONPOLY_FP32_PATTERN3_MIN_PART_K", 64);
   e.fp32_p3_margin = env_float("MOONPOLY_FP32_PATTERN3_MARGIN", 0.97f);
   e.int8_p3_min_k = env_int("MOONPOLY_INT8_PATTERN3_MIN_K", 2048);
   e.int8_p3_min_part_k = env_int("MOONPOLY_INT8_PATTERN3_MIN_PART_K", 512);

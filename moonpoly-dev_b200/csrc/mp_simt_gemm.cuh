@@ -162,23 +162,29 @@ simt_gemm_kernel(const SimtParams p) {
 }
 
 // FP32 tile kernel for operands whose rows are 16-byte aligned (lda, ldb multiples of 4, aligned bases): the same
-// computation as simt_gemm_kernel<float, SEPI_F32, 16*RI, 16*RJ> with every sum formed in the same order (ascending
+// computation as simt_gemm_kernel<float, SEPI_F32, RI*TX, RJ*TY> with every sum formed in the same order (ascending
 // k, one fused multiply-add per term), built for throughput.  Global loads are 16 bytes along K, stored transposed
 // into shared memory ([k][row], conflict-free), the next K step of 16 is fetched into registers while the current
-// one is multiplied (two shared-memory buffers, one barrier per step), a thread owns RI x RJ outputs as rows
-// {4*tx..4*tx+3, 64+4*tx..} x columns {4*ty.., 64+4*ty..} so that both operands arrive as 16-byte shared-memory reads,
+// one is multiplied (two shared-memory buffers, one barrier per step), a thread owns 4 x 4 or 8 x 8 outputs as groups
+// of four neighbouring rows x groups of four neighbouring columns so that both operands arrive as 16-byte
+// shared-memory reads,
 // and the products go through packed FP32 FMAs (two neighbouring rows per instruction).
-template <int RI, int RJ>
-__global__ void __launch_bounds__(256)
+template <int TX, int TY, int RI, int RJ>
+__global__ void __launch_bounds__(TX * TY)
 sgemm_f32_kernel(const SimtParams p) {
-  constexpr int TK = 16, TI = 16 * RI, TJ = 16 * RJ;
-  constexpr int NA = TI * 4 / 256, NB = TJ * 4 / 256;           // 16-byte global loads per thread and K step
-  static_assert((RI == 4 || RI == 8) && (RJ == 4 || RJ == 8), "tiles of 64 or 128");
+  // TX x TY threads with RI x RJ outputs each.  Measured per K step of 16 on one CTA per SM: a 64 x 64 tile as 256
+  // threads of 4 x 4 outputs 1.0 us (bound by its shared-memory reads: two 16-byte reads per 8 packed FMAs), as 64
+  // threads of 8 x 8 1.3 us (two warps cannot hide the global loads); 128 x 64 as 128 threads of 8 x 8 is 9 % faster
+  // than as 256 threads of 8 x 4.  The launch picks 256 x (4 x 4), 128 x (8 x 8) and 256 x (8 x 8).
+  constexpr int TK = 16, NT = TX * TY, TI = RI * TX, TJ = RJ * TY, HI = 4 * TX, HJ = 4 * TY;
+  constexpr int NA = TI * 4 / NT, NB = TJ * 4 / NT;             // 16-byte global loads per thread and K step
+  static_assert((TX == 8 || TX == 16) && (TY == 8 || TY == 16) && (RI == 4 || RI == 8) && (RJ == 4 || RJ == 8) &&
+                NA >= 1 && NB >= 1, "tiles of 64 or 128");
   __shared__ __align__(16) float As[2][TK][TI];
   __shared__ __align__(16) float Bs[2][TK][TJ];
   const float* A = reinterpret_cast<const float*>(p.A);
   const float* B = reinterpret_cast<const float*>(p.B);
-  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+  const int t = threadIdx.x, tx = t % TX, ty = t / TX;
   const int i0 = blockIdx.x * TI, j0 = blockIdx.y * TJ;
   const int k_begin = blockIdx.z * p.k_per_slice;
   const int k_end = min(p.k, k_begin + p.k_per_slice);
@@ -187,7 +193,7 @@ sgemm_f32_kernel(const SimtParams p) {
   auto fetch = [&](int k0) {
 #pragma unroll
     for (int u = 0; u < NA; ++u) {
-      const int f = t + 256 * u, row = f % TI, kq = f / TI;
+      const int f = t + NT * u, row = f % TI, kq = f / TI;
       const int gi = i0 + row, gk = k0 + kq * 4;
       float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (gi < p.m) {
@@ -203,7 +209,7 @@ sgemm_f32_kernel(const SimtParams p) {
     }
 #pragma unroll
     for (int u = 0; u < NB; ++u) {
-      const int f = t + 256 * u, row = f % TJ, kq = f / TJ;
+      const int f = t + NT * u, row = f % TJ, kq = f / TJ;
       const int gj = j0 + row, gk = k0 + kq * 4;
       float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (gj < p.n) {
@@ -221,13 +227,13 @@ sgemm_f32_kernel(const SimtParams p) {
   auto stash = [&](int buf) {
 #pragma unroll
     for (int u = 0; u < NA; ++u) {
-      const int f = t + 256 * u, row = f % TI, kq = f / TI;
+      const int f = t + NT * u, row = f % TI, kq = f / TI;
       As[buf][kq * 4 + 0][row] = ra[u].x; As[buf][kq * 4 + 1][row] = ra[u].y;
       As[buf][kq * 4 + 2][row] = ra[u].z; As[buf][kq * 4 + 3][row] = ra[u].w;
     }
 #pragma unroll
     for (int u = 0; u < NB; ++u) {
-      const int f = t + 256 * u, row = f % TJ, kq = f / TJ;
+      const int f = t + NT * u, row = f % TJ, kq = f / TJ;
       Bs[buf][kq * 4 + 0][row] = rb[u].x; Bs[buf][kq * 4 + 1][row] = rb[u].y;
       Bs[buf][kq * 4 + 2][row] = rb[u].z; Bs[buf][kq * 4 + 3][row] = rb[u].w;
     }
@@ -254,13 +260,13 @@ sgemm_f32_kernel(const SimtParams p) {
       float bv[RJ];
 #pragma unroll
       for (int h = 0; h < RI / 4; ++h) {
-        const float4 v = *reinterpret_cast<const float4*>(&As[cur][kk][64 * h + 4 * tx]);
+        const float4 v = *reinterpret_cast<const float4*>(&As[cur][kk][HI * h + 4 * tx]);
         a2[2 * h] = make_float2(v.x, v.y);
         a2[2 * h + 1] = make_float2(v.z, v.w);
       }
 #pragma unroll
       for (int h = 0; h < RJ / 4; ++h) {
-        const float4 v = *reinterpret_cast<const float4*>(&Bs[cur][kk][64 * h + 4 * ty]);
+        const float4 v = *reinterpret_cast<const float4*>(&Bs[cur][kk][HJ * h + 4 * ty]);
         bv[4 * h] = v.x; bv[4 * h + 1] = v.y; bv[4 * h + 2] = v.z; bv[4 * h + 3] = v.w;
       }
 #pragma unroll
@@ -275,17 +281,17 @@ sgemm_f32_kernel(const SimtParams p) {
     cur ^= 1;
   }
 
-  // thread's rows: i0 + 64*h + 4*tx + e; columns: j0 + 64*h + 4*ty + e
+  // thread's rows: i0 + HI*h + 4*tx + e; columns: j0 + HJ*h + 4*ty + e
   const bool vec_out = p.split_k > 1 ? (p.m % 4 == 0)
                                      : (p.c_stride_i == 1 && p.c_stride_j % 4 == 0 &&
                                         (reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
 #pragma unroll
   for (int b = 0; b < RJ; ++b) {
-    const int j = j0 + 64 * (b / 4) + 4 * ty + (b & 3);
+    const int j = j0 + HJ * (b / 4) + 4 * ty + (b & 3);
     if (j >= p.n) continue;
 #pragma unroll
     for (int h = 0; h < RI / 4; ++h) {
-      const int i = i0 + 64 * h + 4 * tx;
+      const int i = i0 + HI * h + 4 * tx;
       if (i >= p.m) continue;
       const float v[4] = {acc[2 * h][b].x, acc[2 * h][b].y, acc[2 * h + 1][b].x, acc[2 * h + 1][b].y};
       if (p.split_k > 1) {
