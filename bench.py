@@ -17,7 +17,8 @@ ranks and `value` counts the FLOPs of all ranks.
 
 `e2e` is the same metric with the activations A copied from pinned host memory and C copied back
 to pinned host memory inside the timed region of every GEMM (the weight stays resident, as a
-model parameter does).  `roofline` describes the dominant kernel (the tcgen05 GEMM at M = 4096)
+model parameter does; two staging slots per shape, uploads and downloads on their own streams
+overlap the GEMMs).  `roofline` describes the dominant kernel (the tcgen05 GEMM at M = 4096)
 and carries the whole-sweep figures too: `sweep_geomean_frac`, `per_shape_frac` (fraction of
 max(FLOPs/peak, bytes/HBM) per M), and the side tables `int8_scaled_mm`, `fp16_splitk_decode`,
 `fp32_m37` and `stack` (the Llama-3-70B-shaped sharded linear stack at this GPU count).
@@ -53,6 +54,12 @@ WORKLOAD = "fp16_rcc_dynamic_m_sweep_n4096_k4096"
 
 def reps_for(m: int) -> int:
     return 16 if m <= 255 else (8 if m <= 1023 else 4)
+
+
+def e2e_reps(m: int) -> int:
+    """GEMMs per shape and step in the e2e leg: the device sweep's (uploads and downloads are pipelined around the
+    GEMMs; a two-call pipeline would be mostly fill and drain)."""
+    return reps_for(m)
 
 
 def flops(m: int) -> float:
@@ -379,7 +386,6 @@ def run_ours(args, rank, world, local_rank):
     a_dev = {m: [a_host[m].to(dev), a_host[m].to(dev).clone()] for m in SWEEP_M}
     c_dev = {m: torch.empty((N_DIM, m), dtype=torch.float16, device=dev) for m in SWEEP_M}
     c_host = {m: torch.empty((N_DIM, m), dtype=torch.float16).pin_memory() for m in SWEEP_M}
-    a_stage = {m: torch.empty((m, K_DIM), dtype=torch.float16, device=dev) for m in SWEEP_M}
 
     mp_gemm = L.mp_gemm
     arg_cache = {}
@@ -451,51 +457,43 @@ def run_ours(args, rank, world, local_rank):
                 events[m][1].record(stream)
 
     # e2e leg: activations come from pinned host memory and the result goes back to pinned host memory inside the
-    # timed region.  Small problems run copy -> GEMM -> copy on one stream (the copies are a few microseconds and the
-    # host calls dominate); from PIPELINE_MIN_M rows on, two staging slots and two copy streams overlap the upload
-    # of GEMM i+1 and the download of GEMM i-1 with GEMM i (PCIe is full duplex).
-    PIPELINE_MIN_M = 256
+    # timed region.  Two staging slots and two copy streams overlap the upload of GEMM i+1 and the download of GEMM
+    # i-1 with GEMM i (PCIe is full duplex).  Measured against copy -> GEMM -> copy on one stream: M=1 27 -> 18 us
+    # (each small copy costs ~10 us of DMA latency when it is waited for), M=128 70 -> 36 us, M=4096 1012 -> 869 us.
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    a_slot = {m: [torch.empty((m, K_DIM), dtype=torch.float16, device=dev) for _ in range(2)] for m in SWEEP_M if m >= PIPELINE_MIN_M}
-    c_slot = {m: [torch.empty((N_DIM, m), dtype=torch.float16, device=dev) for _ in range(2)] for m in SWEEP_M if m >= PIPELINE_MIN_M}
-    c_host2 = {m: [c_host[m], torch.empty((N_DIM, m), dtype=torch.float16).pin_memory()] for m in SWEEP_M if m >= PIPELINE_MIN_M}
+    a_slot = {m: [torch.empty((m, K_DIM), dtype=torch.float16, device=dev) for _ in range(2)] for m in SWEEP_M}
+    c_slot = {m: [torch.empty((N_DIM, m), dtype=torch.float16, device=dev) for _ in range(2)] for m in SWEEP_M}
+    c_host2 = {m: [c_host[m], torch.empty((N_DIM, m), dtype=torch.float16).pin_memory()] for m in SWEEP_M}
 
     def sweep_e2e(events):
         for m in SWEEP_M:
-            r = max(2, reps_for(m) // 4)
+            r = e2e_reps(m)
             if events is not None:
                 events[m][0].record(stream)
-            if m < PIPELINE_MIN_M:
-                for i in range(r):
-                    counter[0] += 1
-                    a_stage[m].copy_(a_host[m], non_blocking=True)
-                    gemm(m, a_stage[m], weights[counter[0] % WEIGHT_COPIES], c_dev[m])
-                    c_host[m].copy_(c_dev[m], non_blocking=True)
-            else:
-                ev_in = [torch.cuda.Event() for _ in range(2)]
-                ev_done = [torch.cuda.Event() for _ in range(2)]
-                ev_out = [torch.cuda.Event() for _ in range(2)]
-                s_in.wait_stream(stream)                    # nothing of this shape starts before its start event
-                s_out.wait_stream(stream)
-                for i in range(r):
-                    counter[0] += 1
-                    k = i & 1
-                    with torch.cuda.stream(s_in):
-                        if i >= 2:
-                            s_in.wait_event(ev_done[k])     # the GEMM that read this slot has finished
-                        a_slot[m][k].copy_(a_host[m], non_blocking=True)
-                        ev_in[k].record(s_in)
-                    stream.wait_event(ev_in[k])
+            ev_in = [torch.cuda.Event() for _ in range(2)]
+            ev_done = [torch.cuda.Event() for _ in range(2)]
+            ev_out = [torch.cuda.Event() for _ in range(2)]
+            s_in.wait_stream(stream)                    # nothing of this shape starts before its start event
+            s_out.wait_stream(stream)
+            for i in range(r):
+                counter[0] += 1
+                k = i & 1
+                with torch.cuda.stream(s_in):
                     if i >= 2:
-                        stream.wait_event(ev_out[k])        # the download of this slot's previous result has finished
-                    gemm(m, a_slot[m][k], weights[counter[0] % WEIGHT_COPIES], c_slot[m][k])
-                    ev_done[k].record(stream)
-                    with torch.cuda.stream(s_out):
-                        s_out.wait_event(ev_done[k])
-                        c_host2[m][k].copy_(c_slot[m][k], non_blocking=True)
-                        ev_out[k].record(s_out)
-                stream.wait_stream(s_out)                   # the end event covers every copy
-                stream.wait_stream(s_in)
+                        s_in.wait_event(ev_done[k])     # the GEMM that read this slot has finished
+                    a_slot[m][k].copy_(a_host[m], non_blocking=True)
+                    ev_in[k].record(s_in)
+                stream.wait_event(ev_in[k])
+                if i >= 2:
+                    stream.wait_event(ev_out[k])        # the download of this slot's previous result has finished
+                gemm(m, a_slot[m][k], weights[counter[0] % WEIGHT_COPIES], c_slot[m][k])
+                ev_done[k].record(stream)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[k])
+                    c_host2[m][k].copy_(c_slot[m][k], non_blocking=True)
+                    ev_out[k].record(s_out)
+            stream.wait_stream(s_out)                   # the end event covers every copy
+            stream.wait_stream(s_in)
             if events is not None:
                 events[m][1].record(stream)
 
@@ -574,7 +572,7 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         peaks = load_peaks()
         per_launch_ms = {m: per_ms[m] / reps_for(m) for m in SWEEP_M}
-        e2e_launch_ms = {m: e2e_per_ms[m] / max(2, reps_for(m) // 4) for m in SWEEP_M}
+        e2e_launch_ms = {m: e2e_per_ms[m] / e2e_reps(m) for m in SWEEP_M}
         tfl = {m: world * flops(m) / (per_launch_ms[m] * 1e-3) / 1e12 for m in SWEEP_M}
         e2e_tfl = {m: world * flops(m) / (e2e_launch_ms[m] * 1e-3) / 1e12 for m in SWEEP_M}
         per_shape = []
@@ -598,8 +596,8 @@ def run_ours(args, rank, world, local_rank):
         # CPU baseline: the oracle on this box's host cores, bounded sample (all 14 shapes; rows sampled above 128)
         cpu_res, cores = cpu_time_shapes(SWEEP_M, args.cpu_budget)
         cpu_val = geomean([flops(m) / dt / 1e12 for m, dt in cpu_res])
-        h2d = sum(max(2, reps_for(m) // 4) * m * K_DIM * 2 for m in SWEEP_M)
-        d2h = sum(max(2, reps_for(m) // 4) * m * N_DIM * 2 for m in SWEEP_M)
+        h2d = sum(e2e_reps(m) * m * K_DIM * 2 for m in SWEEP_M)
+        d2h = sum(e2e_reps(m) * m * N_DIM * 2 for m in SWEEP_M)
         extras = {}
         if not args.no_extras:
             extras = extra_sections(api, L, st, dev, peaks)
@@ -644,7 +642,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": geomean([e2e_tfl[m] for m in SWEEP_M]), "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "per_shape_us": {str(m): round(e2e_launch_ms[m] * 1e3, 2) for m in SWEEP_M},
-                    "note": "A copied from pinned host and C copied back to pinned host per GEMM, weight resident; M >= 256: two staging slots, uploads and downloads on their own streams overlap the GEMMs; M < 256: copy -> GEMM -> copy on one stream (each small copy costs ~10 us of DMA latency: replaying the chain from a CUDA graph was measured and changes nothing)"},
+                    "note": "A copied from pinned host and C copied back to pinned host per GEMM, weight resident; two staging slots, uploads and downloads on their own streams overlap the GEMMs (a serial copy -> GEMM -> copy chain costs ~10 us of DMA latency per small copy: 27 us at M=1)"},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
