@@ -3,13 +3,19 @@
 // Used for (a) the FP32 path -- the reference's FP32 kernels are SIMT FFMA, not TF32
 // (moonpoly/core/fp32/fp32_rcc.cu:193-2208, OpClassSimt), so exact fp32 multiply-add semantics are
 // kept and no tensor core is involved -- and (b) FP16 / INT8 problems whose K or base pointers do
-// not meet the 16-byte alignment TMA needs (the reference keeps pids with alignment 1/2/4 for those,
-// moonpoly/core/fp16/fp16_rcc_cost.cu:32-36).
+// not meet the 16-byte alignment TMA needs, when no padded copy of the operands can be made (the
+// reference keeps pids with alignment 1/2/4 for those, moonpoly/core/fp16/fp16_rcc_cost.cu:32-36).
 //
-// A tile of TI x TJ outputs per 256-thread CTA, K walked in steps of 16 through shared memory,
-// every thread owning a (TI/16) x (TJ/16) register block.  Optional parallel split-K writes raw
-// partials to a workspace (grid.z = slices) and a second kernel sums them in slice order
-// (the GemmSplitKParallel + ReduceSplitK arrangement of moonpoly/core/fp32/fp32_rcc.cu:136-187).
+// Kernels in this file:
+//   simt_gemm_kernel    the plain tile: TI x TJ outputs per 256-thread CTA, K walked in steps of 16 through
+//                       shared memory, every thread owning a (TI/16) x (TJ/16) register block; any type, any
+//                       alignment
+//   sgemm_f32_kernel    FP32 tiles of 64 / 128 on 16-byte aligned rows, built for throughput
+//   gemv_f32_kernel     FP32, at most 8 rows on the narrow side: a streaming kernel
+//   tile_f32_kernel     FP32, 9..64 rows on the narrow side: square-ish tiles, K split over a cluster
+// Optional parallel split-K of the tile kernels writes raw partials to a workspace (grid.z = slices) and
+// simt_splitk_reduce_kernel sums them in slice order (the GemmSplitKParallel + ReduceSplitK arrangement of
+// moonpoly/core/fp32/fp32_rcc.cu:136-187).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>

@@ -16,7 +16,9 @@
 // memory (deterministic).  A dot product does not care in which order k is visited as long as both
 // operands agree, so a lane loads 16 contiguous bytes of its row and spreads them over the k-slots
 // of two consecutive MMAs; the X fragment is loaded with the same rule.  Every load of W is a full
-// 16-byte vector and the four lanes of a row cover 64 contiguous bytes.
+// 16-byte vector and the four lanes of a row cover 64 contiguous bytes.  Two optional splits multiply
+// the CTAs when the rows of W cannot fill the GPU: the rows of X over neighbouring CTAs (t_split) and K
+// over the CTAs of a cluster (k_split); see StreamParams.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
